@@ -1,0 +1,55 @@
+// Shared declarations of the kernel library: dtype codes, error reporting and
+// scalar load/store helpers. Every exported function returns 0 on success and a
+// non-zero code after storing a message that cuca_last_error() returns.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define CUCA_F32 0
+#define CUCA_BF16 1
+
+#define CUCA_API extern "C" __attribute__((visibility("default")))
+
+// Device-side error word layout: kernels that find a bad index record a code
+// and skip the access instead of faulting.
+#define CUCA_ERR_TOKEN_RANGE 1
+#define CUCA_ERR_BLOCK_RANGE 2
+#define CUCA_ERR_WAIT_TIMEOUT 3
+
+void cuca_set_error(const char* fmt, ...);
+
+#define CUCA_CHECK_LAUNCH(name)                                                     \
+  do {                                                                              \
+    cudaError_t e__ = cudaGetLastError();                                           \
+    if (e__ != cudaSuccess) {                                                       \
+      cuca_set_error("%s: launch failed: %s", name, cudaGetErrorString(e__));       \
+      return 2;                                                                     \
+    }                                                                               \
+  } while (0)
+
+#define CUCA_REQUIRE(cond, ...)                                                     \
+  do {                                                                              \
+    if (!(cond)) {                                                                  \
+      cuca_set_error(__VA_ARGS__);                                                  \
+      return 1;                                                                     \
+    }                                                                               \
+  } while (0)
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}

@@ -1,0 +1,126 @@
+"""Thin Python wrappers over the kernel library: tensors in, launches out.
+
+Each function checks what the kernel cannot (device, dtype, contiguity) and
+launches on torch's current stream. Nothing here computes on the host or falls
+back to torch operators.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import library
+
+F32, BF16 = 0, 1
+EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _CODES[dtype]
+    except KeyError:
+        raise library.KernelError(f"kernels take float32 or bfloat16, not {dtype}") from None
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+def _cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise library.KernelError("kernel arguments must live on the CUDA device (there is no CPU path)")
+
+
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, err: torch.Tensor) -> None:
+    _cuda(table, tokens, out)
+    lib = library.load()
+    V, E = table.shape
+    library.check(lib.cuca_embed(_p(table), dtype_code(table.dtype), _p(tokens), _p(out), tokens.shape[0], E, V,
+                                 _p(err), _stream()), "embed")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float, rows=None) -> None:
+    _cuda(x, weight, out)
+    lib = library.load()
+    n = out.shape[0] if rows is None else rows.shape[0]
+    library.check(lib.cuca_rmsnorm(_p(x), _p(weight), dtype_code(weight.dtype), _p(out), dtype_code(out.dtype),
+                                   _p(rows), n, x.shape[-1], float(eps), _stream()), "rmsnorm")
+
+
+def rope_store(qkv, positions, seq_of_row, tables, cos, sin, rotary_dim, kpool, vpool, block_size,
+               n_heads, n_kv_heads, head_dim, err) -> None:
+    """Rotate q (in place) and k, write k and v to their pages. `tables` is [S, width] int32;
+    pools are [n_blocks, n_kv_heads, block_size, head_dim] (None with n_kv_heads == 0)."""
+    _cuda(qkv, positions, seq_of_row)
+    lib = library.load()
+    n_blocks = kpool.shape[0] if kpool is not None else 0
+    table_rows = cos.shape[0] if cos is not None else 0
+    library.check(lib.cuca_rope_store(
+        _p(qkv), dtype_code(qkv.dtype), _p(positions), _p(seq_of_row), _p(tables),
+        tables.shape[1] if tables is not None else 0, _p(cos), _p(sin), table_rows, int(rotary_dim),
+        _p(kpool), _p(vpool), n_blocks, int(block_size), qkv.shape[0], n_heads, n_kv_heads, head_dim,
+        _p(err), _stream()), "rope_store")
+
+
+def swiglu(gate_up, out) -> None:
+    _cuda(gate_up, out)
+    lib = library.load()
+    library.check(lib.cuca_swiglu(_p(gate_up), _p(out), dtype_code(out.dtype), out.shape[0], out.shape[1],
+                                  _stream()), "swiglu")
+
+
+def add_to_stream(x, delta) -> None:
+    _cuda(x, delta)
+    lib = library.load()
+    library.check(lib.cuca_add_to_stream(_p(x), _p(delta), dtype_code(delta.dtype), x.numel(), _stream()),
+                  "add_to_stream")
+
+
+def gemm_simt(a, w, out, epilogue=EPI_STORE, bias=None) -> None:
+    """out = epilogue(a @ w.T) on CUDA cores; a: [M, K] (row stride >= K), w: [N or 2N, K]."""
+    _cuda(a, w, out)
+    lib = library.load()
+    M, K = a.shape
+    N = out.shape[1]
+    library.check(lib.cuca_gemm_simt(_p(a), _p(w), _p(bias), _p(out), dtype_code(a.dtype), dtype_code(out.dtype),
+                                     M, N, K, a.stride(0), out.stride(0), epilogue, _stream()), "gemm_simt")
+
+
+def attention_generic(q, q_stride, out, kpool, vpool, positions, seq_of_row, tables, n_heads, n_kv_heads,
+                      head_dim, scale, window, err) -> None:
+    _cuda(q, out, kpool, vpool)
+    lib = library.load()
+    library.check(lib.cuca_attention_generic(
+        _p(q), int(q_stride), _p(out), out.stride(0), dtype_code(out.dtype), _p(kpool), _p(vpool), kpool.shape[0],
+        kpool.shape[2], _p(positions), _p(seq_of_row), _p(tables), tables.shape[1], out.shape[0], n_heads,
+        n_kv_heads, head_dim, float(scale), int(window or 0), _p(err), _stream()), "attention_generic")
+
+
+def argmax(logits, out) -> None:
+    _cuda(logits, out)
+    lib = library.load()
+    library.check(lib.cuca_argmax(_p(logits), logits.stride(0), logits.shape[0], logits.shape[1], _p(out),
+                                  _stream()), "argmax")
+
+
+def gemm(a, w, out, epilogue=EPI_STORE, bias=None) -> None:
+    """out = epilogue(a @ w.T), on the kernel that fits dtype and shape."""
+    gemm_simt(a, w, out, epilogue, bias)
+
+
+def attention(qkv, out, cache, step, n_heads, n_kv_heads, head_dim, scale, window, err) -> None:
+    """Paged causal attention of every row of the step; q is the head of each `qkv` row."""
+    attention_generic(qkv, qkv.stride(0), out, cache.k, cache.v, step.positions, step.seq_of_row, cache.tables,
+                      n_heads, n_kv_heads, head_dim, scale, window, err)
+
+
+def scatter_int(dst, idx, val) -> None:
+    """dst.view(-1)[idx[i]] = val[i] on the device (page-table updates)."""
+    _cuda(dst, idx, val)
+    lib = library.load()
+    library.check(lib.cuca_scatter_int(_p(dst), _p(idx), _p(val), idx.shape[0], dst.numel(), _stream()), "scatter_int")

@@ -1,0 +1,103 @@
+"""Grouped-query attention over the paged cache.
+
+q = h Wq^T, k = h Wk^T, v = h Wv^T (+ biases when the tensors exist); q and k
+are rotated, k and v written to the request's pages, and each row attends to
+keys lo..P of its request with scale 1/sqrt(head_dim) applied before the mask;
+query head h reads key head h // (n_heads / n_kv_heads); then the output
+projection is added to the stream (src/provider/local/model/cpu.rs:2822-2991,
+3490-3521, model/cpu/paged_attn.rs:115-175, model/params.rs:704). The three
+projections are stacked into one weight at load (the reference accepts the
+stacked form: model/cpu.rs:3296-3301).
+
+A layer that reads another layer's pages (`shares_cache`) has only q and o.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..kernels import ops
+from .base import POSITIONS, CacheNeeds, KvNeeds, Mixer, PartSpec, TensorNeed, register_mixer
+
+
+@register_mixer("attention")
+class PagedAttention(Mixer):
+    """params: width, n_heads, n_kv_heads, head_dim, window (None: all keys), scale (None: 1/sqrt(head_dim)),
+    position (PartSpec or None), shares_cache (bool). tensors: q, k, v, o and optional q_bias, k_bias,
+    v_bias, o_bias."""
+
+    graph_safe = True
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.width = int(p["width"])
+        self.n_heads = int(p["n_heads"])
+        self.n_kv_heads = int(p["n_kv_heads"])
+        self.head_dim = int(p["head_dim"])
+        self.window = p.get("window")
+        self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.head_dim)
+        self.shares_cache = bool(p.get("shares_cache", False))
+        if self.n_heads % self.n_kv_heads:
+            raise ValueError(f"{self.n_kv_heads} key heads must divide {self.n_heads} query heads")
+        pos = p.get("position")
+        self.position = POSITIONS.get(pos.kind)(pos, runtime) if isinstance(pos, PartSpec) else None
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
+
+    # ------------------------------------------------------------ description
+    def cache_needs(self):
+        return CacheNeeds(kv=KvNeeds(self.n_kv_heads, self.head_dim, self.window))
+
+    def tensors(self):
+        t, d = self.spec.tensors, self.head_dim
+        out = {t["q"]: TensorNeed((self.n_heads * d, self.width)),
+               t["o"]: TensorNeed((self.width, self.n_heads * d))}
+        if not self.shares_cache:
+            out[t["k"]] = TensorNeed((self.n_kv_heads * d, self.width))
+            out[t["v"]] = TensorNeed((self.n_kv_heads * d, self.width))
+        for role, rows in (("q_bias", self.n_heads * d), ("k_bias", self.n_kv_heads * d),
+                           ("v_bias", self.n_kv_heads * d), ("o_bias", self.width)):
+            if role in t and not (self.shares_cache and role in ("k_bias", "v_bias")):
+                out[t[role]] = TensorNeed((rows,), optional=True)
+        return out
+
+    def load(self, get):
+        t = self.spec.tensors
+        roles = ["q"] if self.shares_cache else ["q", "k", "v"]
+        self.w_qkv = torch.cat([get(t[r]) for r in roles], dim=0).contiguous()
+        biases = [get(t[r + "_bias"]) if r + "_bias" in t else None for r in roles]
+        if any(b is not None for b in biases):
+            if any(b is None for b in biases):
+                raise ValueError("attention biases must be given for q, k and v together")
+            self.b_qkv = torch.cat(biases).contiguous()
+        self.w_o = get(t["o"])
+        self.b_o = get(t["o_bias"]) if "o_bias" in t else None
+
+    def weight_bytes(self):
+        return sum(w.numel() * w.element_size() for w in (self.w_qkv, self.w_o, self.b_qkv, self.b_o)
+                   if w is not None)
+
+    def prepare(self, context_length: int) -> None:
+        if self.position is not None:
+            self.position.prepare(context_length)
+
+    # ------------------------------------------------------------ step
+    def forward(self, h, stream, step, cache) -> None:
+        nh, d = self.n_heads, self.head_dim
+        nkv = 0 if self.shares_cache else self.n_kv_heads
+        qkv = self.rt.linear(h, self.w_qkv, bias=self.b_qkv)
+        fused = self.position.fused_tables() if self.position is not None else None
+        if fused is None:
+            if self.position is not None:
+                self.position.apply(qkv, nh, nkv, d, step.positions)
+            cos = sin = None
+            rot = 0
+        else:
+            cos, sin, rot = fused
+        ops.rope_store(qkv, step.positions, step.seq_of_row, cache.tables, cos, sin, rot,
+                       None if nkv == 0 else cache.k, None if nkv == 0 else cache.v, cache.block_size,
+                       nh, nkv, d, self.rt.err)
+        attn = self.rt.empty(h.shape[0], nh * d)
+        ops.attention(qkv, attn, cache, step, nh, self.n_kv_heads, d, self.scale, self.window, self.rt.err)
+        self.rt.linear(attn, self.w_o, out=stream, epilogue=ops.EPI_RESIDUAL, bias=self.b_o)

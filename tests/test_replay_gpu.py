@@ -1,0 +1,95 @@
+"""Trace replay on the GPU against the plain implementation: the four work splits, both tiny configurations,
+32-bit and bfloat16."""
+import pytest
+import torch
+
+import replay_util as ru
+import tiny
+
+pytestmark = pytest.mark.gpu
+
+# relative to the largest logit of a row; set from the measured error of a correct engine, with headroom
+TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+LENGTHS = {"A": [1, 7, 16, 33, 65, 100, 128], "B": [3, 12, 40, 64, 90, 130, 255], "C": [2, 31, 77, 129, 300]}
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    out = {}
+    for which in "ABC":
+        d = tmp_path_factory.mktemp(f"tiny_{which}")
+        tiny.write_tiny(d, which)
+        out[which] = d
+    return out
+
+
+def _requests(which):
+    vocab = tiny.CONFIGS[which]["vocab_size"]
+    return {f"r{n}": tiny.random_tokens(n, vocab, seed=100 + n) for n in LENGTHS[which]}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["A", "B", "C"])
+def test_whole(models, which, dtype):
+    reqs = _requests(which)
+    steps = ru.trace_whole(reqs)
+    got = ru.run_in_process(models[which], dtype, steps, ru.peak_tokens(steps))
+    ru.compare(steps, got, reqs, ru.Oracle(models[which]), TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["A", "B", "C"])
+def test_tail_one_by_one(models, which, dtype):
+    reqs = _requests(which)
+    steps = ru.trace_tail_one_by_one(reqs)
+    got = ru.run_in_process(models[which], dtype, steps, ru.peak_tokens(steps))
+    ru.compare(steps, got, reqs, ru.Oracle(models[which]), TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["A", "B", "C"])
+def test_portions(models, which, dtype):
+    reqs = _requests(which)
+    steps = ru.trace_portions(reqs)
+    got = ru.run_in_process(models[which], dtype, steps, ru.peak_tokens(steps))
+    ru.compare(steps, got, reqs, ru.Oracle(models[which]), TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["A", "B", "C"])
+def test_mixed_pages_reused(models, which, dtype):
+    reqs = _requests(which)
+    reqs.update({f"s{n}": tiny.random_tokens(n, tiny.CONFIGS[which]["vocab_size"], seed=200 + n)
+                 for n in LENGTHS[which][1:5]})
+    steps, peak = ru.trace_mixed(reqs, max_live=4, seed=7)
+    assert peak == ru.peak_tokens(steps)
+    total = sum(ru.round64(len(t)) for t in reqs.values())
+    assert peak < total, "the pool must be so small that pages are used again"
+    got = ru.run_in_process(models[which], dtype, steps, peak)
+    ru.compare(steps, got, reqs, ru.Oracle(models[which]), TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(models, dtype):
+    """bin/trace_run itself, as a subprocess."""
+    reqs = {k: v for k, v in list(_requests("A").items())[:4]}
+    steps = ru.trace_portions(reqs)
+    got = ru.run_subprocess(models["A"], dtype, steps, ru.peak_tokens(steps))
+    ru.compare(steps, got, reqs, ru.Oracle(models["A"]), TOL[dtype])
+
+
+def test_fp32_splits_agree_to_the_bit(models):
+    """In 32-bit a position's logits do not depend on how the tokens were cut: every kernel's arithmetic for a
+    row is independent of the batch, so whole, one-by-one and portioned replays agree exactly."""
+    import numpy as np
+    reqs = {"r": tiny.random_tokens(100, tiny.CONFIGS["B"]["vocab_size"], seed=5)}
+    whole = ru.trace_whole(reqs)
+    a = ru.run_in_process(models["B"], "float32", whole, 128)[0]
+    steps = ru.trace_portions(reqs)
+    got = ru.run_in_process(models["B"], "float32", steps, 128)
+    pos = 0
+    for s in steps:
+        e = s["entries"][0]
+        for j, w in enumerate(e["want"]):
+            assert np.array_equal(got[s["step"]][j], a[pos + w]), f"position {pos + w} differs between splits"
+        pos += len(e["tokens"])
