@@ -60,18 +60,17 @@ def trace_portions(requests: dict, sizes=(5, 2, 17, 3, 2, 32, 7, 2, 64, 11)) -> 
     return steps
 
 
-def trace_mixed(requests: dict, max_live: int = 4, seed: int = 0, prefill_sizes=(9, 2, 30, 5, 16)) -> tuple:
+def trace_mixed(requests: dict, max_live: int = 4, seed: int = 0, prefill_sizes=(9, 2, 30, 5, 16)) -> list:
     """Up to `max_live` live requests; portions of some beside single tokens of others; requests sit out at
-    random. Returns (steps, most tokens live at any time with each request rounded up to 64)."""
+    random."""
     rng = np.random.default_rng(seed)
     waiting = list(requests.items())
     live = {}  # rid -> [tokens, pos, decode_from]
-    steps, n, peak = [], 0, 0
+    steps, n = [], 0
     while waiting or live:
         while waiting and len(live) < max_live:
             rid, toks = waiting.pop(0)
             live[rid] = [toks, 0, max(1, len(toks) - int(rng.integers(4, 20)))]
-        peak = max(peak, sum(round64(len(v[0])) for v in live.values()))
         entries, ended = [], []
         for rid in list(live):
             toks, pos, decode_from = live[rid]
@@ -91,7 +90,7 @@ def trace_mixed(requests: dict, max_live: int = 4, seed: int = 0, prefill_sizes=
         if entries:
             steps.append({"step": n, "entries": entries, "end": ended})
             n += 1
-    return steps, peak
+    return steps
 
 
 def peak_tokens(steps: list) -> int:

@@ -61,8 +61,8 @@ def test_mixed_pages_reused(models, which, dtype):
     reqs = _requests(which)
     reqs.update({f"s{n}": tiny.random_tokens(n, tiny.CONFIGS[which]["vocab_size"], seed=200 + n)
                  for n in LENGTHS[which][1:5]})
-    steps, peak = ru.trace_mixed(reqs, max_live=4, seed=7)
-    assert peak == ru.peak_tokens(steps)
+    steps = ru.trace_mixed(reqs, max_live=4, seed=7)
+    peak = ru.peak_tokens(steps)
     total = sum(ru.round64(len(t)) for t in reqs.values())
     assert peak < total, "the pool must be so small that pages are used again"
     got = ru.run_in_process(models[which], dtype, steps, peak)
