@@ -19,6 +19,7 @@
 #define CUCA_ERR_WAIT_TIMEOUT 3
 
 void cuca_set_error(const char* fmt, ...);
+extern "C" const char* cuca_last_error();
 
 #define CUCA_CHECK_LAUNCH(name)                                                     \
   do {                                                                              \

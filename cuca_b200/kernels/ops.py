@@ -108,9 +108,46 @@ def argmax(logits, out) -> None:
                                   _stream()), "argmax")
 
 
-def gemm(a, w, out, epilogue=EPI_STORE, bias=None) -> None:
-    """out = epilogue(a @ w.T), on the kernel that fits dtype and shape."""
-    gemm_simt(a, w, out, epilogue, bias)
+_scratch: dict = {}
+WORKSPACE_BYTES = 48 << 20
+N_COUNTERS = 1024
+
+
+def gemm_scratch(device):
+    """Split-K scratch of the tensor-core contraction: 32-bit partial tiles and per-tile arrival counters
+    (zeroed once; the kernel leaves them zeroed)."""
+    key = (device.type, device.index)
+    if key not in _scratch:
+        _scratch[key] = (torch.empty(WORKSPACE_BYTES // 4, dtype=torch.float32, device=device),
+                         torch.zeros(N_COUNTERS, dtype=torch.int32, device=device))
+    return _scratch[key]
+
+
+def gemm_tc_supported(a, w) -> bool:
+    lib = library.load()
+    return bool(lib.cuca_gemm_tc_supported(_p(a), _p(w), a.shape[0], w.shape[0], a.shape[1], a.stride(0)))
+
+
+def gemm_tc(a, w, out, epilogue=EPI_STORE, bias=None, err=None, max_splits=16) -> None:
+    """out = epilogue(a @ w.T) on the tcgen05 tensor cores; bf16 operands, K and the row stride multiples of 8."""
+    _cuda(a, w, out)
+    lib = library.load()
+    M, K = a.shape
+    N = out.shape[1]
+    ws, counters = gemm_scratch(a.device)
+    library.check(lib.cuca_gemm_tc(_p(a), _p(w), _p(bias), _p(out), dtype_code(out.dtype), M, N, K, a.stride(0),
+                                   out.stride(0), epilogue, _p(ws), ws.numel() * 4, _p(counters), counters.numel(),
+                                   int(max_splits), _p(err), _stream()), "gemm_tc")
+
+
+def gemm(a, w, out, epilogue=EPI_STORE, bias=None, err=None) -> None:
+    """out = epilogue(a @ w.T), on the kernel that fits dtype and shape: tensor cores for bfloat16
+    (rows of 16-byte multiples), CUDA cores for the 32-bit path and for shapes the former refuses."""
+    if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and (bias is None or bias.dtype == torch.bfloat16) \
+            and gemm_tc_supported(a, w):
+        gemm_tc(a, w, out, epilogue, bias, err)
+    else:
+        gemm_simt(a, w, out, epilogue, bias)
 
 
 def attention(qkv, out, cache, step, n_heads, n_kv_heads, head_dim, scale, window, err) -> None:

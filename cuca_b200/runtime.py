@@ -43,7 +43,7 @@ class Runtime:
         n = w.shape[0] // 2 if epilogue == ops.EPI_SWIGLU else w.shape[0]
         if out is None:
             out = self.empty(a.shape[0], n, dtype=out_dtype or self.dtype)
-        ops.gemm(a, w, out, epilogue, bias)
+        ops.gemm(a, w, out, epilogue, bias, self.err)
         return out
 
     def check_device_errors(self) -> None:

@@ -1,0 +1,244 @@
+"""Each kernel alone against a plain 32-bit PyTorch reference of the same operation, at sizes other than the engine's."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    from cuca_b200.kernels import library
+    library.load()
+    return torch.device("cuda:0")
+
+
+def _ref_gemm(a, w, epilogue, bias, prior):
+    from cuca_b200.kernels import ops
+    y = a.float() @ w.float().T
+    if epilogue == ops.EPI_SWIGLU:
+        n = w.shape[0] // 2
+        return torch.nn.functional.silu(y[:, :n]) * y[:, n:]
+    if bias is not None:
+        y = y + bias.float()
+    if epilogue == ops.EPI_RESIDUAL:
+        y = prior + y
+    return y
+
+
+GEMM_SHAPES = [(1, 64, 64), (3, 96, 96), (8, 176, 64), (16, 128, 200), (17, 331, 120), (33, 1000, 320),
+               (64, 512, 1024), (100, 264, 4096), (130, 640, 256), (300, 384, 136), (8, 4096, 4096)]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+@pytest.mark.parametrize("epilogue", [0, 1, 2])
+def test_gemm_simt_fp32(dev, M, N, K, epilogue):
+    from cuca_b200.kernels import ops
+    if M * N * K > 4e8:
+        pytest.skip("large case is for the tensor-core kernel")
+    g = torch.Generator(device=dev).manual_seed(M * 7 + N * 3 + K)
+    a = torch.randn(M, K, device=dev, generator=g)
+    w = torch.randn((2 if epilogue == 2 else 1) * N, K, device=dev, generator=g) / math.sqrt(K)
+    bias = torch.randn(N, device=dev, generator=g) if epilogue != 2 and M % 2 else None
+    out = torch.randn(M, N, device=dev, generator=g)
+    prior = out.clone()
+    ops.gemm_simt(a, w, out, epilogue, bias)
+    ref = _ref_gemm(a.double(), w.double(), epilogue, None if bias is None else bias.double(), prior.double())
+    assert torch.allclose(out.double(), ref.double(), atol=2e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+@pytest.mark.parametrize("epilogue", [0, 1, 2])
+@pytest.mark.parametrize("max_splits", [1, 16])
+def test_gemm_tcgen05(dev, M, N, K, epilogue, max_splits):
+    """tcgen05 contraction against 32-bit math on the same bf16 inputs: store, residual add, SwiGLU; with and
+    without split-K; K tails, N tails, M from 1 to 300."""
+    from cuca_b200.kernels import ops
+    g = torch.Generator(device=dev).manual_seed(M * 7 + N * 3 + K)
+    a = torch.randn(M, K, device=dev, generator=g).bfloat16()
+    w = (torch.randn((2 if epilogue == 2 else 1) * N, K, device=dev, generator=g) / math.sqrt(K)).bfloat16()
+    bias = torch.randn(N, device=dev, generator=g).bfloat16() if epilogue != 2 and M % 2 else None
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    out_dtype = torch.float32 if epilogue == 1 or (epilogue == 0 and N % 2 == 0) else torch.bfloat16
+    out = torch.randn(M, N, device=dev, generator=g).to(out_dtype)
+    prior = out.clone()
+    assert ops.gemm_tc_supported(a, w)
+    ops.gemm_tc(a, w, out, epilogue, bias, err, max_splits=max_splits)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    ref = _ref_gemm(a, w, epilogue, bias, prior.float())
+    tol = 2e-2 if out_dtype == torch.bfloat16 else 2e-3
+    assert torch.allclose(out.float(), ref, atol=tol, rtol=tol), float((out.float() - ref).abs().max())
+    # the scratch counters are left zeroed for the next launch
+    assert int(ops.gemm_scratch(dev)[1].abs().sum().item()) == 0
+
+
+def test_gemm_tcgen05_refuses_unaligned(dev):
+    from cuca_b200.kernels import ops
+    a = torch.zeros(4, 100, device=dev, dtype=torch.bfloat16)  # K = 100 is no multiple of 8
+    w = torch.zeros(32, 100, device=dev, dtype=torch.bfloat16)
+    assert not ops.gemm_tc_supported(a, w)
+    out = torch.zeros(4, 32, device=dev, dtype=torch.bfloat16)
+    ops.gemm(a, w, out)  # falls to the CUDA-core kernel instead of computing something wrong
+
+
+def test_rmsnorm(dev):
+    from cuca_b200.kernels import ops
+    for T, E, eps in [(1, 64, 1e-5), (7, 96, 1e-6), (33, 1000, 1e-5), (5, 4096, 1e-5)]:
+        x = torch.randn(T, E, device=dev) * 3
+        w = torch.randn(E, device=dev)
+        ref = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w
+        for dt, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
+            out = torch.empty(T, E, device=dev, dtype=dt)
+            ops.rmsnorm(x, w, out, eps)
+            assert torch.allclose(out.float(), ref, atol=tol, rtol=tol)
+        rows = torch.tensor([T - 1, 0], device=dev, dtype=torch.int32)
+        out = torch.empty(2, E, device=dev)
+        ops.rmsnorm(x, w, out, eps, rows)
+        assert torch.allclose(out, ref[[T - 1, 0]], atol=1e-5, rtol=1e-5)
+
+
+def test_embed_and_bad_token(dev):
+    from cuca_b200.kernels import ops
+    table = torch.randn(50, 24, device=dev).bfloat16()
+    toks = torch.tensor([3, 49, 0, 7], device=dev, dtype=torch.int32)
+    out = torch.empty(4, 24, device=dev)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    ops.embed(table, toks, out, err)
+    assert torch.equal(out, table[toks.long()].float()) and int(err.item()) == 0
+    ops.embed(table, torch.tensor([50], device=dev, dtype=torch.int32), out[:1], err)
+    assert int(err.item()) == 1  # recorded, not faulted
+
+
+def test_swiglu_and_argmax(dev):
+    from cuca_b200.kernels import ops
+    gu = torch.randn(9, 2 * 40, device=dev)
+    out = torch.empty(9, 40, device=dev)
+    ops.swiglu(gu, out)
+    assert torch.allclose(out, torch.nn.functional.silu(gu[:, :40]) * gu[:, 40:], atol=1e-6)
+    logits = torch.randn(5, 1003, device=dev)
+    logits[2, 10] = logits[2, 900] = 50.0  # first maximum wins
+    logits[3, :] = float("-inf")
+    ids = torch.empty(5, dtype=torch.int32, device=dev)
+    ops.argmax(logits, ids)
+    want = logits.argmax(-1).tolist()
+    want[2], want[3] = 10, 0
+    assert ids.tolist() == want
+
+
+def _paged_setup(dev, dtype, lens, nh, nkv, d, bs, n_blocks, seed=0):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    S = len(lens)
+    width = max(-(-l // bs) for l in lens) + 1
+    perm = torch.randperm(n_blocks, device=dev, generator=g).tolist()  # scrambled pages
+    tables = torch.full((S, width), -1, dtype=torch.int32, device=dev)
+    k = [torch.randn(l, nkv, d, device=dev, generator=g) for l in lens]
+    v = [torch.randn(l, nkv, d, device=dev, generator=g) for l in lens]
+    kpool = torch.zeros(n_blocks, nkv, bs, d, device=dev, dtype=dtype)
+    vpool = torch.zeros_like(kpool)
+    nxt = 0
+    for s, l in enumerate(lens):
+        for b in range(-(-l // bs)):
+            page = perm[nxt]
+            nxt += 1
+            tables[s, b] = page
+            n = min(bs, l - b * bs)
+            kpool[page, :, :n] = k[s][b * bs:b * bs + n].transpose(0, 1).to(dtype)
+            vpool[page, :, :n] = v[s][b * bs:b * bs + n].transpose(0, 1).to(dtype)
+    return k, v, kpool, vpool, tables
+
+
+def _ref_attention(q, k, v, pos, scale, window):
+    # q: [nh, d]; k, v: [len, nkv, d]; keys lo..pos
+    nh, nkv = q.shape[0], k.shape[1]
+    lo = max(0, pos - (window - 1)) if window else 0
+    out = torch.empty_like(q)
+    for h in range(nh):
+        kv = h // (nh // nkv)
+        s = (k[lo:pos + 1, kv] @ q[h]) * scale
+        out[h] = torch.softmax(s, 0) @ v[lo:pos + 1, kv]
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,d,bs,window", [(4, 2, 16, 16, None), (3, 1, 32, 16, None), (6, 3, 48, 8, 20),
+                                                (8, 8, 64, 32, None), (8, 2, 128, 16, 33), (2, 1, 256, 16, None)])
+def test_attention_generic_paged(dev, dtype, nh, nkv, d, bs, window):
+    """Paged attention over scrambled page tables against contiguous 32-bit attention; lengths around page and
+    tile edges; rows of several requests in one launch; one far key made to stand out."""
+    from cuca_b200.kernels import ops
+    lens = [1, 2, 15, 16, 17, 33, 50, 129]
+    k, v, kpool, vpool, tables = _paged_setup(dev, dtype, lens, nh, nkv, d, bs, n_blocks=64)
+    g = torch.Generator(device=dev).manual_seed(1)
+    rows, ref = [], []
+    for s, l in enumerate(lens):
+        for pos in sorted({0, l // 2, l - 1}):
+            q = torch.randn(nh, d, device=dev, generator=g)
+            if pos > 3:
+                q[0] = k[s][1, 0] * 4.0  # a far key among many: its score stands out
+            rows.append((s, pos, q))
+            kk, vv = k[s].to(dtype).float(), v[s].to(dtype).float()
+            ref.append(_ref_attention(q.to(dtype).float(), kk, vv, pos, 1.0 / math.sqrt(d), window))
+    T = len(rows)
+    qbuf = torch.stack([r[2] for r in rows]).reshape(T, nh * d).to(dtype).contiguous()
+    positions = torch.tensor([r[1] for r in rows], dtype=torch.int32, device=dev)
+    seq = torch.tensor([r[0] for r in rows], dtype=torch.int32, device=dev)
+    out = torch.empty(T, nh * d, device=dev, dtype=dtype)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    ops.attention_generic(qbuf, nh * d, out, kpool, vpool, positions, seq, tables, nh, nkv, d, 1.0 / math.sqrt(d),
+                          window, err)
+    assert int(err.item()) == 0
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    got = out.float().view(T, nh, d)
+    for i in range(T):
+        assert torch.allclose(got[i], ref[i], atol=tol, rtol=tol), (rows[i][0], rows[i][1])
+    # a row alone gives the same bits as the row in the batch
+    one = torch.empty(1, nh * d, device=dev, dtype=dtype)
+    i = T - 2
+    ops.attention_generic(qbuf[i:i + 1], nh * d, one, kpool, vpool, positions[i:i + 1], seq[i:i + 1], tables, nh, nkv,
+                          d, 1.0 / math.sqrt(d), window, err)
+    assert torch.equal(one[0], out[i])
+    # a missing page is recorded, not read
+    bad = tables.clone()
+    bad[seq[i], 0] = -1
+    ops.attention_generic(qbuf[i:i + 1], nh * d, one, kpool, vpool, positions[i:i + 1], seq[i:i + 1], bad, nh, nkv, d,
+                          1.0 / math.sqrt(d), None, err)
+    assert int(err.item()) == 2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rope_store(dev, dtype):
+    """Rotation of q and k (half-split pairs, partial rotary size) and the write of k, v to their pages."""
+    from cuca_b200.kernels import ops
+    from cuca_b200.parts.rope import rope_tables
+    nh, nkv, d, rot, bs = 6, 2, 48, 32, 8
+    T, n_blocks = 11, 9
+    cos, sin = rope_tables(64, rot, 10000.0)
+    cos, sin = cos.to(dev), sin.to(dev)
+    qkv = torch.randn(T, (nh + 2 * nkv) * d, device=dev).to(dtype)
+    orig = qkv.float().clone()
+    positions = torch.tensor([0, 1, 2, 3, 4, 5, 6, 7, 8, 40, 41], dtype=torch.int32, device=dev)
+    seq = torch.tensor([0] * 9 + [1, 1], dtype=torch.int32, device=dev)
+    tables = torch.full((2, 8), -1, dtype=torch.int32, device=dev)
+    tables[0, 0], tables[0, 1], tables[1, 5] = 4, 2, 7
+    kpool = torch.zeros(n_blocks, nkv, bs, d, device=dev, dtype=dtype)
+    vpool = torch.zeros_like(kpool)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    ops.rope_store(qkv, positions, seq, tables, cos, sin, rot, kpool, vpool, bs, nh, nkv, d, err)
+    assert int(err.item()) == 0
+
+    def rotate(x, p):  # x: [heads, d]
+        c, s = cos[p], sin[p]
+        a, b = x[:, :rot // 2], x[:, rot // 2:rot]
+        return torch.cat([a * c - b * s, a * s + b * c, x[:, rot:]], dim=1)
+
+    tol = 1e-6 if dtype == torch.float32 else 2e-2
+    for r in range(T):
+        p, s = int(positions[r]), int(seq[r])
+        page, off = int(tables[s, p // bs]), p % bs
+        heads = orig[r].view(nh + 2 * nkv, d)
+        assert torch.allclose(qkv[r].float().view(-1, d)[:nh], rotate(heads[:nh], p), atol=tol)
+        assert torch.allclose(kpool[page, :, off].float(), rotate(heads[nh:nh + nkv], p), atol=tol)
+        assert torch.equal(vpool[page, :, off].float(), heads[nh + nkv:])
+    assert int((kpool.float().abs().sum(dim=(1, 2, 3)) > 0).sum()) == 3  # only the three pages named were written
