@@ -173,7 +173,8 @@ __device__ __forceinline__ void write_out(const Params& p, int n, int m, float v
     return;
   }
   if (p.bias) v += __bfloat162float(p.bias[n]);
-  if (p.epilogue == EPI_RESIDUAL) ((float*)p.out)[o] += v;
+  if (p.epilogue == EPI_RESIDUAL) atomicAdd((float*)p.out + o, v);  // result unused: a fire-and-forget reduction;
+                                                                   // one CTA owns each element, so the sum is exact
   else if (p.out_f32) ((float*)p.out)[o] = v;
   else ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v);
 }
@@ -307,15 +308,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         __threadfence();
         const float* base = p.workspace + (size_t)tile * p.splits * C::NCOLS * TILE_N;
 #pragma unroll 1
-        for (int c = 0; c < BN; ++c) {
+        for (int c = 0; c < BN; c += 8) {
           if (m0 + c >= p.M) break;
-          float v = 0.f, u = 0.f;
-          for (int s = 0; s < p.splits; ++s) {
-            const float* part = base + (size_t)s * C::NCOLS * TILE_N;
-            v += part[(size_t)c * TILE_N + threadIdx.x];
-            if (DUAL) u += part[(size_t)(BN + c) * TILE_N + threadIdx.x];
+          float v[8], u[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = u[j] = 0.f;
+          for (int s = 0; s < p.splits; ++s) {  // split order: the sum does not depend on who arrived last
+            const float* part = base + (size_t)s * C::NCOLS * TILE_N + threadIdx.x;
+            float a[8], b[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              a[j] = __ldcg(part + (size_t)(c + j) * TILE_N);
+              if (DUAL) b[j] = __ldcg(part + (size_t)(BN + c + j) * TILE_N);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              v[j] += a[j];
+              if (DUAL) u[j] += b[j];
+            }
           }
-          write_out<DUAL>(p, feature, m0 + c, v, u);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) write_out<DUAL>(p, feature, m0 + c + j, v[j], u[j]);
         }
         if (threadIdx.x == 0) p.counters[tile] = 0;  // ready for the next launch
       }
@@ -331,6 +344,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 }
 
 // ------------------------------------------------------------------ host side
+int device_sms() {
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  return sms;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -409,17 +433,6 @@ int launch_tc(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p, d
   return 0;
 }
 
-int device_sms() {
-  static int sms = 0;
-  if (!sms) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (sms <= 0) sms = 148;
-  }
-  return sms;
-}
-
 }  // namespace
 
 // 1 when the tensor-core kernel takes this problem, else 0 with the reason in cuca_last_error().
@@ -441,6 +454,8 @@ CUCA_API int cuca_gemm_tc(const void* A, const void* W, const void* bias, void* 
   CUCA_REQUIRE(epilogue != EPI_SWIGLU || (bias == nullptr && out_dtype == CUCA_BF16), "gemm_tc: SwiGLU writes bf16, no bias");
   const bool dual = epilogue == EPI_SWIGLU;
   int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  // more, narrower token tiles when the wide ones would leave SMs idle (the weight tile is re-read from L2)
+  while (bn > 64 && ((N + TILE_N - 1) / TILE_N) * ((M + bn - 1) / bn) < device_sms()) bn >>= 1;
   CUtensorMap tmW, tmX;
   CUCA_REQUIRE(tensor_map(W, (uint64_t)N * (dual ? 2 : 1), K, K, TILE_N, &tmW), "gemm_tc: weight tensor map failed");
   CUCA_REQUIRE(tensor_map(A, M, K, lda, bn, &tmX), "gemm_tc: activation tensor map failed");
@@ -448,7 +463,7 @@ CUCA_API int cuca_gemm_tc(const void* A, const void* W, const void* bias, void* 
   const int tiles = grid.x * grid.y;
   const int ksteps = (K + TILE_K - 1) / TILE_K;
   int splits = 1;
-  if (workspace && counters && max_splits > 1 && tiles < device_sms()) {
+  if (workspace && counters && max_splits > 1 && tiles < device_sms() && bn <= 64) {
     splits = device_sms() / tiles;
     if (splits > max_splits) splits = max_splits;
     if (splits > ksteps / 4) splits = ksteps / 4;  // at least four K steps per CTA

@@ -1,0 +1,221 @@
+"""The library entry in the reference's manner: `LocalModel.load(config)` then `generate(...)`
+(src/provider/local/mod.rs:2423,3213,3276). Token ids in, token ids out: chat templates and tokenizers are
+outside this engine."""
+from __future__ import annotations
+
+import json
+import time
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Iterable, Optional, Sequence
+
+import torch
+
+from ..config.engine_config import LocalModelConfig, SamplingConfig
+from ..config.model_config import read_config_json
+from ..config.registry import build_spec
+from ..kernels import ops
+from ..weights.loader import FolderSource
+from .core import EngineCore
+from .scheduler import Plan, Request, Scheduler, SchedulerConfig, Sequence_
+from .step import StepEntry
+
+
+@dataclass
+class Usage:
+    prompt_tokens: int
+    completion_tokens: int
+
+
+@dataclass
+class GenerationReport:
+    """src/provider/local/mod.rs:3155-3168: exact token counts, why it stopped, how long it queued."""
+
+    usage: Usage
+    finish_reason: str  # "stop" | "length" | "error"
+    queue_secs: float
+    error: Optional[str] = None
+    preemptions: int = 0
+
+
+@dataclass
+class LocalGeneration:
+    tokens: list
+    report: GenerationReport
+
+
+class GpuBackend:
+    """Runs the scheduler's plans on the device: one step, then one sampled token per wanted row."""
+
+    def __init__(self, core: EngineCore):
+        self.core = core
+        dev = core.rt.device
+        n = core.max_sequences
+        self.rng = torch.zeros(n, dtype=torch.int64, device=dev)
+        self.temperature = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.top_k = torch.zeros(n, dtype=torch.int32, device=dev)
+        self.top_p = torch.ones(n, dtype=torch.float32, device=dev)
+        self._scratch = None
+        self._needs_scratch = [False] * n
+        self.vocab = core.spec.vocab_size
+
+    def start(self, seq: Sequence_) -> None:
+        """A request takes its slot: clear its state, set its sampling constants and its generator."""
+        r, s = seq.request, seq.slot
+        self.core.cache.clear_slot(s)
+        state = seq.rng_state()
+        self.rng[s] = state - (1 << 64) if state >= (1 << 63) else state
+        self.temperature[s] = float(r.temperature)
+        self.top_k[s] = int(r.top_k)
+        self.top_p[s] = float(r.top_p)
+        ranked = 0 < r.top_k < self.vocab
+        self._needs_scratch[s] = r.temperature > 0 and ((ranked and r.top_k > 1024) or (not ranked and r.top_p < 1.0))
+
+    def run(self, plans: Sequence[Plan]) -> list:
+        entries = [StepEntry(p.seq.blocks, p.seq.slot, p.tokens, [len(p.tokens) - 1] if p.want_last else [])
+                   for p in plans]
+        logits = self.core.stepper.step(entries)
+        if logits is None:
+            return []
+        rows = [p.seq.slot for p in plans if p.want_last]
+        slot_of_row = torch.tensor(rows, dtype=torch.int32).to(self.core.rt.device, non_blocking=True)
+        out = torch.empty(len(rows), dtype=torch.int32, device=self.core.rt.device)
+        scratch = None
+        if any(self._needs_scratch[s] for s in rows):
+            words = ops.sample_scratch_words(self.vocab)
+            if self._scratch is None or self._scratch.shape[0] < len(rows):
+                self._scratch = torch.empty(max(len(rows), 4), words, dtype=torch.int64, device=self.core.rt.device)
+            scratch = self._scratch
+        ops.sample(logits, self.temperature, self.top_k, self.top_p, self.rng, slot_of_row, out, scratch)
+        tokens = out.tolist()  # the one synchronisation of a step
+        self.core.rt.check_device_errors()
+        return tokens
+
+
+def _file_sampling(model_dir: Optional[Path]) -> dict:
+    """generation_config.json of the checkpoint: its temperature, top_k, top_p (src/provider/local/sampling.rs:8-32)."""
+    if model_dir is None:
+        return {}
+    f = Path(model_dir) / "generation_config.json"
+    if not f.is_file():
+        return {}
+    try:
+        g = json.loads(f.read_text())
+    except ValueError:
+        return {}
+    return {k: g[k] for k in ("temperature", "top_k", "top_p") if g.get(k) is not None}
+
+
+class LocalModel:
+    """A loaded model with its scheduler. One process, one GPU, one engine."""
+
+    def __init__(self, core: EngineCore, config: LocalModelConfig, sizes: dict, model_dir: Optional[Path]):
+        self.core = core
+        self.config = config
+        self.sizes = sizes
+        self.backend = GpuBackend(core)
+        self.scheduler = Scheduler(core.pools, core.slots, self.backend, SchedulerConfig(
+            max_sequences=config.batching.max_sequences, max_step_tokens=sizes["max_step_tokens"],
+            prefill_chunk=sizes["prefill_chunk"], context_length=sizes["context_length"],
+            eos_token_ids=tuple(core.spec.eos_token_ids)))
+        self._file_sampling = _file_sampling(model_dir)
+        self.load_seconds = 0.0
+
+    # ------------------------------------------------------------ loading
+    @classmethod
+    def load(cls, config: LocalModelConfig) -> "LocalModel":
+        t0 = time.perf_counter()
+        config.validate()
+        if config.source is not None:
+            model_dir = Path(config.source)
+            cfg_json = read_config_json(model_dir)
+        else:
+            model_dir, cfg_json = None, config.model_config
+        spec = build_spec(cfg_json)
+        sizes = config.resolve(spec.max_positions)
+        kw = dict(dtype=config.dtype, device=config.device, context_length=sizes["context_length"],
+                  kv_tokens=sizes["kv_tokens"], max_sequences=config.batching.max_sequences,
+                  block_size=config.kv_block_size, max_step_tokens=sizes["max_step_tokens"])
+        if model_dir is not None:
+            core = EngineCore(spec, FolderSource(model_dir), **kw)
+        else:
+            core = EngineCore(spec, None, random_seed=config.random_weights.seed,
+                              random_std=config.random_weights.std, **kw)
+        model = cls(core, config, sizes, model_dir)
+        model.load_seconds = time.perf_counter() - t0
+        return model
+
+    # ------------------------------------------------------------ requests
+    def _request(self, prompt, max_tokens, temperature, top_k, top_p, seed, stop_token_ids) -> Request:
+        """request > config.sampling > the checkpoint's generation_config.json > 1.0 / 64 / 0.95
+        (src/provider/local/sampling.rs:1-19,93-111)."""
+        s, f = self.config.sampling, self._file_sampling
+
+        def pick(req, cfg, key, default):
+            if req is not None:
+                return req
+            if cfg is not None:
+                return cfg
+            return f.get(key, default)
+
+        return Request(
+            prompt=list(prompt), max_tokens=max_tokens,
+            temperature=float(pick(temperature, s.temperature, "temperature", SamplingConfig.DEFAULT_TEMPERATURE)),
+            top_k=int(pick(top_k, s.top_k, "top_k", SamplingConfig.DEFAULT_TOP_K)),
+            top_p=float(pick(top_p, s.top_p, "top_p", SamplingConfig.DEFAULT_TOP_P)),
+            seed=seed if seed is not None else s.seed, stop_token_ids=tuple(stop_token_ids or ()))
+
+    def generate(self, prompts, max_tokens: Optional[int] = None, temperature: Optional[float] = None,
+                 top_k: Optional[int] = None, top_p: Optional[float] = None, seed: Optional[int] = None,
+                 stop_token_ids: Iterable[int] = (), on_token=None):
+        """Generate for one prompt (a list of token ids) or several (a list of lists); returns one
+        `LocalGeneration` or a list of them, in the order given. All prompts run together under continuous
+        batching."""
+        single = len(prompts) > 0 and not isinstance(prompts[0], (list, tuple))
+        batch = [prompts] if single else list(prompts)
+        seqs = [self.scheduler.submit(self._request(p, max_tokens, temperature, top_k, top_p, seed, stop_token_ids))
+                for p in batch]
+        self.scheduler.run_until_done(on_token)
+        out = [LocalGeneration(list(s.completion), GenerationReport(
+            Usage(s.prompt_tokens, len(s.completion)), s.finish_reason or "error",
+            max(0.0, s.started_at - s.queued_at), s.error, s.preemptions)) for s in seqs]
+        for s in seqs:
+            if s in self.scheduler.finished:
+                self.scheduler.finished.remove(s)
+        return out[0] if single else out
+
+    def generate_tokens(self, prompt, **kw):
+        """Stream one request's tokens as they are sampled (src/provider/local/mod.rs:3276)."""
+        seq = self.scheduler.submit(self._request(
+            prompt, kw.get("max_tokens"), kw.get("temperature"), kw.get("top_k"), kw.get("top_p"), kw.get("seed"),
+            kw.get("stop_token_ids", ())))
+        sent = 0
+        while True:
+            while sent < len(seq.completion):
+                yield seq.completion[sent]
+                sent += 1
+            if seq.done:
+                break
+            self.scheduler.turn()
+        if seq in self.scheduler.finished:
+            self.scheduler.finished.remove(seq)
+
+    # ------------------------------------------------------------ facts
+    def serving_stats(self):
+        return self.scheduler.stats
+
+    def kv_cache_bytes(self) -> int:
+        return self.core.cache.bytes()
+
+    def context_length(self) -> int:
+        return self.sizes["context_length"]
+
+
+def generate(model, prompts, **kw):
+    """`generate(model_dir | LocalModelConfig | LocalModel, prompts, max_tokens=..., temperature=..., top_k=...,
+    top_p=..., seed=..., stop_token_ids=...)`: load if needed, then generate."""
+    if isinstance(model, (str, Path)):
+        model = LocalModel.load(LocalModelConfig(source=str(model)))
+    elif isinstance(model, LocalModelConfig):
+        model = LocalModel.load(model)
+    return model.generate(prompts, **kw)

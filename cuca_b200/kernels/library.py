@@ -35,6 +35,7 @@ _SIGNATURES = {
     "cuca_attention_generic": [_P, _I, _P, _I, _I, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "cuca_argmax": [_P, c_size_t, _I, _I, _P, _P],
     "cuca_scatter_int": [_P, _P, _P, _I, ctypes.c_longlong, _P],
+    "cuca_sample": [_P, c_size_t, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _P],
     "cuca_gemm_tc_supported": [_P, _P, _I, _I, _I, _I],
     "cuca_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, c_size_t, _P, _I, _I, _P, _P],
 }

@@ -161,3 +161,21 @@ def scatter_int(dst, idx, val) -> None:
     _cuda(dst, idx, val)
     lib = library.load()
     library.check(lib.cuca_scatter_int(_p(dst), _p(idx), _p(val), idx.shape[0], dst.numel(), _stream()), "scatter_int")
+
+
+def sample_scratch_words(vocab: int) -> int:
+    n = 1
+    while n < vocab:
+        n <<= 1
+    return n
+
+
+def sample(logits, temperature, top_k, top_p, rng_state, slot_of_row, out, scratch=None) -> None:
+    """One token per row of `logits` [R, V] (32-bit). temperature/top_p: float32 [slots]; top_k: int32 [slots];
+    rng_state: int64 [slots] SplitMix64 states, advanced for rows that draw; slot_of_row: int32 [R];
+    scratch: int64 [R, words] for rows whose cut is wider than 1024 candidates (see `sample_scratch_words`)."""
+    _cuda(logits, temperature, top_k, top_p, rng_state, slot_of_row, out)
+    lib = library.load()
+    library.check(lib.cuca_sample(_p(logits), logits.stride(0), logits.shape[0], logits.shape[1], _p(temperature),
+                                  _p(top_k), _p(top_p), _p(rng_state), _p(slot_of_row), _p(out), _p(scratch),
+                                  0 if scratch is None else scratch.shape[1], _stream()), "sample")

@@ -1,0 +1,202 @@
+"""The sampling kernel against the plain sampler (tests/plain_llama.py), and generation through the entry point."""
+import numpy as np
+import pytest
+import torch
+
+import plain_llama
+import tiny
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN, M64 = 0x9E3779B97F4A7C15, (1 << 64) - 1
+
+
+def _signed(x):
+    return x - (1 << 64) if x >= (1 << 63) else x
+
+
+def _device_sample(logits, temperature, top_k, top_p, seeds, draws=1):
+    """Each row samples `draws` tokens in a row from its own generator; returns [rows][draws]."""
+    from cuca_b200.kernels import ops
+    dev = torch.device("cuda:0")
+    R, V = logits.shape
+    lg = torch.tensor(logits, dtype=torch.float32, device=dev)
+    rng = torch.tensor([_signed(s & M64) for s in seeds], dtype=torch.int64, device=dev)
+    t = torch.tensor(temperature, dtype=torch.float32, device=dev)
+    k = torch.tensor(top_k, dtype=torch.int32, device=dev)
+    p = torch.tensor(top_p, dtype=torch.float32, device=dev)
+    slots = torch.arange(R, dtype=torch.int32, device=dev)
+    out = torch.empty(R, dtype=torch.int32, device=dev)
+    scratch = torch.empty(R, ops.sample_scratch_words(V), dtype=torch.int64, device=dev)
+    got = []
+    for _ in range(draws):
+        ops.sample(lg, t, k, p, rng, slots, out, scratch)
+        got.append(out.tolist())
+    return [list(col) for col in zip(*got)]
+
+
+def _plain(logits_row, temperature, top_k, top_p, seed, draws):
+    rng = plain_llama.SplitMix64(seed)
+    return [plain_llama.sample(logits_row, temperature, top_k, top_p, rng) for _ in range(draws)]
+
+
+def test_splitmix64_reference_vector():
+    rng = plain_llama.SplitMix64(0)  # src/provider/local/sampler.rs:371-376
+    assert rng.next_u64() == 0xE220A8397B1DCDAF and rng.next_u64() == 0x6E789E6AA1B965F4
+
+
+@pytest.mark.parametrize("V", [7, 331, 5000])
+def test_sampler_matches_plain_on_every_path(V):
+    rs = np.random.default_rng(V)
+    cases = [  # temperature, top_k, top_p
+        (0.0, 0, 1.0), (0.8, 64, 0.95), (1.0, 5, 0.95), (1.5, 1, 1.0), (1.0, 3, 1.0), (0.7, 40, 0.5),
+        (1.0, 0, 1.0), (1.3, 0, 1e-6), (1.0, 0, 0.3), (1.0, 0, 0.9), (2.0, 0, 0.97), (1.0, 2000, 0.9),
+        (0.5, 2000, 1.0),
+    ]
+    R = len(cases)
+    logits = (rs.standard_normal((R, V)) * 3).astype(np.float32)
+    logits[:, 3] = logits[:, 5]  # ties: equal logits rank by ascending id
+    logits[2, 1] = -np.inf
+    seeds = [1000 + i for i in range(R)]
+    got = _device_sample(logits, [c[0] for c in cases], [c[1] for c in cases], [c[2] for c in cases], seeds, draws=24)
+    for i, (t, k, p) in enumerate(cases):
+        want = _plain(logits[i], t, k, p, seeds[i], 24)
+        wide = (k == 0 or k >= V or k > 1024) and t > 0
+        if not wide:
+            assert got[i] == want, f"case {i} {cases[i]}: {got[i]} != {want}"
+        else:
+            # wide cuts use parallel sums: same distribution, rounding may move a boundary draw
+            same = sum(a == b for a, b in zip(got[i], want))
+            assert same >= 22, f"case {i} {cases[i]}: only {same}/24 draws agree"
+
+
+def test_sampler_statistics_follow_the_distribution():
+    V = 50
+    logits = np.linspace(-2, 2, V, dtype=np.float32)[None, :].repeat(4, 0)
+    got = _device_sample(logits, [1.0] * 4, [0, 0, 10, 10], [1.0, 0.8, 1.0, 0.8], [1, 2, 3, 4], draws=4000)
+    p = np.exp(logits[0] - logits[0].max())
+    p /= p.sum()
+    freq = np.bincount(got[0], minlength=V) / 4000.0
+    assert np.abs(freq - p).max() < 0.02
+    assert set(got[2]) <= set(range(V - 10, V))  # top_k keeps the 10 best
+    order = np.argsort(-p)
+    nucleus = set(order[: int(np.searchsorted(np.cumsum(p[order]), 0.8)) + 1].tolist())
+    assert set(got[1]) <= nucleus
+    assert len(set(got[1])) > 5
+
+
+def test_masked_ids_are_never_drawn_and_greedy_ignores_the_generator():
+    V = 40
+    logits = np.zeros((2, V), dtype=np.float32)
+    logits[:, ::2] = -np.inf
+    got = _device_sample(logits, [1.0, 0.0], [0, 0], [1.0, 1.0], [5, 5], draws=200)
+    assert all(t % 2 == 1 for t in got[0])
+    assert got[1] == [1] * 200  # first maximum
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    out = {}
+    for which in "AB":
+        d = tmp_path_factory.mktemp(f"gen_{which}")
+        tiny.write_tiny(d, which)
+        out[which] = d
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_matches_plain(folders, dtype):
+    """Tiny A's workload: prompts of 1/7/16/33 random ids (seed 1), 16 greedy tokens each, all four requests
+    together under continuous batching, against the plain implementation re-run for every token."""
+    from cuca_b200 import LocalModel, LocalModelConfig, BatchingConfig
+    cfg, weights = plain_llama.load_model_dir(folders["A"])
+    rs = np.random.default_rng(1)
+    prompts = [rs.integers(0, cfg["vocab_size"], size=n).tolist() for n in (1, 7, 16, 33)]
+    model = LocalModel.load(LocalModelConfig(source=str(folders["A"]), dtype=dtype,
+                                             batching=BatchingConfig(max_sequences=4)))
+    outs = model.generate(prompts, max_tokens=16, temperature=0.0)
+    for prompt, out in zip(prompts, outs):
+        assert out.report.finish_reason == "length" and out.report.usage.completion_tokens == 16
+        want = plain_llama.generate_greedy(cfg, weights, prompt, 16)
+        if dtype == "float32":
+            assert out.tokens == want
+        else:
+            # bfloat16 may take another branch where two logits nearly tie; until then it must agree
+            ref = plain_llama.forward(cfg, weights, prompt + out.tokens)
+            for i, tok in enumerate(out.tokens):
+                row = ref[len(prompt) - 1 + i]
+                assert float(row.max() - row[tok]) < 0.03 * float(row.abs().max()), f"token {i} is no near-maximum"
+    # alone == together
+    alone = model.generate(prompts[2], max_tokens=16, temperature=0.0)
+    if dtype == "float32":
+        assert alone.tokens == outs[2].tokens
+    st = model.serving_stats()
+    assert st.generated_tokens == 5 * 16 and st.running == 0 and st.used_blocks == 0
+
+
+def test_seeded_sampling_matches_plain_in_32_bit(folders):
+    """Tiny B's workload: 6 prompts of 3/12/40/64/90/130 ids (seed 3), portions of 32, pages of 16, 24 tokens at
+    temperature 0.8 with seed 4: the engine's tokens equal the plain sampler run on the plain logits."""
+    from cuca_b200 import LocalModel, LocalModelConfig, BatchingConfig, SamplingConfig
+    cfg, weights = plain_llama.load_model_dir(folders["B"])
+    rs = np.random.default_rng(3)
+    prompts = [rs.integers(0, cfg["vocab_size"], size=n).tolist() for n in (3, 12, 40, 64, 90, 130)]
+    model = LocalModel.load(LocalModelConfig(
+        source=str(folders["B"]), dtype="float32", kv_block_size=16, sampling=SamplingConfig(seed=4),
+        batching=BatchingConfig(max_sequences=4, max_step_tokens=64, prefill_chunk=32)))
+    outs = model.generate(prompts, max_tokens=24, temperature=0.8)
+    for prompt, out in zip(prompts, outs):
+        rng = plain_llama.SplitMix64(4)  # every request restarts the generator from the seed
+        ids = list(prompt)
+        for i in range(24):
+            logits = plain_llama.forward(cfg, weights, ids)[-1].numpy()
+            tok = plain_llama.sample(logits, 0.8, 64, 0.95, rng)
+            assert out.tokens[i] == tok, f"prompt of {len(prompt)}: token {i} differs"
+            ids.append(tok)
+    again = model.generate(prompts[1], max_tokens=24, temperature=0.8)
+    assert again.tokens == outs[1].tokens  # a fixed seed reproduces
+    other = model.generate(prompts[1], max_tokens=24, temperature=0.8, seed=5)
+    assert other.tokens != outs[1].tokens
+    k1 = model.generate(prompts[1], max_tokens=8, temperature=1.5, top_k=1)
+    greedy = model.generate(prompts[1], max_tokens=8, temperature=0.0)
+    assert k1.tokens == greedy.tokens  # top_k = 1 is greedy for any seed
+
+
+def test_generation_with_so_few_pages_that_requests_queue_and_are_preempted(folders):
+    from cuca_b200 import LocalModel, LocalModelConfig, BatchingConfig
+    cfg, weights = plain_llama.load_model_dir(folders["A"])
+    rs = np.random.default_rng(11)
+    prompts = [rs.integers(0, cfg["vocab_size"], size=n).tolist() for n in (30, 28, 12, 40)]
+    roomy = LocalModel.load(LocalModelConfig(source=str(folders["A"]), dtype="float32",
+                                             batching=BatchingConfig(max_sequences=4)))
+    want = [o.tokens for o in roomy.generate(prompts, max_tokens=40, temperature=0.0)]
+    tight = LocalModel.load(LocalModelConfig(source=str(folders["A"]), dtype="float32", context_length=96,
+                                             batching=BatchingConfig(max_sequences=4, kv_tokens=112)))  # 7 pages
+    outs = tight.generate(prompts, max_tokens=40, temperature=0.0)
+    assert [o.tokens for o in outs] == want
+    st = tight.serving_stats()
+    assert st.preemptions >= 1 and st.used_blocks == 0 and st.running == 0
+    tight.core.pools.check()
+
+
+def test_streaming_and_stop_token(folders):
+    from cuca_b200 import LocalModel, LocalModelConfig
+    model = LocalModel.load(LocalModelConfig(source=str(folders["A"]), dtype="float32"))
+    prompt = [5, 9, 200, 31]
+    whole = model.generate(prompt, max_tokens=12, temperature=0.0)
+    assert list(model.generate_tokens(prompt, max_tokens=12, temperature=0.0)) == whole.tokens
+    cut = model.generate(prompt, max_tokens=12, temperature=0.0, stop_token_ids=[whole.tokens[5]])
+    first = whole.tokens.index(whole.tokens[5])
+    assert cut.tokens == whole.tokens[:first] and cut.report.finish_reason == "stop"
+
+
+def test_command_line(folders):
+    import subprocess, sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    r = subprocess.run([sys.executable, "-m", "cuca_b200", "--model-dir", str(folders["A"]), "--prompt", "5 9 200 31",
+                        "--max-tokens", "6", "--temperature", "0", "--dtype", "float32"],
+                       capture_output=True, text=True, cwd=root, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert len(r.stdout.split()) == 6
+    assert "load:" in r.stderr and "loaded on" in r.stderr and "timing: 4 prompt tokens" in r.stderr
