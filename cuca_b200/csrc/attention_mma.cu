@@ -1,0 +1,479 @@
+// Paged causal grouped-query attention for bfloat16 on tensor cores (mma.sync m16n8k16, 32-bit
+// accumulate and softmax), in two forms that share one core:
+//
+//  * prefill: a CTA takes up to 64 consecutive rows of one request and one query head; its four
+//    warps own 16 rows each and walk the request's keys in tiles of 64 absolute positions, from the
+//    first key any row may see to the last row's own position;
+//  * decode: a CTA takes one row, one key/value head and one chunk of key positions; the 16 MMA rows
+//    are the (up to 16) query heads that share the key head, so keys and values are read once per
+//    group; the four warps split each tile's keys and merge at the end; chunks of a row are merged
+//    in chunk order by the last CTA to arrive (the result does not depend on arrival order).
+//
+// Key/value tiles come straight from the pages through the request's block table with 16-byte
+// cp.async copies, double buffered; rows of a tile are padded by 16 bytes so ldmatrix is free of
+// bank conflicts. Positions outside a row's range (causal, window) are masked after scaling.
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+
+constexpr int TILE = 64;      // keys per shared-memory tile
+constexpr int NTHREADS = 128;
+
+struct AttnParams {
+  const __nv_bfloat16* q;
+  int q_stride;
+  __nv_bfloat16* out;
+  int out_stride;
+  const __nv_bfloat16* kpool;
+  const __nv_bfloat16* vpool;
+  int n_blocks, bs;
+  const int* tables;
+  int table_stride;
+  const int* positions;
+  const int* seq_of_row;
+  const int* rows;       // decode: row numbers (null: 0..n-1)
+  const int* tile_row0;  // prefill: first row of each tile
+  const int* tile_nrows; // prefill: rows in each tile (1..64)
+  int nh, nkv;
+  float scale_log2e;
+  int window;
+  int chunk;             // decode: key positions per split (multiple of 64)
+  float* part;           // decode: [rows][nh][splits][D + 2] partial (acc, m, l)
+  int* counters;         // decode: [rows][nkv], zero before and after
+  int* err;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int D>
+struct Smem {
+  static constexpr int RS = D + 8;  // row stride in elements: 16 bytes of padding
+  static constexpr int TILE_ELEMS = TILE * RS;
+  static constexpr int BYTES = 2 /*stages*/ * 2 /*k, v*/ * TILE_ELEMS * 2;
+};
+
+// One warp's state over its 16 MMA rows: thread (g, t) holds rows g and g + 8.
+template <int D>
+struct WarpState {
+  float acc[D / 8][4];
+  float m[2], l[2];
+};
+
+template <int D, bool DECODE>
+__global__ void __launch_bounds__(NTHREADS)
+attn_mma_kernel(const AttnParams p) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  using S = Smem<D>;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int G = p.nh / p.nkv;
+
+  // ---------------------------------------------------------------- what this CTA and warp own
+  int seq, kvh, range_lo, range_hi;   // keys [range_lo, range_hi) of request `seq`
+  int row_token[2], row_head[2], row_pos[2];  // per owned MMA row (g, g + 8): token row, query head, position
+  bool row_ok[2];
+  int dec_row = 0, P = 0, warp_pmax = 0;
+  if (DECODE) {
+    dec_row = p.rows ? p.rows[blockIdx.z] : blockIdx.z;
+    seq = p.seq_of_row[dec_row];
+    if (seq < 0) return;
+    P = p.positions[dec_row];
+    kvh = blockIdx.y;
+    int lo = (p.window > 0 && P - (p.window - 1) > 0) ? P - (p.window - 1) : 0;
+    range_lo = max(lo, (int)blockIdx.x * p.chunk);
+    range_hi = min(P + 1, ((int)blockIdx.x + 1) * p.chunk);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      int item = g + 8 * h;
+      row_ok[h] = item < G;
+      row_token[h] = dec_row;
+      row_head[h] = kvh * G + item;
+      row_pos[h] = P;
+    }
+  } else {
+    const int tile = blockIdx.x;
+    const int row0 = p.tile_row0[tile], n = p.tile_nrows[tile];
+    seq = p.seq_of_row[row0];
+    if (seq < 0) return;
+    const int pos0 = p.positions[row0];
+    const int head = blockIdx.y;
+    kvh = head / G;
+    range_lo = (p.window > 0 && pos0 - (p.window - 1) > 0) ? pos0 - (p.window - 1) : 0;
+    range_hi = pos0 + n;
+    warp_pmax = pos0 + warp * 16 + 15;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      int i = warp * 16 + g + 8 * h;
+      row_ok[h] = i < n;
+      row_token[h] = row0 + i;
+      row_head[h] = head;
+      row_pos[h] = pos0 + i;
+    }
+  }
+  const int* table = p.tables + (size_t)seq * p.table_stride;
+
+  // ---------------------------------------------------------------- query fragments (A operand), from global
+  uint32_t qf[D / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint32_t lo = 0, hi = 0;
+      if (row_ok[h]) {
+        const __nv_bfloat16* qp = p.q + (size_t)row_token[h] * p.q_stride + (size_t)row_head[h] * D + ks * 16 + 2 * t;
+        lo = *reinterpret_cast<const uint32_t*>(qp);
+        hi = *reinterpret_cast<const uint32_t*>(qp + 8);
+      }
+      qf[ks][h] = lo;       // a0 (row g) / a1 (row g + 8): k = 2t, 2t + 1
+      qf[ks][2 + h] = hi;   // a2 / a3: k = 2t + 8, 2t + 9
+    }
+  }
+
+  WarpState<D> st;
+#pragma unroll
+  for (int j = 0; j < D / 8; ++j)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) st.acc[j][c] = 0.f;
+  st.m[0] = st.m[1] = -INFINITY;
+  st.l[0] = st.l[1] = 0.f;
+
+  // ---------------------------------------------------------------- tile loop
+  const int first_tile = range_lo < range_hi ? (range_lo / TILE) : 0;
+  const int n_tiles = range_lo < range_hi ? ((range_hi - 1) / TILE - first_tile + 1) : 0;
+
+  auto load_tile = [&](int stage, int tile_index) {
+    const int start = (first_tile + tile_index) * TILE;
+    __nv_bfloat16* ks = smem + (size_t)stage * 2 * S::TILE_ELEMS;
+    __nv_bfloat16* vs = ks + S::TILE_ELEMS;
+    constexpr int CH = D / 8;  // 16-byte chunks per row
+    for (int idx = threadIdx.x; idx < TILE * CH; idx += NTHREADS) {
+      int key = idx / CH, ch = idx % CH;
+      int kp = start + key;
+      bool valid = kp >= range_lo && kp < range_hi;
+      size_t off = 0;
+      if (valid) {
+        int blk = table[kp / p.bs];
+        if (blk < 0 || blk >= p.n_blocks) {
+          if (p.err) atomicExch(p.err, CUCA_ERR_BLOCK_RANGE);
+          valid = false;
+        } else {
+          off = (((size_t)blk * p.nkv + kvh) * p.bs + (kp % p.bs)) * D + ch * 8;
+        }
+      }
+      cp_async16(smem_u32(ks + key * S::RS + ch * 8), p.kpool + off, valid);
+      cp_async16(smem_u32(vs + key * S::RS + ch * 8), p.vpool + off, valid);
+    }
+  };
+
+  if (n_tiles > 0) load_tile(0, 0);
+  cp_async_commit();
+
+  for (int ti = 0; ti < n_tiles; ++ti) {
+    const int stage = ti & 1;
+    if (ti + 1 < n_tiles) load_tile(stage ^ 1, ti + 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const int start = (first_tile + ti) * TILE;
+    const __nv_bfloat16* ks = smem + (size_t)stage * 2 * S::TILE_ELEMS;
+    const __nv_bfloat16* vs = ks + S::TILE_ELEMS;
+
+    // decode: this warp owns keys [16 warp, 16 warp + 16) of the tile; prefill: all four sub-tiles
+    const int sub_begin = DECODE ? warp : 0, sub_end = DECODE ? warp + 1 : TILE / 16;
+#pragma unroll 1
+    for (int sub = sub_begin; sub < sub_end; ++sub) {
+      const int kp0 = start + sub * 16;
+      if (kp0 >= range_hi || kp0 + 16 <= range_lo) continue;
+      if (!DECODE && kp0 > warp_pmax) continue;  // every row of this warp lies before these keys (causal)
+      // ---- S = Q K^T for 16 keys: two n-tiles of 8 keys
+      float s[2][4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) s[nt][c] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        uint32_t b[4];
+        int mat = lane >> 3, r = lane & 7;
+        int key = sub * 16 + (mat >> 1) * 8 + r;
+        int dim = kk * 16 + (mat & 1) * 8;
+        ldsm_x4(b, smem_u32(ks + key * S::RS + dim));
+        mma_bf16(s[0], qf[kk], b[0], b[1]);
+        mma_bf16(s[1], qf[kk], b[2], b[3]);
+      }
+      // ---- scale, mask, online softmax (per row: g and g + 8)
+      float pmat[2][4];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        int lo_row = (p.window > 0 && row_pos[h] - (p.window - 1) > 0) ? row_pos[h] - (p.window - 1) : 0;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            int kp = kp0 + nt * 8 + 2 * t + e;
+            bool ok = row_ok[h] && kp <= row_pos[h] && kp >= lo_row && kp >= range_lo && kp < range_hi;
+            float v = ok ? s[nt][2 * h + e] * p.scale_log2e : -INFINITY;
+            s[nt][2 * h + e] = v;
+            mx = fmaxf(mx, v);
+          }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        float m_new = fmaxf(st.m[h], mx);
+        float corr = (m_new == -INFINITY) ? 1.f : exp2f(st.m[h] - m_new);
+        float sum = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            float v = s[nt][2 * h + e];
+            float pv = (v == -INFINITY) ? 0.f : exp2f(v - m_new);
+            pmat[nt][2 * h + e] = pv;
+            sum += pv;
+          }
+        st.l[h] = st.l[h] * corr + sum;
+        st.m[h] = m_new;
+#pragma unroll
+        for (int j = 0; j < D / 8; ++j) {
+          st.acc[j][2 * h] *= corr;
+          st.acc[j][2 * h + 1] *= corr;
+        }
+      }
+      // ---- O += P V: P is the A operand (16 rows x 16 keys), V tiles are read transposed
+      uint32_t pa[4];
+      pa[0] = pack_bf16(pmat[0][0], pmat[0][1]);
+      pa[1] = pack_bf16(pmat[0][2], pmat[0][3]);
+      pa[2] = pack_bf16(pmat[1][0], pmat[1][1]);
+      pa[3] = pack_bf16(pmat[1][2], pmat[1][3]);
+#pragma unroll
+      for (int j = 0; j < D / 8; j += 2) {
+        uint32_t b[4];
+        int mat = lane >> 3, r = lane & 7;
+        int key = sub * 16 + (mat & 1) * 8 + r;
+        int dim = j * 8 + (mat >> 1) * 8;
+        ldsm_x4_trans(b, smem_u32(vs + key * S::RS + dim));
+        mma_bf16(st.acc[j], pa, b[0], b[1]);
+        mma_bf16(st.acc[j + 1], pa, b[2], b[3]);
+      }
+    }
+    __syncthreads();  // the stage is overwritten by the load issued in the next iteration
+  }
+  cp_async_wait<0>();
+  // row sums live spread over the four threads of a quad
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 1);
+    st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 2);
+  }
+
+  if (!DECODE) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (!row_ok[h]) continue;
+      float inv = st.l[h] > 0.f ? 1.f / st.l[h] : 0.f;
+      __nv_bfloat16* o = p.out + (size_t)row_token[h] * p.out_stride + (size_t)row_head[h] * D;
+#pragma unroll
+      for (int j = 0; j < D / 8; ++j) {
+        uint32_t v = pack_bf16(st.acc[j][2 * h] * inv, st.acc[j][2 * h + 1] * inv);
+        *reinterpret_cast<uint32_t*>(o + j * 8 + 2 * t) = v;
+      }
+    }
+    return;
+  }
+
+  // ---------------------------------------------------------------- decode: merge the four warps, then the chunks
+  __syncthreads();
+  float* fs = reinterpret_cast<float*>(smem_raw);   // [4 warps][16 rows][D + 2]
+  constexpr int FR = D + 2;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    int rowi = g + 8 * h;
+    float* dst = fs + ((size_t)warp * 16 + rowi) * FR;
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+      dst[j * 8 + 2 * t] = st.acc[j][2 * h];
+      dst[j * 8 + 2 * t + 1] = st.acc[j][2 * h + 1];
+    }
+    if (t == 0) {
+      dst[D] = st.m[h];
+      dst[D + 1] = st.l[h];
+    }
+  }
+  __syncthreads();
+  const int n_splits = gridDim.x;
+  // scratch and counters are indexed by the ordinal of the decode row in this launch
+  float* part_row = p.part + ((size_t)blockIdx.z * p.nh + (size_t)kvh * G) * n_splits * FR;
+  for (int idx = threadIdx.x; idx < G * D; idx += NTHREADS) {
+    int item = idx / D, dim = idx % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, fs[((size_t)w * 16 + item) * FR + D]);
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float* src = fs + ((size_t)w * 16 + item) * FR;
+      float f = (src[D] == -INFINITY) ? 0.f : exp2f(src[D] - M);
+      L += src[D + 1] * f;
+      O += src[dim] * f;
+    }
+    if (n_splits == 1) {
+      p.out[(size_t)dec_row * p.out_stride + (size_t)(kvh * G + item) * D + dim] =
+          __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+    } else {
+      float* dst = part_row + ((size_t)item * n_splits + blockIdx.x) * FR;
+      dst[dim] = O;
+      if (dim == 0) { dst[D] = M; dst[D + 1] = L; }
+    }
+  }
+  if (n_splits == 1) return;
+  __threadfence();
+  __syncthreads();
+  __shared__ int last;
+  if (threadIdx.x == 0) {
+    int arrived = atomicAdd(&p.counters[blockIdx.z * p.nkv + kvh], 1);
+    last = arrived == n_splits - 1;
+  }
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < G * D; idx += NTHREADS) {
+    int item = idx / D, dim = idx % D;
+    const float* src0 = part_row + (size_t)item * n_splits * FR;
+    float M = -INFINITY;
+    for (int sidx = 0; sidx < n_splits; ++sidx) M = fmaxf(M, __ldcg(src0 + (size_t)sidx * FR + D));
+    float L = 0.f, O = 0.f;
+    for (int sidx = 0; sidx < n_splits; ++sidx) {  // chunk order: independent of which CTA came last
+      const float* src = src0 + (size_t)sidx * FR;
+      float ms = __ldcg(src + D);
+      float f = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
+      L += __ldcg(src + D + 1) * f;
+      O += __ldcg(src + dim) * f;
+    }
+    p.out[(size_t)dec_row * p.out_stride + (size_t)(kvh * G + item) * D + dim] =
+        __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+  }
+  if (threadIdx.x == 0) p.counters[blockIdx.z * p.nkv + kvh] = 0;
+}
+
+template <int D, bool DECODE>
+int launch(const AttnParams& p, dim3 grid, cudaStream_t stream) {
+  int smem = Smem<D>::BYTES;
+  if (DECODE) {
+    int need = 4 * 16 * (D + 2) * (int)sizeof(float);
+    if (need > smem) smem = need;
+  }
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_mma_kernel<D, DECODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) {
+      cuca_set_error("attention: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+      return 2;
+    }
+    configured = true;
+  }
+  attn_mma_kernel<D, DECODE><<<grid, NTHREADS, smem, stream>>>(p);
+  CUCA_CHECK_LAUNCH("attention_mma");
+  return 0;
+}
+
+template <bool DECODE>
+int dispatch(int d, const AttnParams& p, dim3 grid, cudaStream_t stream) {
+  switch (d) {
+    case 16: return launch<16, DECODE>(p, grid, stream);
+    case 32: return launch<32, DECODE>(p, grid, stream);
+    case 48: return launch<48, DECODE>(p, grid, stream);
+    case 64: return launch<64, DECODE>(p, grid, stream);
+    case 80: return launch<80, DECODE>(p, grid, stream);
+    case 96: return launch<96, DECODE>(p, grid, stream);
+    case 112: return launch<112, DECODE>(p, grid, stream);
+    case 128: return launch<128, DECODE>(p, grid, stream);
+  }
+  cuca_set_error("attention_mma: head size %d is not one of 16, 32, ..., 128", d);
+  return 1;
+}
+
+}  // namespace
+
+// 1 if the tensor-core attention kernels take this shape (bf16 only).
+CUCA_API int cuca_attention_mma_supported(int nh, int nkv, int d, int q_stride, int out_stride) {
+  if (d % 16 != 0 || d < 16 || d > 128) return 0;
+  if (nkv <= 0 || nh % nkv != 0 || nh / nkv > 16) return 0;
+  if (q_stride % 2 != 0 || out_stride % 2 != 0) return 0;
+  return 1;
+}
+
+// Floats of scratch the decode form needs for `n_rows` rows split into `n_splits` chunks.
+CUCA_API size_t cuca_attention_decode_scratch(int n_rows, int nh, int d, int n_splits) {
+  return (size_t)n_rows * nh * n_splits * (d + 2);
+}
+
+// Decode form: one query row per entry of `rows` (null: rows 0..n_rows-1), keys split in chunks of `chunk`
+// positions (a multiple of 64), `n_splits` chunks cover every row's keys (n_splits * chunk > largest position).
+CUCA_API int cuca_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* kpool,
+                                   const void* vpool, int n_blocks, int bs, const int* positions,
+                                   const int* seq_of_row, const int* tables, int table_stride, const int* rows,
+                                   int n_rows, int nh, int nkv, int d, float scale, int window, int chunk,
+                                   int n_splits, float* part, int* counters, int* err, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  CUCA_REQUIRE(cuca_attention_mma_supported(nh, nkv, d, q_stride, out_stride), "attention_decode: unsupported shape "
+               "(heads %d/%d, head size %d)", nh, nkv, d);
+  CUCA_REQUIRE(chunk > 0 && chunk % TILE == 0 && n_splits >= 1 && n_splits <= 65535, "attention_decode: bad chunking");
+  CUCA_REQUIRE(n_splits == 1 || (part && counters), "attention_decode: split keys need scratch");
+  CUCA_REQUIRE(n_rows <= 65535, "attention_decode: too many rows");
+  AttnParams p;
+  p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride; p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
+  p.kpool = (const __nv_bfloat16*)kpool; p.vpool = (const __nv_bfloat16*)vpool; p.n_blocks = n_blocks; p.bs = bs;
+  p.tables = tables; p.table_stride = table_stride; p.positions = positions; p.seq_of_row = seq_of_row;
+  p.rows = rows; p.tile_row0 = nullptr; p.tile_nrows = nullptr; p.nh = nh; p.nkv = nkv;
+  p.scale_log2e = scale * 1.4426950408889634f; p.window = window; p.chunk = chunk; p.part = part;
+  p.counters = counters; p.err = err;
+  return dispatch<true>(d, p, dim3(n_splits, nkv, n_rows), stream);
+}
+
+// Prefill form: tile i covers rows tile_row0[i] .. +tile_nrows[i]-1 (at most 64 consecutive rows of one request).
+CUCA_API int cuca_attention_prefill(const void* q, int q_stride, void* out, int out_stride, const void* kpool,
+                                    const void* vpool, int n_blocks, int bs, const int* positions,
+                                    const int* seq_of_row, const int* tables, int table_stride,
+                                    const int* tile_row0, const int* tile_nrows, int n_tiles, int nh, int nkv, int d,
+                                    float scale, int window, int* err, cudaStream_t stream) {
+  if (n_tiles == 0) return 0;
+  CUCA_REQUIRE(cuca_attention_mma_supported(nh, nkv, d, q_stride, out_stride), "attention_prefill: unsupported "
+               "shape (heads %d/%d, head size %d)", nh, nkv, d);
+  CUCA_REQUIRE(nh <= 65535, "attention_prefill: too many heads");
+  AttnParams p;
+  p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride; p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
+  p.kpool = (const __nv_bfloat16*)kpool; p.vpool = (const __nv_bfloat16*)vpool; p.n_blocks = n_blocks; p.bs = bs;
+  p.tables = tables; p.table_stride = table_stride; p.positions = positions; p.seq_of_row = seq_of_row;
+  p.rows = nullptr; p.tile_row0 = tile_row0; p.tile_nrows = tile_nrows; p.nh = nh; p.nkv = nkv;
+  p.scale_log2e = scale * 1.4426950408889634f; p.window = window; p.chunk = 0; p.part = nullptr;
+  p.counters = nullptr; p.err = err;
+  return dispatch<false>(d, p, dim3(n_tiles, nh), stream);
+}

@@ -42,6 +42,26 @@ class StepEntry:
 
 
 @dataclass
+class AttentionPlan:
+    """How the step's rows are handed to the attention kernels: single-token requests to the decode form,
+    longer portions in tiles of up to 64 rows to the prefill form."""
+
+    decode_rows: Optional[torch.Tensor]  # [n_decode] int32 row numbers; None: rows 0..n_decode-1
+    n_decode: int
+    max_len: int  # largest position + 1 among the decode rows (bounds the key chunks)
+    tile_row0: Optional[torch.Tensor]
+    tile_nrows: Optional[torch.Tensor]
+    n_tiles: int
+    fixed_chunking: Optional[tuple] = None  # (chunk, n_splits) frozen for a captured graph
+
+    def chunk(self, n_kv_heads: int):
+        if self.fixed_chunking is not None:
+            return self.fixed_chunking
+        from ..kernels.ops import decode_chunking
+        return decode_chunking(self.n_decode, n_kv_heads, self.max_len)
+
+
+@dataclass
 class StepBatch:
     """The step as the parts see it (device tensors unless said otherwise)."""
 
@@ -54,6 +74,7 @@ class StepBatch:
     logit_rows: Optional[torch.Tensor]  # [wanted] int32 row numbers
     n_logit_rows: int
     host: dict = field(default_factory=dict)  # the same lists on the host, for parts that plan there
+    attention_plan: Optional[AttentionPlan] = None
 
 
 class _Staging:
@@ -146,6 +167,23 @@ class Stepper:
             counts.append(t)
             row += t
         T, S, R = row, len(entries), len(logit_rows)
+        # attention plan: single-token requests are decode rows, longer portions are cut into tiles of 64 rows
+        decode_rows, tile_row0, tile_nrows, max_len = [], [], [], 1
+        r0 = 0
+        for start, t in zip(starts, counts):
+            if t == 1:
+                decode_rows.append(r0)
+                max_len = max(max_len, start + 1)
+            else:
+                for off in range(0, t, 64):
+                    tile_row0.append(r0 + off)
+                    tile_nrows.append(min(64, t - off))
+            r0 += t
+        # heavy tiles (late positions see most keys) first
+        order = sorted(range(len(tile_row0)), key=lambda i: -positions[tile_row0[i]])
+        tile_row0 = [tile_row0[i] for i in order]
+        tile_nrows = [tile_nrows[i] for i in order]
+        identity = len(decode_rows) == T
         # page-table entries that changed since they were last uploaded
         upd_idx, upd_val = [[] for _ in self.pools.groups], [[] for _ in self.pools.groups]
         W = self.cache.table_width
@@ -156,7 +194,9 @@ class Stepper:
                     upd_idx[gi].extend(range(e.slot * W + lo, e.slot * W + len(table)))
                     upd_val[gi].extend(table[lo:])
                     e.blocks.dirty_from[gi] = len(table)
-        parts = [tokens, positions, slot_of_row, slots, logit_rows]
+        parts = [tokens, positions, slot_of_row, slots, logit_rows, [] if identity else decode_rows, tile_row0,
+                 tile_nrows]
+        n_fixed = len(parts)
         for gi in range(len(self.pools.groups)):
             parts += [upd_idx[gi], upd_val[gi]]
         sizes = [len(p) for p in parts]
@@ -167,13 +207,16 @@ class Stepper:
             views.append(dev[off:off + n])
             off += n
         for gi in range(len(self.pools.groups)):
-            idx, val = views[5 + 2 * gi], views[6 + 2 * gi]
+            idx, val = views[n_fixed + 2 * gi], views[n_fixed + 1 + 2 * gi]
             if idx.shape[0]:
                 ops.scatter_int(self.cache.tables[gi], idx, val)
         return StepBatch(n_rows=T, n_seqs=S, tokens=views[0], positions=views[1], seq_of_row=views[2],
                          slots=views[3], logit_rows=views[4] if R else None, n_logit_rows=R,
                          host={"starts": starts, "counts": counts, "slots": slots, "tokens": tokens,
-                               "positions": positions})
+                               "positions": positions},
+                         attention_plan=AttentionPlan(None if identity else views[5], len(decode_rows), max_len,
+                                                      views[6] if tile_row0 else None,
+                                                      views[7] if tile_row0 else None, len(tile_row0)))
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run one step; returns logits [wanted, vocab] (32-bit, on the device) or None if nothing is wanted."""

@@ -150,8 +150,74 @@ def gemm(a, w, out, epilogue=EPI_STORE, bias=None, err=None) -> None:
         gemm_simt(a, w, out, epilogue, bias)
 
 
+_attn_scratch: dict = {}
+
+
+def attention_scratch(device, floats: int, counters: int):
+    """Scratch of the split-key decode attention: partial (acc, max, sum) per chunk, arrival counters
+    (zeroed once; the kernel leaves them zeroed). Grows when a step needs more."""
+    key = (device.type, device.index)
+    part, cnt = _attn_scratch.get(key, (None, None))
+    if part is None or part.numel() < floats:
+        part = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
+    if cnt is None or cnt.numel() < counters:
+        cnt = torch.zeros(max(counters, 4096), dtype=torch.int32, device=device)
+    _attn_scratch[key] = (part, cnt)
+    return part, cnt
+
+
+def attention_mma_supported(n_heads, n_kv_heads, head_dim, q_stride, out_stride) -> bool:
+    lib = library.load()
+    return bool(lib.cuca_attention_mma_supported(n_heads, n_kv_heads, head_dim, q_stride, out_stride))
+
+
+def decode_chunking(n_rows: int, n_kv_heads: int, max_len: int, sms: int = 148):
+    """Key positions per chunk (a multiple of 64) and number of chunks: the widest chunk that still gives
+    about two CTAs per SM, so a single long request is split finely and a full batch coarsely."""
+    chunk = 64
+    for c in (1024, 512, 256, 128):
+        if n_rows * n_kv_heads * -(-max_len // c) >= 2 * sms:
+            chunk = c
+            break
+    return chunk, max(1, -(-max_len // chunk))
+
+
+def attention_decode(q, q_stride, out, kpool, vpool, positions, seq_of_row, tables, rows, n_rows, n_heads,
+                     n_kv_heads, head_dim, scale, window, chunk, n_splits, err) -> None:
+    lib = library.load()
+    part, cnt = attention_scratch(out.device, n_rows * n_heads * n_splits * (head_dim + 2), n_rows * n_kv_heads)
+    library.check(lib.cuca_attention_decode(
+        _p(q), int(q_stride), _p(out), out.stride(0), _p(kpool), _p(vpool), kpool.shape[0], kpool.shape[2],
+        _p(positions), _p(seq_of_row), _p(tables), tables.shape[1], _p(rows), n_rows, n_heads, n_kv_heads, head_dim,
+        float(scale), int(window or 0), chunk, n_splits, _p(part), _p(cnt), _p(err), _stream()), "attention_decode")
+
+
+def attention_prefill(q, q_stride, out, kpool, vpool, positions, seq_of_row, tables, tile_row0, tile_nrows, n_tiles,
+                      n_heads, n_kv_heads, head_dim, scale, window, err) -> None:
+    lib = library.load()
+    library.check(lib.cuca_attention_prefill(
+        _p(q), int(q_stride), _p(out), out.stride(0), _p(kpool), _p(vpool), kpool.shape[0], kpool.shape[2],
+        _p(positions), _p(seq_of_row), _p(tables), tables.shape[1], _p(tile_row0), _p(tile_nrows), n_tiles, n_heads,
+        n_kv_heads, head_dim, float(scale), int(window or 0), _p(err), _stream()), "attention_prefill")
+
+
 def attention(qkv, out, cache, step, n_heads, n_kv_heads, head_dim, scale, window, err) -> None:
-    """Paged causal attention of every row of the step; q is the head of each `qkv` row."""
+    """Paged causal attention of every row of the step; q is the head of each `qkv` row. bfloat16 with head
+    sizes 16..128 in steps of 16 runs on tensor cores: single-token requests through the split-key decode form,
+    portions of prompts through the prefill form; everything else (the 32-bit path, other head sizes) through
+    the plain kernel."""
+    plan = getattr(step, "attention_plan", None)
+    if (out.dtype == torch.bfloat16 and plan is not None
+            and attention_mma_supported(n_heads, n_kv_heads, head_dim, qkv.stride(0), out.stride(0))):
+        if plan.n_decode:
+            attention_decode(qkv, qkv.stride(0), out, cache.k, cache.v, step.positions, step.seq_of_row,
+                             cache.tables, plan.decode_rows, plan.n_decode, n_heads, n_kv_heads, head_dim, scale,
+                             window, plan.chunk(n_kv_heads)[0], plan.chunk(n_kv_heads)[1], err)
+        if plan.n_tiles:
+            attention_prefill(qkv, qkv.stride(0), out, cache.k, cache.v, step.positions, step.seq_of_row,
+                              cache.tables, plan.tile_row0, plan.tile_nrows, plan.n_tiles, n_heads, n_kv_heads,
+                              head_dim, scale, window, err)
+        return
     attention_generic(qkv, qkv.stride(0), out, cache.k, cache.v, step.positions, step.seq_of_row, cache.tables,
                       n_heads, n_kv_heads, head_dim, scale, window, err)
 

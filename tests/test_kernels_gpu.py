@@ -242,3 +242,87 @@ def test_rope_store(dev, dtype):
         assert torch.allclose(kpool[page, :, off].float(), rotate(heads[nh:nh + nkv], p), atol=tol)
         assert torch.equal(vpool[page, :, off].float(), heads[nh + nkv:])
     assert int((kpool.float().abs().sum(dim=(1, 2, 3)) > 0).sum()) == 3  # only the three pages named were written
+
+
+MMA_SHAPES = [(4, 2, 16, 16, None), (3, 1, 32, 16, None), (6, 3, 48, 8, 20), (8, 8, 64, 32, None),
+              (8, 2, 128, 16, 33), (32, 8, 128, 16, None), (16, 1, 80, 64, 100), (2, 2, 112, 4, None)]
+
+
+@pytest.mark.parametrize("nh,nkv,d,bs,window", MMA_SHAPES)
+@pytest.mark.parametrize("chunk", [64, 256])
+def test_attention_decode_mma(dev, nh, nkv, d, bs, window, chunk):
+    """Split-key decode attention on tensor cores against contiguous 32-bit attention: scrambled pages,
+    lengths around page, tile and chunk edges, a row list with gaps, one far key that stands out."""
+    from cuca_b200.kernels import ops
+    dtype = torch.bfloat16
+    lens = [1, 2, 15, 16, 17, 63, 64, 65, 129, 300, 513]
+    k, v, kpool, vpool, tables = _paged_setup(dev, dtype, lens, nh, nkv, d, bs,
+                                              n_blocks=sum(-(-l // bs) for l in lens) + 5, seed=3)
+    g = torch.Generator(device=dev).manual_seed(2)
+    T = len(lens) + 2
+    qbuf = torch.randn(T, nh * d, device=dev, generator=g)
+    positions = torch.zeros(T, dtype=torch.int32, device=dev)
+    seq = torch.full((T,), -1, dtype=torch.int32, device=dev)
+    rows, ref = [], {}
+    for s, l in enumerate(lens):
+        r = s + 1  # row 0 and the last row are not decode rows
+        pos = l - 1
+        if pos > 3:
+            qbuf[r, :d] = k[s][1, 0] * 4.0
+        positions[r], seq[r] = pos, s
+        rows.append(r)
+        ref[r] = _ref_attention(qbuf[r].to(dtype).float().view(nh, d), k[s].to(dtype).float(), v[s].to(dtype).float(),
+                                pos, 1.0 / math.sqrt(d), window)
+    qb = qbuf.to(dtype).contiguous()
+    out = torch.zeros(T, nh * d, device=dev, dtype=dtype)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    rows_t = torch.tensor(rows, dtype=torch.int32, device=dev)
+    n_splits = -(-max(lens) // chunk)
+    for _ in range(2):  # twice: the arrival counters must be left zeroed
+        out.zero_()
+        ops.attention_decode(qb, nh * d, out, kpool, vpool, positions, seq, tables, rows_t, len(rows), nh, nkv, d,
+                             1.0 / math.sqrt(d), window, chunk, n_splits, err)
+        assert int(err.item()) == 0
+        for r in rows:
+            got = out[r].float().view(nh, d)
+            assert torch.allclose(got, ref[r], atol=2e-2, rtol=2e-2), (r, float((got - ref[r]).abs().max()))
+    assert float(out[0].abs().sum()) == 0 and float(out[-1].abs().sum()) == 0  # rows not listed stay untouched
+
+
+@pytest.mark.parametrize("nh,nkv,d,bs,window", MMA_SHAPES)
+def test_attention_prefill_mma(dev, nh, nkv, d, bs, window):
+    """Prefill attention on tensor cores: portions that start at position 0 and in the middle of a request
+    (keys partly from earlier steps), tiles of 64 rows and ragged tails, against 32-bit attention."""
+    from cuca_b200.kernels import ops
+    dtype = torch.bfloat16
+    lens = [5, 64, 70, 200, 131]
+    starts = [0, 0, 33, 90, 129]  # the portion covers positions start..len-1
+    k, v, kpool, vpool, tables = _paged_setup(dev, dtype, lens, nh, nkv, d, bs,
+                                              n_blocks=sum(-(-l // bs) for l in lens) + 3, seed=5)
+    g = torch.Generator(device=dev).manual_seed(4)
+    pos_list, seq_list, tile_row0, tile_nrows = [], [], [], []
+    for s, (l, st) in enumerate(zip(lens, starts)):
+        r0 = len(pos_list)
+        n = l - st
+        pos_list += list(range(st, l))
+        seq_list += [s] * n
+        for off in range(0, n, 64):
+            tile_row0.append(r0 + off)
+            tile_nrows.append(min(64, n - off))
+    T = len(pos_list)
+    qbuf = torch.randn(T, nh * d, device=dev, generator=g).to(dtype)
+    positions = torch.tensor(pos_list, dtype=torch.int32, device=dev)
+    seq = torch.tensor(seq_list, dtype=torch.int32, device=dev)
+    out = torch.zeros(T, nh * d, device=dev, dtype=dtype)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    ops.attention_prefill(qbuf, nh * d, out, kpool, vpool, positions, seq, tables,
+                          torch.tensor(tile_row0, dtype=torch.int32, device=dev),
+                          torch.tensor(tile_nrows, dtype=torch.int32, device=dev), len(tile_row0), nh, nkv, d,
+                          1.0 / math.sqrt(d), window, err)
+    assert int(err.item()) == 0
+    for r in range(T):
+        s, pos = seq_list[r], pos_list[r]
+        want = _ref_attention(qbuf[r].float().view(nh, d), k[s].to(dtype).float(), v[s].to(dtype).float(), pos,
+                              1.0 / math.sqrt(d), window)
+        got = out[r].float().view(nh, d)
+        assert torch.allclose(got, want, atol=2e-2, rtol=2e-2), (r, s, pos, float((got - want).abs().max()))
