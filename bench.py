@@ -1,0 +1,282 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200, on the Llama-3.1-8B shape with random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl reference]
+
+One JSON line: `value` is decoded tokens per second at batch 8 (K captured decode steps back to back on the
+device, timed with CUDA events); `e2e` is the same through the public entry point (`LocalModel.generate`, host
+token ids in and out every step); `prefill` is one 2,048-token prompt; `roofline` compares the bytes a decode
+step must read (weights once, the live requests' keys and values) with the measured copy bandwidth; `points`
+holds batch 1 and 64. A step reads 16 GB of weights, far more than the 126 MB L2, so no flush is needed between
+steps. For more than one GPU it prints one line saying so and exits with 2: this engine runs on one GPU.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LLAMA_31_8B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 32, "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8,
+    "head_dim": 128, "intermediate_size": 14336, "vocab_size": 128256, "max_position_embeddings": 131072,
+    "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "tie_word_embeddings": False,
+}
+CONTEXT = 8192
+PROMPT = 1024
+PREFILL_TOKENS = 2048
+SEED = 5
+
+
+def peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    try:
+        with open(path) as f:
+            m = json.load(f)
+        if "hbm_gbs" in m:
+            out["hbm_gbs"] = float(m["hbm_gbs"])
+        if "bf16_tflops" in m:
+            out["bf16_tflops"] = float(m["bf16_tflops"])
+        if "bf16_tflops_sustained" in m:
+            out["bf16_tflops_sustained"] = float(m["bf16_tflops_sustained"])
+        out["source"] = "measured"
+    except (OSError, ValueError):
+        pass
+    return out
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed regions run."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples, self.proc, self.thread = [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.perf_counter(), line.strip()))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, windows) -> dict:
+        mhz, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for t, line in self.samples:
+            if not any(a <= t <= b for a, b in windows):
+                continue
+            parts = [p.strip() for p in line.split(",")]
+            try:
+                mhz.append(int(parts[0]))
+                mx = max(mx, int(parts[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": int(statistics.median(mhz)) if mhz else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the model has (reported)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "nassor/cuca is a Rust crate (rust-toolchain 1.100.0): no cargo/rustc in this image and "
+                          "no network for crates.io, so it cannot be built or installed; its CUDA backend was "
+                          "never run by its authors either"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured (use --gpus 1)")
+        return 2
+    args.warmup = max(3, args.warmup)
+    if args.steps + args.warmup + 2 > 1000:
+        print("bench.py: --steps + --warmup must stay below 1000")
+        return 2
+
+    import numpy as np
+    import torch
+
+    from cuca_b200 import BatchingConfig, LocalModel, LocalModelConfig, RandomWeights
+    from cuca_b200.engine.scheduler import DECODE, Request
+    from cuca_b200.kernels import library
+
+    cfg = dict(LLAMA_31_8B)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    layers = cfg["num_hidden_layers"]
+    pk = peaks()
+    max_batch = args.batch if args.no_points else max(64, args.batch)
+    per_request = PROMPT + 2 * (args.steps + args.warmup) + 64
+    kv_tokens = max(CONTEXT + 16, max_batch * (-(-per_request // 16) * 16) + PREFILL_TOKENS + 64)
+    t0 = time.perf_counter()
+    model = LocalModel.load(LocalModelConfig(
+        model_config=cfg, random_weights=RandomWeights(seed=SEED, std=0.02), dtype="bfloat16", context_length=CONTEXT,
+        kv_block_size=16, batching=BatchingConfig(max_sequences=max_batch, kv_tokens=kv_tokens,
+                                                  max_step_tokens=max(PREFILL_TOKENS, max_batch),
+                                                  prefill_chunk=PREFILL_TOKENS)))
+    load_s = time.perf_counter() - t0
+    core, sched, backend = model.core, model.scheduler, model.backend
+    vocab = cfg["vocab_size"]
+    rng = np.random.default_rng(SEED)
+    clocks = ClockSampler()
+    clocks.start()
+    windows = []
+
+    def prompts(n, length):
+        return [rng.integers(0, vocab, size=length).tolist() for _ in range(n)]
+
+    # ------------------------------------------------------------ prefill: one 2,048-token prompt, one step
+    def prefill_once():
+        p = prompts(1, PREFILL_TOKENS)[0]
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        model.generate(p, max_tokens=1, temperature=0.0)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b)
+
+    for _ in range(3):
+        prefill_once()
+    w0 = time.perf_counter()
+    prefill_ms = statistics.median(prefill_once() for _ in range(5))
+    windows.append((w0, time.perf_counter()))
+    E, ff, nh, nkv, d = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_attention_heads"], \
+        cfg["num_key_value_heads"], cfg["head_dim"]
+    gemm_params = layers * (E * (nh + 2 * nkv) * d + nh * d * E + 3 * E * ff)
+    T = PREFILL_TOKENS
+    prefill_flops = 2.0 * T * gemm_params + layers * 4.0 * nh * d * (T * (T + 1) / 2) + 2.0 * E * vocab
+    prefill = {"value": round(T / (prefill_ms / 1e3), 1), "tokens": T, "ms": round(prefill_ms, 3),
+               "frac": round(prefill_flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+               "tflops": round(prefill_flops / (prefill_ms / 1e3) / 1e12, 1)}
+
+    # ------------------------------------------------------------ decode, device only: K captured steps
+    def decode_device(batch, steps, warmup):
+        seqs = [sched.submit(Request(p, max_tokens=2 * (steps + warmup) + 8, temperature=0.0))
+                for p in prompts(batch, PROMPT)]
+        while any(s.phase != DECODE for s in seqs):
+            sched.turn()
+        tokens = [s.pending for s in seqs]
+        hist = backend.burst(seqs, tokens, warmup)
+        tokens = hist[-1].tolist()
+        ctx0 = seqs[0].blocks.length
+        launches0 = library.launches
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        w = time.perf_counter()
+        a.record()
+        hist = backend.burst(seqs, tokens, steps)
+        b.record()
+        torch.cuda.synchronize()
+        windows.append((w, time.perf_counter()))
+        ms = a.elapsed_time(b)
+        out_tokens = hist.cpu()
+        assert out_tokens.shape == (steps, batch) and int(out_tokens.min()) >= 0
+        core.rt.check_device_errors()
+        g = backend.graphs.get(batch, seqs[0].blocks.length, False)
+        for s in list(seqs):
+            sched._release(s)
+            sched._finish(s, "length")
+        sched.finished.clear()
+        mean_ctx = ctx0 + (steps - 1) / 2.0 + 1
+        return ms / steps, mean_ctx, g
+
+    ms_step, mean_ctx, g8 = decode_device(args.batch, args.steps, args.warmup)
+    value = args.batch / (ms_step / 1e3)
+    step_bytes = model.core.model.weight_bytes() + args.batch * mean_ctx * core.cache.bytes_per_token()
+    achieved = step_bytes / (ms_step / 1e3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(step_bytes),
+                "peaks": pk["source"]}
+    launches_per_step = getattr(g8, "launches", 0)
+
+    # ------------------------------------------------------------ decode, end to end through generate()
+    stamps = []
+
+    def on_token(seq, tok):
+        if seq.id == first_id[0]:
+            stamps.append(time.perf_counter())
+
+    first_id = [sched._next_id]
+    ps = prompts(args.batch, PROMPT)
+    w = time.perf_counter()
+    model.generate(ps, max_tokens=args.warmup + args.steps + 1, temperature=0.0, on_token=on_token)
+    windows.append((w, time.perf_counter()))
+    e2e_s = stamps[args.warmup + args.steps] - stamps[args.warmup]
+    bucket = g8.bucket
+    e2e = {"value": round(args.batch * args.steps / e2e_s, 1), "unit": "tokens/s",
+           "h2d_bytes_per_step": 3 * bucket * 4, "d2h_bytes_per_step": bucket * 4,
+           "ms_per_step": round(e2e_s / args.steps * 1e3, 4)}
+
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            ms_b, _, _ = decode_device(b, min(args.steps, 64), args.warmup)
+            points[f"decode_b{b}"] = round(b / (ms_b / 1e3), 1)
+    clocks.stop()
+
+    line = {
+        "metric": "decode tokens/s, Llama-3.1-8B shape, bf16, batch %d, 1024-token prompts" % args.batch,
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random token ids, random weights N(0, 0.02) seed 5",
+        "config": {
+            "model": "Llama-3.1-8B shape", "layers": layers, "layers_of_model": full_layers,
+            "hidden_size": E, "heads": nh, "kv_heads": nkv, "head_dim": d, "intermediate_size": ff,
+            "vocab_size": vocab, "rms_norm_eps": cfg["rms_norm_eps"],
+            "rope": "theta 5e5, llama3 factor 8 low 1 high 4 original 8192",
+            "global_batch": args.batch, "seq_len": CONTEXT, "prompt_tokens": PROMPT, "kv_block_size": 16,
+            "decode_context": round(mean_ctx, 1), "prefill_tokens": PREFILL_TOKENS,
+            "l2": "no flush: a step reads %.1f GB, far above the 126 MB L2" % (step_bytes / 1e9),
+            "parallelism": "1 GPU",
+        },
+        "e2e": e2e, "gpu_launches": int(launches_per_step * args.steps), "launches_per_step": launches_per_step,
+        "clocks": clocks.summary(windows), "prefill": prefill, "roofline": roofline, "points": points,
+        "load_seconds": round(load_s, 1), "impl": "ours",
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -290,6 +290,10 @@ sample_kernel(const float* __restrict__ logits, size_t row_stride, int V, const 
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * row_stride;
   const int slot = slot_of_row[r];
+  if (slot < 0) {  // a padding row of a fixed-size batch
+    if (threadIdx.x == 0) out[r] = -1;
+    return;
+  }
   const float temp = temperature[slot];
   if (!(temp > 0.f) || V <= 1) {
     int id = block_argmax(row, V, sh);
@@ -456,5 +460,35 @@ CUCA_API int cuca_sample(const float* logits, size_t row_stride, int n_rows, int
   sample_kernel<<<n_rows, NT, 0, stream>>>(logits, row_stride, V, temperature, top_k, top_p, rng, slot_of_row, out,
                                            scratch, scratch_stride);
   CUCA_CHECK_LAUNCH("sample");
+  return 0;
+}
+
+namespace {
+__global__ void decode_advance_kernel(int* __restrict__ tokens, int* __restrict__ positions,
+                                      const int* __restrict__ slot_of_row, const int* __restrict__ sampled,
+                                      int* __restrict__ history, int* __restrict__ counter, int n, int max_steps) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  int step = *counter;
+  if (i < n) {
+    if (slot_of_row[i] >= 0) {
+      tokens[i] = sampled[i];
+      positions[i] += 1;
+    }
+    if (history && step < max_steps) history[(size_t)step * n + i] = sampled[i];
+  }
+  __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x == 0) *counter = step + 1;
+}
+}  // namespace
+
+// After a decode step: every live row's sampled token becomes its next input and its position moves on, so the
+// same captured step can run again without the host; sampled tokens are also appended to history[step][row].
+// One block only (n <= 1024), so the counter update is ordered after every read of it.
+CUCA_API int cuca_decode_advance(int* tokens, int* positions, const int* slot_of_row, const int* sampled,
+                                 int* history, int* counter, int n, int max_steps, cudaStream_t stream) {
+  if (n == 0) return 0;
+  CUCA_REQUIRE(n <= 1024, "decode_advance: at most 1024 rows");
+  decode_advance_kernel<<<1, 1024, 0, stream>>>(tokens, positions, slot_of_row, sampled, history, counter, n, max_steps);
+  CUCA_CHECK_LAUNCH("decode_advance");
   return 0;
 }

@@ -9,6 +9,7 @@ from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Iterable, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..config.engine_config import LocalModelConfig, SamplingConfig
@@ -17,6 +18,7 @@ from ..config.registry import build_spec
 from ..kernels import ops
 from ..weights.loader import FolderSource
 from .core import EngineCore
+from .graphs import MAX_HISTORY, DecodeGraphs
 from .scheduler import Plan, Request, Scheduler, SchedulerConfig, Sequence_
 from .step import StepEntry
 
@@ -58,6 +60,10 @@ class GpuBackend:
         self._scratch = None
         self._needs_scratch = [False] * n
         self.vocab = core.spec.vocab_size
+        self.use_graphs = core.model.graph_safe()
+        self.graphs = DecodeGraphs(core, self)
+        self.graph_steps = 0
+        self.eager_steps = 0
 
     def start(self, seq: Sequence_) -> None:
         """A request takes its slot: clear its state, set its sampling constants and its generator."""
@@ -71,7 +77,64 @@ class GpuBackend:
         ranked = 0 < r.top_k < self.vocab
         self._needs_scratch[s] = r.temperature > 0 and ((ranked and r.top_k > 1024) or (not ranked and r.top_p < 1.0))
 
+    # ------------------------------------------------------------ decode through a captured graph
+    def _table_updates(self, seqs) -> None:
+        """Upload page-table entries that changed (new pages) for these requests."""
+        core = self.core
+        W = core.cache.table_width
+        for gi in range(len(core.pools.groups)):
+            idx, val = [], []
+            for s in seqs:
+                table, lo = s.blocks.tables[gi], s.blocks.dirty_from[gi]
+                if lo < len(table):
+                    idx.extend(range(s.slot * W + lo, s.slot * W + len(table)))
+                    val.extend(table[lo:])
+                    s.blocks.dirty_from[gi] = len(table)
+            if idx:
+                dev = core.stepper._staging.upload(np.asarray(idx + val, dtype=np.int32))
+                ops.scatter_int(core.cache.tables[gi], dev[:len(idx)], dev[len(idx):])
+
+    def _run_decode_graph(self, plans: Sequence[Plan]) -> list:
+        seqs = [p.seq for p in plans]
+        n = len(seqs)
+        max_len = max(s.blocks.length for s in seqs) + 1
+        g = self.graphs.get(n, max_len, any(self._needs_scratch[s.slot] for s in seqs))
+        self._table_updates(seqs)
+        g.load_rows([p.tokens[0] for p in plans], [s.blocks.length for s in seqs], [s.slot for s in seqs])
+        g.replay()
+        tokens = g.sampled[:n].tolist()  # the one synchronisation of a step
+        for s in seqs:
+            s.blocks.length += 1
+            self.core.pools.release_window(s.blocks)
+        self.core.stepper.steps += 1
+        self.graph_steps += 1
+        return tokens
+
+    def burst(self, seqs, tokens, n_steps: int):
+        """`n_steps` decode steps back to back on the device, each feeding its sampled tokens to the next; the
+        host only reserves pages ahead and reads the tokens at the end. Returns a [n_steps, requests] tensor."""
+        core = self.core
+        n = len(seqs)
+        if n_steps > MAX_HISTORY:
+            raise ValueError(f"a burst holds at most {MAX_HISTORY} steps")
+        for s in seqs:
+            core.pools.reserve(s.blocks, s.blocks.length + n_steps)
+        max_len = max(s.blocks.length for s in seqs) + n_steps
+        g = self.graphs.get(n, max_len, any(self._needs_scratch[s.slot] for s in seqs))
+        self._table_updates(seqs)
+        g.load_rows(tokens, [s.blocks.length for s in seqs], [s.slot for s in seqs])
+        g.counter.zero_()
+        for _ in range(n_steps):
+            g.replay()
+        for s in seqs:
+            s.blocks.length += n_steps
+        self.graph_steps += n_steps
+        return g.history[:n_steps, :n]
+
     def run(self, plans: Sequence[Plan]) -> list:
+        if self.use_graphs and all(len(p.tokens) == 1 and p.want_last for p in plans):
+            return self._run_decode_graph(plans)
+        self.eager_steps += 1
         entries = [StepEntry(p.seq.blocks, p.seq.slot, p.tokens, [len(p.tokens) - 1] if p.want_last else [])
                    for p in plans]
         logits = self.core.stepper.step(entries)

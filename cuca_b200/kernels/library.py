@@ -41,6 +41,7 @@ _SIGNATURES = {
                               _P, _P, _P, _P],
     "cuca_attention_prefill": [_P, _I, _P, _I, _P, _P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _P,
                                _P],
+    "cuca_decode_advance": [_P, _P, _P, _P, _P, _P, _I, _I, _P],
     "cuca_gemm_tc_supported": [_P, _P, _I, _I, _I, _I],
     "cuca_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, c_size_t, _P, _I, _I, _P, _P],
 }
@@ -87,7 +88,12 @@ def declare(name: str, argtypes: list) -> None:
         fn.argtypes = argtypes
 
 
+launches = 0  # kernels launched through this library by this process (bench.py reports it)
+
+
 def check(code: int, what: str) -> None:
+    global launches
+    launches += 1
     if code != 0:
         msg = _lib.cuca_last_error().decode(errors="replace") if _lib is not None else ""
         raise KernelError(f"{what}: {msg or 'error ' + str(code)}")

@@ -245,3 +245,10 @@ def sample(logits, temperature, top_k, top_p, rng_state, slot_of_row, out, scrat
     library.check(lib.cuca_sample(_p(logits), logits.stride(0), logits.shape[0], logits.shape[1], _p(temperature),
                                   _p(top_k), _p(top_p), _p(rng_state), _p(slot_of_row), _p(out), _p(scratch),
                                   0 if scratch is None else scratch.shape[1], _stream()), "sample")
+
+
+def decode_advance(tokens, positions, slot_of_row, sampled, history, counter, max_steps) -> None:
+    """tokens <- sampled, positions += 1 for live rows; history[counter] <- sampled; counter += 1."""
+    lib = library.load()
+    library.check(lib.cuca_decode_advance(_p(tokens), _p(positions), _p(slot_of_row), _p(sampled), _p(history),
+                                          _p(counter), tokens.shape[0], int(max_steps), _stream()), "decode_advance")

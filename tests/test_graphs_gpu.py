@@ -1,0 +1,68 @@
+"""Decode through captured CUDA graphs: same tokens as the eager step, page tables kept in step, bursts."""
+import numpy as np
+import pytest
+import torch
+
+import plain_llama
+import tiny
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folder(tmp_path_factory):
+    d = tmp_path_factory.mktemp("graph_B")
+    tiny.write_tiny(d, "B")
+    return d
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_graph_decode_equals_eager_decode(folder, dtype):
+    from cuca_b200 import BatchingConfig, LocalModel, LocalModelConfig
+    rs = np.random.default_rng(21)
+    prompts = [rs.integers(0, 512, size=n).tolist() for n in (3, 20, 47)]
+    cfg = LocalModelConfig(source=str(folder), dtype=dtype, batching=BatchingConfig(max_sequences=4))
+    with_graphs = LocalModel.load(cfg)
+    assert with_graphs.backend.use_graphs
+    a = with_graphs.generate(prompts, max_tokens=40, temperature=0.0)
+    assert with_graphs.backend.graph_steps >= 39
+    eager = LocalModel.load(cfg)
+    eager.backend.use_graphs = False
+    b = eager.generate(prompts, max_tokens=40, temperature=0.0)
+    assert eager.backend.graph_steps == 0
+    if dtype == "float32":
+        assert [o.tokens for o in a] == [o.tokens for o in b]
+        cfgj, weights = plain_llama.load_model_dir(folder)
+        assert a[1].tokens == plain_llama.generate_greedy(cfgj, weights, prompts[1], 40)
+    else:
+        agree = sum(x == y for o, p in zip(a, b) for x, y in zip(o.tokens, p.tokens))
+        assert agree >= 100  # bf16: the split of keys over chunks differs between the two paths
+
+
+def test_sampled_decode_through_graphs_keeps_each_requests_generator(folder):
+    from cuca_b200 import BatchingConfig, LocalModel, LocalModelConfig
+    rs = np.random.default_rng(22)
+    prompts = [rs.integers(0, 512, size=n).tolist() for n in (5, 9)]
+    cfg = LocalModelConfig(source=str(folder), dtype="float32", batching=BatchingConfig(max_sequences=4))
+    m = LocalModel.load(cfg)
+    together = m.generate(prompts, max_tokens=20, temperature=0.9, seed=77)
+    alone = [m.generate(p, max_tokens=20, temperature=0.9, seed=77) for p in prompts]
+    assert [o.tokens for o in together] == [o.tokens for o in alone]
+
+
+def test_burst_feeds_tokens_back_on_the_device(folder):
+    from cuca_b200 import BatchingConfig, LocalModel, LocalModelConfig
+    from cuca_b200.engine.scheduler import DECODE, Request
+    rs = np.random.default_rng(23)
+    prompts = [rs.integers(0, 512, size=n).tolist() for n in (17, 30, 4)]
+    m = LocalModel.load(LocalModelConfig(source=str(folder), dtype="float32",
+                                         batching=BatchingConfig(max_sequences=4)))
+    want = [o.tokens for o in m.generate(prompts, max_tokens=25, temperature=0.0)]
+    seqs = [m.scheduler.submit(Request(p, max_tokens=100, temperature=0.0)) for p in prompts]
+    while any(s.phase != DECODE for s in seqs):
+        m.scheduler.turn()
+    first = [s.pending for s in seqs]
+    hist = m.backend.burst(seqs, first, 24).cpu().tolist()
+    got = [[first[i]] + [row[i] for row in hist] for i in range(3)]
+    assert got == want
+    m.core.pools.check()
