@@ -477,3 +477,74 @@ CUCA_API int cuca_attention_prefill(const void* q, int q_stride, void* out, int 
   p.counters = nullptr; p.err = err;
   return dispatch<false>(d, p, dim3(n_tiles, nh), stream);
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// The allocation-free variant (see no_alloc.h): the same decode kernel, its scratch in the library's image.
+// ---------------------------------------------------------------------------------------------------------
+#include "no_alloc.h"
+#include <mutex>
+
+// Counters first (they are the part that must start at zero), partials behind them. In host code this name is
+// only a handle for cudaGetSymbolAddress; it is not a device address and must never be handed to a kernel.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[CUCA_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int NOALLOC_MAX_DEVICES = 64;
+void* g_noalloc_addr[NOALLOC_MAX_DEVICES];
+bool g_noalloc_ready[NOALLOC_MAX_DEVICES];
+std::mutex g_noalloc_mu;
+
+// Device address of the scratch array on the current device; looked up once per device.
+int noalloc_scratch(void** addr) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) {
+    cuca_set_error("attention_decode_noalloc: no usable current device (%s)", cudaGetErrorString(e));
+    return 2;
+  }
+  std::lock_guard<std::mutex> lock(g_noalloc_mu);
+  if (!g_noalloc_ready[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      cuca_set_error("attention_decode_noalloc: cudaGetSymbolAddress failed on device %d: %s", dev,
+                     cudaGetErrorString(e));
+      return 2;
+    }
+    g_noalloc_addr[dev] = p;
+    g_noalloc_ready[dev] = true;
+  }
+  *addr = g_noalloc_addr[dev];
+  return 0;
+}
+}  // namespace
+
+CUCA_API int cuca_attention_decode_noalloc(const void* q, int q_stride, void* out, int out_stride, const void* kpool,
+                                           const void* vpool, int n_blocks, int bs, const int* positions,
+                                           const int* seq_of_row, const int* tables, int table_stride,
+                                           const int* rows, int n_rows, int nh, int nkv, int d, float scale,
+                                           int window, int chunk, int n_splits, int* err, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  CUCA_REQUIRE(n_rows > 0 && nh > 0 && nkv > 0 && d > 0 && n_splits >= 1, "attention_decode_noalloc: bad sizes");
+  const size_t part_floats = cuca_attention_decode_scratch(n_rows, nh, d, n_splits);
+  const size_t counters = (size_t)n_rows * nkv;
+  CUCA_REQUIRE(part_floats <= CUCA_NOALLOC_PART_FLOATS && counters <= CUCA_NOALLOC_COUNTERS,
+               "attention_decode_noalloc: %d rows x %d heads x %d chunks x head size %d needs %zu scratch floats and "
+               "%zu counters; the built-in scratch holds %u floats and %u counters. Use fewer chunks or rows, or "
+               "cuca_attention_decode with a buffer of your own",
+               n_rows, nh, n_splits, d, part_floats, counters, CUCA_NOALLOC_PART_FLOATS, CUCA_NOALLOC_COUNTERS);
+  void* base = nullptr;
+  int rc = noalloc_scratch(&base);
+  if (rc) return rc;
+  int* cnt = reinterpret_cast<int*>(base);
+  float* part = reinterpret_cast<float*>(static_cast<unsigned char*>(base) + CUCA_NOALLOC_COUNTERS * 4u);
+  // the array keeps the last call's contents: the counters this call uses must start at zero
+  cudaError_t e = cudaMemsetAsync(cnt, 0, counters * sizeof(int), stream);
+  if (e != cudaSuccess) {
+    cuca_set_error("attention_decode_noalloc: clearing the counters failed: %s", cudaGetErrorString(e));
+    return 2;
+  }
+  return cuca_attention_decode(q, q_stride, out, out_stride, kpool, vpool, n_blocks, bs, positions, seq_of_row,
+                               tables, table_stride, rows, n_rows, nh, nkv, d, scale, window, chunk, n_splits, part,
+                               cnt, err, stream);
+}
