@@ -179,7 +179,9 @@ def main() -> int:
     for _ in range(3):
         prefill_once()
     w0 = time.perf_counter()
+    torch.cuda.nvtx.range_push("prefill_timed")
     prefill_ms = statistics.median(prefill_once() for _ in range(5))
+    torch.cuda.nvtx.range_pop()
     windows.append((w0, time.perf_counter()))
     E, ff, nh, nkv, d = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_attention_heads"], \
         cfg["num_key_value_heads"], cfg["head_dim"]
@@ -204,10 +206,12 @@ def main() -> int:
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         w = time.perf_counter()
+        torch.cuda.nvtx.range_push("decode_timed_b%d" % batch)
         a.record()
         hist = backend.burst(seqs, tokens, steps)
         b.record()
         torch.cuda.synchronize()
+        torch.cuda.nvtx.range_pop()
         windows.append((w, time.perf_counter()))
         ms = a.elapsed_time(b)
         out_tokens = hist.cpu()
