@@ -17,6 +17,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                          const int* __restrict__ tables, int table_stride, int nh, int nkv, int d,
                          float scale, int window, int* err) {
   extern __shared__ float qs[];  // [4][d]
+  pdl_trigger();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.y;
   const int head = blockIdx.x * 4 + warp;
@@ -104,13 +106,14 @@ CUCA_API int cuca_attention_generic(const void* q, int q_stride, void* out, int 
   dim3 grid((nh + 3) / 4, n_rows);
   size_t smem = (size_t)4 * d * sizeof(float);
   if (dtype == CUCA_F32)
-    attention_generic_kernel<float><<<grid, 128, smem, stream>>>((const float*)q, q_stride, (float*)out, out_stride,
-        (const float*)kpool, (const float*)vpool, n_blocks, bs, positions, seq_of_row, tables, table_stride, nh, nkv,
-        d, scale, window, err);
+    cuca_launch(attention_generic_kernel<float>, grid, dim3(128), smem, stream, true, (const float*)q, q_stride,
+                (float*)out, out_stride, (const float*)kpool, (const float*)vpool, n_blocks, bs, positions,
+                seq_of_row, tables, table_stride, nh, nkv, d, scale, window, err);
   else if (dtype == CUCA_BF16)
-    attention_generic_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>((const __nv_bfloat16*)q, q_stride,
-        (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, n_blocks, bs,
-        positions, seq_of_row, tables, table_stride, nh, nkv, d, scale, window, err);
+    cuca_launch(attention_generic_kernel<__nv_bfloat16>, grid, dim3(128), smem, stream, true,
+                (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)kpool,
+                (const __nv_bfloat16*)vpool, n_blocks, bs, positions, seq_of_row, tables, table_stride, nh, nkv, d,
+                scale, window, err);
   else
     CUCA_REQUIRE(false, "attention: unknown dtype %d", dtype);
   CUCA_CHECK_LAUNCH("attention_generic");

@@ -38,7 +38,7 @@ struct AttnParams {
   int nh, nkv;
   float scale_log2e;
   int window;
-  int chunk;             // decode: key positions per split (multiple of 64)
+  int chunk;             // decode: key positions per split (multiple of 64); 0: each row divides its own length
   float* part;           // decode: [rows][nh][splits][D + 2] partial (acc, m, l)
   int* counters;         // decode: [rows][nkv], zero before and after
   int* err;
@@ -95,6 +95,8 @@ attn_mma_kernel(const AttnParams p) {
   using S = Smem<D>;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int G = p.nh / p.nkv;
+  pdl_trigger();
+  pdl_wait();
 
   // ---------------------------------------------------------------- what this CTA and warp own
   int seq, kvh, range_lo, range_hi;   // keys [range_lo, range_hi) of request `seq`
@@ -108,8 +110,14 @@ attn_mma_kernel(const AttnParams p) {
     P = p.positions[dec_row];
     kvh = blockIdx.y;
     int lo = (p.window > 0 && P - (p.window - 1) > 0) ? P - (p.window - 1) : 0;
-    range_lo = max(lo, (int)blockIdx.x * p.chunk);
-    range_hi = min(P + 1, ((int)blockIdx.x + 1) * p.chunk);
+    // chunk 0: every row spreads its own keys evenly (in tiles of 64) over the gridDim.x chunks
+    int chunk = p.chunk;
+    if (chunk == 0) {
+      int tiles = (P + TILE) / TILE;
+      chunk = ((tiles + (int)gridDim.x - 1) / (int)gridDim.x) * TILE;
+    }
+    range_lo = max(lo, (int)blockIdx.x * chunk);
+    range_hi = min(P + 1, ((int)blockIdx.x + 1) * chunk);
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       int item = g + 8 * h;
@@ -169,29 +177,40 @@ attn_mma_kernel(const AttnParams p) {
   const int first_tile = range_lo < range_hi ? (range_lo / TILE) : 0;
   const int n_tiles = range_lo < range_hi ? ((range_hi - 1) / TILE - first_tile + 1) : 0;
 
+  // Row offsets of a tile's 64 keys in the pools (-1: masked or without a page), one tile ahead of the copies:
+  // the page-table lookups of tile i + 2 are in flight while tile i is computed, so no copy waits on one.
+  __shared__ long long s_rowoff[2][TILE];
+  const int bs_shift = __ffs(p.bs) - 1, bs_mask = p.bs - 1;
+  auto row_offset = [&](int tile_index) -> long long {
+    int kp = (first_tile + tile_index) * TILE + (int)threadIdx.x;
+    if (kp < range_lo || kp >= range_hi) return -1;
+    int blk = table[kp >> bs_shift];
+    if (blk < 0 || blk >= p.n_blocks) {
+      if (p.err) atomicExch(p.err, CUCA_ERR_BLOCK_RANGE);
+      return -1;
+    }
+    return ((((long long)blk * p.nkv + kvh) << bs_shift) + (kp & bs_mask)) * D;
+  };
   auto load_tile = [&](int stage, int tile_index) {
-    const int start = (first_tile + tile_index) * TILE;
     __nv_bfloat16* ks = smem + (size_t)stage * 2 * S::TILE_ELEMS;
     __nv_bfloat16* vs = ks + S::TILE_ELEMS;
+    const long long* ro = s_rowoff[tile_index & 1];
     constexpr int CH = D / 8;  // 16-byte chunks per row
+#pragma unroll
     for (int idx = threadIdx.x; idx < TILE * CH; idx += NTHREADS) {
       int key = idx / CH, ch = idx % CH;
-      int kp = start + key;
-      bool valid = kp >= range_lo && kp < range_hi;
-      size_t off = 0;
-      if (valid) {
-        int blk = table[kp / p.bs];
-        if (blk < 0 || blk >= p.n_blocks) {
-          if (p.err) atomicExch(p.err, CUCA_ERR_BLOCK_RANGE);
-          valid = false;
-        } else {
-          off = (((size_t)blk * p.nkv + kvh) * p.bs + (kp % p.bs)) * D + ch * 8;
-        }
-      }
-      cp_async16(smem_u32(ks + key * S::RS + ch * 8), p.kpool + off, valid);
-      cp_async16(smem_u32(vs + key * S::RS + ch * 8), p.vpool + off, valid);
+      long long off = ro[key];
+      bool valid = off >= 0;
+      size_t o = valid ? (size_t)off + ch * 8 : 0;
+      cp_async16(smem_u32(ks + key * S::RS + ch * 8), p.kpool + o, valid);
+      cp_async16(smem_u32(vs + key * S::RS + ch * 8), p.vpool + o, valid);
     }
   };
+  if (threadIdx.x < TILE) {
+    if (n_tiles > 0) s_rowoff[0][threadIdx.x] = row_offset(0);
+    if (n_tiles > 1) s_rowoff[1][threadIdx.x] = row_offset(1);
+  }
+  __syncthreads();
 
   if (n_tiles > 0) load_tile(0, 0);
   cp_async_commit();
@@ -202,6 +221,9 @@ attn_mma_kernel(const AttnParams p) {
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
+    long long next_off = -1;
+    const bool look_ahead = threadIdx.x < TILE && ti + 2 < n_tiles;
+    if (look_ahead) next_off = row_offset(ti + 2);
     const int start = (first_tile + ti) * TILE;
     const __nv_bfloat16* ks = smem + (size_t)stage * 2 * S::TILE_ELEMS;
     const __nv_bfloat16* vs = ks + S::TILE_ELEMS;
@@ -284,6 +306,7 @@ attn_mma_kernel(const AttnParams p) {
         mma_bf16(st.acc[j + 1], pa, b[2], b[3]);
       }
     }
+    if (look_ahead) s_rowoff[ti & 1][threadIdx.x] = next_off;  // read last for tile ti, one iteration ago
     __syncthreads();  // the stage is overwritten by the load issued in the next iteration
   }
   cp_async_wait<0>();
@@ -364,21 +387,45 @@ attn_mma_kernel(const AttnParams p) {
   __syncthreads();
   if (!last) return;
   __threadfence();
+  // Merge the chunks in chunk order. All loads of a phase are independent and issued together, so the merge
+  // costs a few memory round trips, not one per chunk.
+  constexpr int MAXS = 32;
+  __shared__ float s_m[16][MAXS], s_f[16][MAXS], s_inv[16];
+  for (int qd = threadIdx.x; qd < G * MAXS; qd += NTHREADS) {
+    int item = qd / MAXS, sidx = qd % MAXS;
+    float ms = -INFINITY, ls = 0.f;
+    if (sidx < n_splits) {
+      const float* src = part_row + ((size_t)item * n_splits + sidx) * FR;
+      ms = __ldcg(src + D);
+      ls = __ldcg(src + D + 1);
+    }
+    s_m[item][sidx] = ms;
+    s_f[item][sidx] = ls;
+  }
+  __syncthreads();
+  if (threadIdx.x < G) {
+    int item = threadIdx.x;
+    float M = -INFINITY;
+    for (int sidx = 0; sidx < n_splits; ++sidx) M = fmaxf(M, s_m[item][sidx]);
+    float L = 0.f;
+    for (int sidx = 0; sidx < n_splits; ++sidx) {  // chunk order: independent of which CTA came last
+      float f = (s_m[item][sidx] == -INFINITY) ? 0.f : exp2f(s_m[item][sidx] - M);
+      L += s_f[item][sidx] * f;
+      s_f[item][sidx] = f;
+    }
+    s_inv[item] = L > 0.f ? 1.f / L : 0.f;
+  }
+  __syncthreads();
   for (int idx = threadIdx.x; idx < G * D; idx += NTHREADS) {
     int item = idx / D, dim = idx % D;
-    const float* src0 = part_row + (size_t)item * n_splits * FR;
-    float M = -INFINITY;
-    for (int sidx = 0; sidx < n_splits; ++sidx) M = fmaxf(M, __ldcg(src0 + (size_t)sidx * FR + D));
-    float L = 0.f, O = 0.f;
-    for (int sidx = 0; sidx < n_splits; ++sidx) {  // chunk order: independent of which CTA came last
-      const float* src = src0 + (size_t)sidx * FR;
-      float ms = __ldcg(src + D);
-      float f = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
-      L += __ldcg(src + D + 1) * f;
-      O += __ldcg(src + dim) * f;
-    }
-    p.out[(size_t)dec_row * p.out_stride + (size_t)(kvh * G + item) * D + dim] =
-        __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+    const float* src0 = part_row + (size_t)item * n_splits * FR + dim;
+    float v[MAXS];
+#pragma unroll
+    for (int sidx = 0; sidx < MAXS; ++sidx) v[sidx] = sidx < n_splits ? __ldcg(src0 + (size_t)sidx * FR) : 0.f;
+    float O = 0.f;
+#pragma unroll
+    for (int sidx = 0; sidx < MAXS; ++sidx) O += v[sidx] * s_f[item][sidx];
+    p.out[(size_t)dec_row * p.out_stride + (size_t)(kvh * G + item) * D + dim] = __float2bfloat16_rn(O * s_inv[item]);
   }
   if (threadIdx.x == 0) p.counters[blockIdx.z * p.nkv + kvh] = 0;
 }
@@ -399,7 +446,7 @@ int launch(const AttnParams& p, dim3 grid, cudaStream_t stream) {
     }
     configured = true;
   }
-  attn_mma_kernel<D, DECODE><<<grid, NTHREADS, smem, stream>>>(p);
+  cuca_launch(attn_mma_kernel<D, DECODE>, grid, dim3(NTHREADS), smem, stream, true, p);
   CUCA_CHECK_LAUNCH("attention_mma");
   return 0;
 }
@@ -437,6 +484,7 @@ CUCA_API size_t cuca_attention_decode_scratch(int n_rows, int nh, int d, int n_s
 
 // Decode form: one query row per entry of `rows` (null: rows 0..n_rows-1), keys split in chunks of `chunk`
 // positions (a multiple of 64), `n_splits` chunks cover every row's keys (n_splits * chunk > largest position).
+// chunk = 0: each row divides its own keys evenly over the n_splits chunks, whatever its length.
 CUCA_API int cuca_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* kpool,
                                    const void* vpool, int n_blocks, int bs, const int* positions,
                                    const int* seq_of_row, const int* tables, int table_stride, const int* rows,
@@ -445,7 +493,8 @@ CUCA_API int cuca_attention_decode(const void* q, int q_stride, void* out, int o
   if (n_rows == 0) return 0;
   CUCA_REQUIRE(cuca_attention_mma_supported(nh, nkv, d, q_stride, out_stride), "attention_decode: unsupported shape "
                "(heads %d/%d, head size %d)", nh, nkv, d);
-  CUCA_REQUIRE(chunk > 0 && chunk % TILE == 0 && n_splits >= 1 && n_splits <= 65535, "attention_decode: bad chunking");
+  CUCA_REQUIRE(chunk >= 0 && chunk % TILE == 0 && n_splits >= 1 && n_splits <= 32, "attention_decode: bad chunking (at most 32 chunks)");
+  CUCA_REQUIRE(bs > 0 && (bs & (bs - 1)) == 0, "attention_decode: %d positions per page is no power of two", bs);
   CUCA_REQUIRE(n_splits == 1 || (part && counters), "attention_decode: split keys need scratch");
   CUCA_REQUIRE(n_rows <= 65535, "attention_decode: too many rows");
   AttnParams p;
@@ -468,6 +517,7 @@ CUCA_API int cuca_attention_prefill(const void* q, int q_stride, void* out, int 
   CUCA_REQUIRE(cuca_attention_mma_supported(nh, nkv, d, q_stride, out_stride), "attention_prefill: unsupported "
                "shape (heads %d/%d, head size %d)", nh, nkv, d);
   CUCA_REQUIRE(nh <= 65535, "attention_prefill: too many heads");
+  CUCA_REQUIRE(bs > 0 && (bs & (bs - 1)) == 0, "attention_prefill: %d positions per page is no power of two", bs);
   AttnParams p;
   p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride; p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
   p.kpool = (const __nv_bfloat16*)kpool; p.vpool = (const __nv_bfloat16*)vpool; p.n_blocks = n_blocks; p.bs = bs;

@@ -38,6 +38,32 @@ extern "C" const char* cuca_last_error();
     }                                                                               \
   } while (0)
 
+// Programmatic dependent launch: a kernel launched with the attribute may start while its predecessor in
+// the stream still runs. pdl_trigger() lets the successor's CTAs become resident early; pdl_wait() blocks
+// until the predecessor has completed and its writes are visible. Every kernel calls pdl_wait() in every CTA
+// before it reads or writes anything an earlier kernel touches (both are no-ops without the attribute).
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+bool cuca_pdl_enabled();
+
+// Launch `kernel`; with `pdl` (and PDL enabled) as a programmatic dependent of the previous kernel in `stream`.
+template <typename... KArgs, typename... Args>
+cudaError_t cuca_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl,
+                        Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (pdl && cuca_pdl_enabled()) ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <typename T> __device__ __forceinline__ T from_f32(float v);

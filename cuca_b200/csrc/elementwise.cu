@@ -15,12 +15,26 @@ void cuca_set_error(const char* fmt, ...) {
   g_last_error = buf;
 }
 CUCA_API const char* cuca_last_error() { return g_last_error.c_str(); }
-CUCA_API int cuca_abi_version() { return 3; }
+CUCA_API int cuca_abi_version() { return 4; }
+
+#include <stdlib.h>
+static int g_pdl = -1;
+bool cuca_pdl_enabled() {
+  if (g_pdl < 0) {
+    const char* e = getenv("CUCA_PDL");
+    g_pdl = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_pdl != 0;
+}
+// 1: kernels are launched as programmatic dependents of their predecessors (default); 0: plain stream order.
+CUCA_API int cuca_set_pdl(int on) { g_pdl = on ? 1 : 0; return 0; }
 
 // ---------------------------------------------------------------- embedding
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
                              float* __restrict__ x, int E, int V, int* err) {
+  pdl_trigger();
+  pdl_wait();
   int row = blockIdx.x;
   int tok = tokens[row];
   if (tok < 0 || tok >= V) {
@@ -54,6 +68,8 @@ template <typename TW, typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
                                const int* __restrict__ rows, int E, float eps) {
   __shared__ float red[8];
+  pdl_trigger();
+  pdl_wait();
   int orow = blockIdx.x;
   int irow = rows ? rows[orow] : orow;
   if (irow < 0) return;
@@ -80,7 +96,7 @@ CUCA_API int cuca_rmsnorm(const float* x, const void* w, int w_dtype, void* out,
   if (n_rows == 0) return 0;
   CUCA_REQUIRE(E > 0, "rmsnorm: bad width %d", E);
 #define LAUNCH(TW, TO) \
-  rmsnorm_kernel<TW, TO><<<n_rows, 256, 0, stream>>>(x, (const TW*)w, (TO*)out, rows, E, eps)
+  cuca_launch(rmsnorm_kernel<TW, TO>, dim3(n_rows), dim3(256), 0, stream, true, x, (const TW*)w, (TO*)out, rows, E, eps)
   if (w_dtype == CUCA_F32 && out_dtype == CUCA_F32) LAUNCH(float, float);
   else if (w_dtype == CUCA_F32 && out_dtype == CUCA_BF16) LAUNCH(float, __nv_bfloat16);
   else if (w_dtype == CUCA_BF16 && out_dtype == CUCA_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
@@ -102,6 +118,8 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
                                   int table_stride, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                   int table_rows, int rot, T* __restrict__ kpool, T* __restrict__ vpool,
                                   int n_blocks, int bs, int nh, int nkv, int d, int* err) {
+  pdl_trigger();
+  pdl_wait();
   int row = blockIdx.x;
   int head = blockIdx.y;  // 0..nh-1 q, nh..nh+nkv-1 k, then v
   int seq = seq_of_row[row];
@@ -153,12 +171,13 @@ CUCA_API int cuca_rope_store(void* qkv, int dtype, const int* positions, const i
   dim3 grid(n_rows, nh + 2 * nkv);
   int threads = d / 2 >= 64 ? 64 : 32;
   if (dtype == CUCA_F32)
-    rope_store_kernel<float><<<grid, threads, 0, stream>>>((float*)qkv, positions, seq_of_row, tables, table_stride,
-        cos_t, sin_t, table_rows, rot, (float*)kpool, (float*)vpool, n_blocks, bs, nh, nkv, d, err);
+    cuca_launch(rope_store_kernel<float>, grid, dim3(threads), 0, stream, true, (float*)qkv, positions, seq_of_row,
+                tables, table_stride, cos_t, sin_t, table_rows, rot, (float*)kpool, (float*)vpool, n_blocks, bs, nh,
+                nkv, d, err);
   else if (dtype == CUCA_BF16)
-    rope_store_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((__nv_bfloat16*)qkv, positions, seq_of_row, tables,
-        table_stride, cos_t, sin_t, table_rows, rot, (__nv_bfloat16*)kpool, (__nv_bfloat16*)vpool, n_blocks, bs, nh,
-        nkv, d, err);
+    cuca_launch(rope_store_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, true, (__nv_bfloat16*)qkv,
+                positions, seq_of_row, tables, table_stride, cos_t, sin_t, table_rows, rot, (__nv_bfloat16*)kpool,
+                (__nv_bfloat16*)vpool, n_blocks, bs, nh, nkv, d, err);
   else
     CUCA_REQUIRE(false, "rope_store: unknown dtype %d", dtype);
   CUCA_CHECK_LAUNCH("rope_store");

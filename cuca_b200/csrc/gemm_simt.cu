@@ -25,6 +25,8 @@ gemm_simt_kernel(const TI* __restrict__ A, const TI* __restrict__ W, const TI* _
   constexpr bool DUAL = EPI == EPI_SWIGLU;
   __shared__ float As[BK][BM + 1];
   __shared__ float Bs[DUAL ? 2 : 1][BK][BN + 1];
+  pdl_trigger();
+  pdl_wait();
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   float acc[TM][4];
@@ -102,12 +104,12 @@ void launch(const void* A, const void* W, const void* bias, void* out, int M, in
             cudaStream_t stream) {
   if (M <= 16) {
     dim3 grid((N + BN - 1) / BN, (M + 15) / 16);
-    gemm_simt_kernel<TI, TO, 1, EPI><<<grid, 256, 0, stream>>>((const TI*)A, (const TI*)W, (const TI*)bias, (TO*)out,
-                                                              M, N, K, lda, ldo);
+    cuca_launch(gemm_simt_kernel<TI, TO, 1, EPI>, grid, dim3(256), 0, stream, true, (const TI*)A, (const TI*)W,
+                (const TI*)bias, (TO*)out, M, N, K, lda, ldo);
   } else {
     dim3 grid((N + BN - 1) / BN, (M + 63) / 64);
-    gemm_simt_kernel<TI, TO, 4, EPI><<<grid, 256, 0, stream>>>((const TI*)A, (const TI*)W, (const TI*)bias, (TO*)out,
-                                                              M, N, K, lda, ldo);
+    cuca_launch(gemm_simt_kernel<TI, TO, 4, EPI>, grid, dim3(256), 0, stream, true, (const TI*)A, (const TI*)W,
+                (const TI*)bias, (TO*)out, M, N, K, lda, ldo);
   }
 }
 

@@ -33,7 +33,6 @@ namespace {
 constexpr int TILE_N = 128;  // weight rows (output features) per CTA = TMEM lanes
 constexpr int TILE_K = 64;   // bf16 elements per stage row = 128 bytes = one swizzle span
 constexpr int UMMA_K = 16;
-constexpr int SMEM_BUDGET = 200 * 1024;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -156,6 +155,9 @@ struct Cfg {
   static constexpr int W_BYTES = TILE_N * TILE_K * 2 * (DUAL ? 2 : 1);
   static constexpr int X_BYTES = BN * TILE_K * 2;
   static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
+  // decode-sized tiles keep under half of an SM's shared memory, so the CTAs of the next contraction can move
+  // in and prefetch their weights while this one drains; prefill-sized tiles take most of it
+  static constexpr int SMEM_BUDGET = (BN <= 64 ? 108 : 200) * 1024;
   static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) > 8 ? 8 : (SMEM_BUDGET / STAGE_BYTES);
   static constexpr int NCOLS = BN * (DUAL ? 2 : 1);
   static constexpr int TMEM_COLS = NCOLS < 32 ? 32 : NCOLS;
@@ -201,6 +203,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   if (ks_end > total_ksteps) ks_end = total_ksteps;
   const int nk = ks_end - ks_begin;
 
+  pdl_trigger();
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(&full[s], 1);
@@ -222,7 +225,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 
   if (warp == 0 && lane == 0) {
     // ------------------------------------------------ producer: TMA loads into the stage ring
-    for (int i = 0; i < nk; ++i) {
+    // Weights are never written by a kernel, so the first ring of weight tiles is requested before waiting
+    // for the predecessor; activations only after it.
+    const int pre = nk < C::STAGES ? nk : C::STAGES;
+    for (int i = 0; i < pre; ++i) {
+      uint8_t* st = smem + i * C::STAGE_BYTES;
+      mbar_expect_tx(&full[i], C::STAGE_BYTES);
+      int kc = (ks_begin + i) * TILE_K;
+      tma_load_2d(st, &tmW, &full[i], kc, n0);
+      if (DUAL) tma_load_2d(st + TILE_N * TILE_K * 2, &tmW, &full[i], kc, p.N + n0);
+    }
+    pdl_wait();
+    for (int i = 0; i < pre; ++i)
+      tma_load_2d(smem + i * C::STAGE_BYTES + C::W_BYTES, &tmX, &full[i], (ks_begin + i) * TILE_K, m0);
+    for (int i = pre; i < nk; ++i) {
       int s = i % C::STAGES;
       uint32_t ph = (i / C::STAGES) & 1;
       if (!mbar_wait(&empty[s], ph ^ 1, p.err)) { ok = false; break; }
@@ -234,6 +250,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       tma_load_2d(st + C::W_BYTES, &tmX, &full[s], kc, m0);
     }
   } else if (warp == 1 && lane == 0) {
+    pdl_wait();
     // ------------------------------------------------ MMA issuer
     constexpr uint32_t idesc = instr_desc(BN);
     for (int i = 0; i < nk; ++i) {
@@ -255,6 +272,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       umma_commit(&empty[s]);
     }
     umma_commit(accum_full);
+  } else {
+    pdl_wait();
   }
   __syncwarp();
 
@@ -313,19 +332,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           float v[8], u[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) v[j] = u[j] = 0.f;
-          for (int s = 0; s < p.splits; ++s) {  // split order: the sum does not depend on who arrived last
-            const float* part = base + (size_t)s * C::NCOLS * TILE_N + threadIdx.x;
-            float a[8], b[8];
+          // split order: the sum does not depend on who arrived last; four splits' loads are in flight at once
+          for (int s0 = 0; s0 < p.splits; s0 += 4) {
+            float a[4][8], b[4][8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              a[j] = __ldcg(part + (size_t)(c + j) * TILE_N);
-              if (DUAL) b[j] = __ldcg(part + (size_t)(BN + c + j) * TILE_N);
+            for (int ss = 0; ss < 4; ++ss) {
+              const bool live = s0 + ss < p.splits;
+              const float* part = base + (size_t)(s0 + ss) * C::NCOLS * TILE_N + threadIdx.x;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                a[ss][j] = live ? __ldcg(part + (size_t)(c + j) * TILE_N) : 0.f;
+                if (DUAL) b[ss][j] = live ? __ldcg(part + (size_t)(BN + c + j) * TILE_N) : 0.f;
+              }
             }
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              v[j] += a[j];
-              if (DUAL) u[j] += b[j];
-            }
+            for (int ss = 0; ss < 4; ++ss)
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                v[j] += a[ss][j];
+                if (DUAL) u[j] += b[ss][j];
+              }
           }
 #pragma unroll
           for (int j = 0; j < 8; ++j) write_out<DUAL>(p, feature, m0 + c + j, v[j], u[j]);
@@ -428,7 +454,7 @@ int launch_tc(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p, d
     }
     configured = true;
   }
-  gemm_tc_kernel<BN, DUAL><<<grid, 128, C::SMEM, stream>>>(tmW, tmX, p);
+  cuca_launch(gemm_tc_kernel<BN, DUAL>, grid, dim3(128), C::SMEM, stream, true, tmW, tmX, p);
   CUCA_CHECK_LAUNCH("gemm_tc");
   return 0;
 }

@@ -287,6 +287,8 @@ sample_kernel(const float* __restrict__ logits, size_t row_stride, int V, const 
               const int* __restrict__ slot_of_row, int* __restrict__ out, unsigned long long* __restrict__ scratch,
               int scratch_stride) {
   __shared__ Shared sh;
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * row_stride;
   const int slot = slot_of_row[r];
@@ -457,8 +459,8 @@ CUCA_API int cuca_sample(const float* logits, size_t row_stride, int n_rows, int
   CUCA_REQUIRE(V > 0, "sample: empty vocabulary");
   CUCA_REQUIRE(scratch == nullptr || scratch_stride >= cuca_sample_scratch_stride(V),
                "sample: scratch rows of %d words are too short for a vocabulary of %d", scratch_stride, V);
-  sample_kernel<<<n_rows, NT, 0, stream>>>(logits, row_stride, V, temperature, top_k, top_p, rng, slot_of_row, out,
-                                           scratch, scratch_stride);
+  cuca_launch(sample_kernel, dim3(n_rows), dim3(NT), 0, stream, true, logits, row_stride, V, temperature, top_k, top_p,
+              rng, slot_of_row, out, scratch, scratch_stride);
   CUCA_CHECK_LAUNCH("sample");
   return 0;
 }
@@ -467,6 +469,8 @@ namespace {
 __global__ void decode_advance_kernel(int* __restrict__ tokens, int* __restrict__ positions,
                                       const int* __restrict__ slot_of_row, const int* __restrict__ sampled,
                                       int* __restrict__ history, int* __restrict__ counter, int n, int max_steps) {
+  pdl_trigger();
+  pdl_wait();
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   int step = *counter;
   if (i < n) {
@@ -488,7 +492,8 @@ CUCA_API int cuca_decode_advance(int* tokens, int* positions, const int* slot_of
                                  int* history, int* counter, int n, int max_steps, cudaStream_t stream) {
   if (n == 0) return 0;
   CUCA_REQUIRE(n <= 1024, "decode_advance: at most 1024 rows");
-  decode_advance_kernel<<<1, 1024, 0, stream>>>(tokens, positions, slot_of_row, sampled, history, counter, n, max_steps);
+  cuca_launch(decode_advance_kernel, dim3(1), dim3(1024), 0, stream, true, tokens, positions, slot_of_row, sampled,
+              history, counter, n, max_steps);
   CUCA_CHECK_LAUNCH("decode_advance");
   return 0;
 }

@@ -42,6 +42,7 @@ _SIGNATURES = {
     "cuca_attention_prefill": [_P, _I, _P, _I, _P, _P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _P,
                                _P],
     "cuca_decode_advance": [_P, _P, _P, _P, _P, _P, _I, _I, _P],
+    "cuca_set_pdl": [_I],
     "cuca_gemm_tc_supported": [_P, _P, _I, _I, _I, _I],
     "cuca_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, c_size_t, _P, _I, _I, _P, _P],
 }

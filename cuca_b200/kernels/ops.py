@@ -171,15 +171,13 @@ def attention_mma_supported(n_heads, n_kv_heads, head_dim, q_stride, out_stride)
     return bool(lib.cuca_attention_mma_supported(n_heads, n_kv_heads, head_dim, q_stride, out_stride))
 
 
-def decode_chunking(n_rows: int, n_kv_heads: int, max_len: int, sms: int = 148):
-    """Key positions per chunk (a multiple of 64) and number of chunks: the widest chunk that still gives
-    about two CTAs per SM, so a single long request is split finely and a full batch coarsely."""
-    chunk = 64
-    for c in (1024, 512, 256, 128):
-        if n_rows * n_kv_heads * -(-max_len // c) >= 2 * sms:
-            chunk = c
-            break
-    return chunk, max(1, -(-max_len // chunk))
+def decode_chunking(n_rows: int, n_kv_heads: int, max_len: int, cta_slots: int = 444):
+    """(chunk, n_splits) of the decode attention. chunk 0: every row spreads its own keys evenly over n_splits
+    chunks; n_splits is what fills the GPU once (three CTAs per SM fit) for this many rows, at most one chunk per
+    tile of 64 keys of the longest row and at most 32."""
+    tiles = max(1, -(-max_len // 64))
+    n_splits = max(1, min(32, tiles, cta_slots // max(1, n_rows * n_kv_heads)))
+    return 0, n_splits
 
 
 def attention_decode(q, q_stride, out, kpool, vpool, positions, seq_of_row, tables, rows, n_rows, n_heads,
@@ -207,7 +205,8 @@ def attention(qkv, out, cache, step, n_heads, n_kv_heads, head_dim, scale, windo
     portions of prompts through the prefill form; everything else (the 32-bit path, other head sizes) through
     the plain kernel."""
     plan = getattr(step, "attention_plan", None)
-    if (out.dtype == torch.bfloat16 and plan is not None
+    bs = cache.block_size
+    if (out.dtype == torch.bfloat16 and plan is not None and bs & (bs - 1) == 0
             and attention_mma_supported(n_heads, n_kv_heads, head_dim, qkv.stride(0), out.stride(0))):
         if plan.n_decode:
             attention_decode(qkv, qkv.stride(0), out, cache.k, cache.v, step.positions, step.seq_of_row,

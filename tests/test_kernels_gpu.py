@@ -249,7 +249,7 @@ MMA_SHAPES = [(4, 2, 16, 16, None), (3, 1, 32, 16, None), (6, 3, 48, 8, 20), (8,
 
 
 @pytest.mark.parametrize("nh,nkv,d,bs,window", MMA_SHAPES)
-@pytest.mark.parametrize("chunk", [64, 256])
+@pytest.mark.parametrize("chunk", [64, 256, 0])
 def test_attention_decode_mma(dev, nh, nkv, d, bs, window, chunk):
     """Split-key decode attention on tensor cores against contiguous 32-bit attention: scrambled pages,
     lengths around page, tile and chunk edges, a row list with gaps, one far key that stands out."""
@@ -277,7 +277,7 @@ def test_attention_decode_mma(dev, nh, nkv, d, bs, window, chunk):
     out = torch.zeros(T, nh * d, device=dev, dtype=dtype)
     err = torch.zeros(1, dtype=torch.int32, device=dev)
     rows_t = torch.tensor(rows, dtype=torch.int32, device=dev)
-    n_splits = -(-max(lens) // chunk)
+    n_splits = -(-max(lens) // chunk) if chunk else 5  # chunk 0: each row spreads its keys over 5 chunks
     for _ in range(2):  # twice: the arrival counters must be left zeroed
         out.zero_()
         ops.attention_decode(qb, nh * d, out, kpool, vpool, positions, seq, tables, rows_t, len(rows), nh, nkv, d,
