@@ -93,3 +93,57 @@ def test_fp32_splits_agree_to_the_bit(models):
         for j, w in enumerate(e["want"]):
             assert np.array_equal(got[s["step"]][j], a[pos + w]), f"position {pos + w} differs between splits"
         pos += len(e["tokens"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_one_by_one(models, dtype):
+    """A short prompt, then two hundred tokens one at a time: every position crosses page and key-tile edges."""
+    reqs = {"long": tiny.random_tokens(250, tiny.CONFIGS["B"]["vocab_size"], seed=77)}
+    steps = ru.trace_tail_one_by_one(reqs, tail=230)
+    got = ru.run_in_process(models["B"], dtype, steps, 256)
+    ru.compare(steps, got, reqs, ru.Oracle(models["B"]), TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["A", "B"])
+def test_first_tokens_of_a_sequence(models, which, dtype):
+    """Positions 0, 1, 2 ...: a request that starts with single tokens, beside one that starts with two."""
+    vocab = tiny.CONFIGS[which]["vocab_size"]
+    reqs = {"x": tiny.random_tokens(6, vocab, seed=1), "y": tiny.random_tokens(7, vocab, seed=2)}
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": reqs["x"][:1], "want": [0]},
+                                     {"id": "y", "tokens": reqs["y"][:2], "want": [0, 1]}], "end": []}]
+    for i in range(1, 6):
+        steps.append({"step": i, "entries": [{"id": "x", "tokens": reqs["x"][i:i + 1], "want": [0]},
+                                             {"id": "y", "tokens": reqs["y"][i + 1:i + 2], "want": [0]}],
+                      "end": ["x", "y"] if i == 5 else []})
+    got = ru.run_in_process(models[which], dtype, steps, 128)
+    ru.compare(steps, got, reqs, ru.Oracle(models[which]), TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_far_key_among_hundreds_is_found_after_cuts(tmp_path_factory, dtype):
+    """Random weights give flat attention that would hide a lost key. Here layer 0's query and key projections
+    are scaled so that scores are sharp, and the sequence repeats one early token late: the late position's
+    logits then depend on a key hundreds of positions back, across pages written in earlier steps."""
+    import plain_llama
+    from cuca_b200.weights import safetensors_io as st
+    d = tmp_path_factory.mktemp("sharp")
+    tiny.write_tiny(d, "B")
+    w = plain_llama.read_safetensors(d / "model.safetensors")
+    for name in ("model.layers.0.self_attn.q_proj.weight", "model.layers.0.self_attn.k_proj.weight"):
+        w[name] = (w[name].float() * 12.0).to(torch.bfloat16)
+    st.write_safetensors(d / "model.safetensors", w)
+    toks = tiny.random_tokens(240, 512, seed=31)
+    toks[3] = 499
+    toks = [t if t != 499 or i == 3 else 498 for i, t in enumerate(toks)]
+    toks[-1] = 499  # the last position looks for its own token's earlier key at position 3
+    reqs = {"s": toks}
+    cfg, weights = plain_llama.load_model_dir(d)
+    ref = plain_llama.forward(cfg, weights, toks)
+    moved = toks[:]
+    moved[3] = 7
+    assert float((plain_llama.forward(cfg, weights, moved)[-1] - ref[-1]).abs().max()) > 10 * TOL[dtype] * float(
+        ref[-1].abs().max()), "the far key must matter for this test to see a lost page"
+    for steps in (ru.trace_portions(reqs, sizes=(100, 2, 60, 7, 64, 3, 2, 2)), ru.trace_tail_one_by_one(reqs)):
+        got = ru.run_in_process(d, dtype, steps, 256)
+        ru.compare(steps, got, reqs, ru.Oracle(d), TOL[dtype])
