@@ -47,7 +47,8 @@ def _register_toy_parts():
             for slot, count in zip(step.host["slots"], step.host["counts"]):
                 cs = torch.cumsum(h[r:r + count].float(), 0) + cache.state[slot]
                 cache.state[slot] = cs[-1]
-                stream[r:r + count] += cs @ self.w.float().T
+                # 64-bit products: torch's 32-bit matmul may run in a reduced-precision tensor-core mode
+                stream[r:r + count] += (cs.double() @ self.w.double().T).float()
                 r += count
 
     @register_feed_forward("toy_routed")
@@ -73,13 +74,13 @@ def _register_toy_parts():
             self.down = [get(t["down"].format(e)) for e in range(self.p["experts"])]
 
         def forward(self, h, stream, step):
-            x = h.float()
-            choice = (x @ self.router.float().T).argmax(-1)
+            x = h.double()
+            choice = (x @ self.router.double().T).argmax(-1)
             for e in range(self.p["experts"]):
                 rows = (choice == e).nonzero().flatten()
                 if rows.numel():
-                    y = torch.relu(x[rows] @ self.up[e].float().T) @ self.down[e].float().T
-                    stream.index_add_(0, rows, y)
+                    y = torch.relu(x[rows] @ self.up[e].double().T) @ self.down[e].double().T
+                    stream.index_add_(0, rows, y.float())
 
     @register_position("toy_adjacent_rope")
     class AdjacentRope(PositionEncoding):
@@ -97,7 +98,7 @@ def _register_toy_parts():
             heads = qkv[:, :(n_heads + n_kv_heads) * head_dim].view(T, n_heads + n_kv_heads, head_dim // 2, 2)
             c = self.cos[positions.long()][:, None, :]
             s = self.sin[positions.long()][:, None, :]
-            a, b = heads[..., 0].float(), heads[..., 1].float()
+            a, b = heads[..., 0].float().clone(), heads[..., 1].float().clone()  # .float() of 32-bit is a view
             heads[..., 0] = (a * c - b * s).to(qkv.dtype)
             heads[..., 1] = (a * s + b * c).to(qkv.dtype)
 

@@ -123,27 +123,38 @@ def test_first_tokens_of_a_sequence(models, which, dtype):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_a_far_key_among_hundreds_is_found_after_cuts(tmp_path_factory, dtype):
     """Random weights give flat attention that would hide a lost key. Here layer 0's query and key projections
-    are scaled so that scores are sharp, and the sequence repeats one early token late: the late position's
-    logits then depend on a key hundreds of positions back, across pages written in earlier steps."""
+    are scaled so that scores are sharp, and one embedding row is built so that the last token's query (head 0)
+    points at the key of position 3: the last position's logits then hang on a key hundreds of positions back,
+    in a page written by an earlier step."""
     import plain_llama
     from cuca_b200.weights import safetensors_io as st
     d = tmp_path_factory.mktemp("sharp")
     tiny.write_tiny(d, "B")
-    w = plain_llama.read_safetensors(d / "model.safetensors")
-    for name in ("model.layers.0.self_attn.q_proj.weight", "model.layers.0.self_attn.k_proj.weight"):
-        w[name] = (w[name].float() * 12.0).to(torch.bfloat16)
+    cfg, w = plain_llama.load_model_dir(d)
+    pre = "model.layers.0.self_attn."
+    for name, scale in (("q_proj", 8.0), ("k_proj", 8.0), ("v_proj", 4.0), ("o_proj", 4.0)):
+        w[pre + name + ".weight"] = (w[pre + name + ".weight"].float() * scale).to(torch.bfloat16)
+    P, far, dh = 239, 3, cfg["head_dim"]
+    cos, sin = plain_llama.rope_tables(P + 1, dh, cfg["rope_theta"], plain_llama.llama3_factors(cfg, dh))
+    E = w["model.embed_tokens.weight"].float()
+    wq, wk = w[pre + "q_proj.weight"].float()[:dh], w[pre + "k_proj.weight"].float()
+    n_key = plain_llama.rms_norm(E[498:499], torch.ones(E.shape[1]), cfg["rms_norm_eps"])
+    k_far = plain_llama.rotate_half_split((n_key @ wk.T).view(1, 1, dh), cos[far:far + 1], sin[far:far + 1])
+    target = plain_llama.rotate_half_split(k_far, cos[P:P + 1], -sin[P:P + 1])[0, 0]  # rotate back from position P
+    n_query = torch.linalg.pinv(wq) @ target
+    E[499] = n_query / n_query.norm() * E[498].norm()
+    w["model.embed_tokens.weight"] = E.to(torch.bfloat16)
     st.write_safetensors(d / "model.safetensors", w)
-    toks = tiny.random_tokens(240, 512, seed=31)
-    toks[3] = 499
-    toks = [t if t != 499 or i == 3 else 498 for i, t in enumerate(toks)]
-    toks[-1] = 499  # the last position looks for its own token's earlier key at position 3
+
+    toks = [t if t not in (498, 499) else 497 for t in tiny.random_tokens(P + 1, 512, seed=31)]
+    toks[far], toks[P] = 498, 499
     reqs = {"s": toks}
     cfg, weights = plain_llama.load_model_dir(d)
     ref = plain_llama.forward(cfg, weights, toks)
     moved = toks[:]
-    moved[3] = 7
-    assert float((plain_llama.forward(cfg, weights, moved)[-1] - ref[-1]).abs().max()) > 10 * TOL[dtype] * float(
-        ref[-1].abs().max()), "the far key must matter for this test to see a lost page"
+    moved[far] = 7
+    influence = float((plain_llama.forward(cfg, weights, moved)[-1] - ref[-1]).abs().max())
+    assert influence > 10 * TOL[dtype] * float(ref[-1].abs().max()), "the far key must matter, or a lost page hides"
     for steps in (ru.trace_portions(reqs, sizes=(100, 2, 60, 7, 64, 3, 2, 2)), ru.trace_tail_one_by_one(reqs)):
         got = ru.run_in_process(d, dtype, steps, 256)
         ru.compare(steps, got, reqs, ru.Oracle(d), TOL[dtype])
