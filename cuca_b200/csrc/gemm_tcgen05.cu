@@ -1,23 +1,25 @@
 // bfloat16 contraction on the 5th-generation tensor cores: out = epilogue(X[M,K] W[N,K]^T).
 //
-// The weight is the MMA's 128-row operand and the tokens are its N dimension
-// (16..256), so one kernel serves a 2048-token prefill and a handful of decode
-// rows: D[feature, token] accumulates in tensor memory, one TMEM lane per
-// output feature. Both operands are K-major, as stored: TMA brings 128 x 64
-// weight tiles and BN x 64 activation tiles (128-byte swizzle) into a ring of
-// shared-memory stages; one thread issues tcgen05.mma (kind::f16, 32-bit
-// accumulate) and tcgen05.commit hands each stage back to the producer. The
-// epilogue reads TMEM with tcgen05.ld and fuses bias, the add into the 32-bit
-// residual stream, or SwiGLU (gate and up tiles accumulate side by side in
-// TMEM, so the same thread holds both values of a feature).
+// A persistent, warp-specialised kernel: one warp streams tiles with TMA (128-byte swizzle) into a ring of
+// shared-memory stages, one thread issues tcgen05.mma (kind::f16, 32-bit accumulate) into one of two TMEM
+// accumulators, and four warps drain the other accumulator with tcgen05.ld and run the epilogue (store, bias,
+// add into the 32-bit residual stream, or SwiGLU), so the epilogue of one tile overlaps the main loop of the
+// next. tcgen05.commit hands stages back to the producer and accumulators to the epilogue.
 //
-// Decode shapes have fewer 128-row tiles than the GPU has SMs, so K is split
-// over several CTAs: each writes its 32-bit partial tile to a workspace and the
-// last one to arrive adds the partials in split order (the result does not
-// depend on arrival order) and runs the epilogue.
+// Two orientations share the code. Up to 64 tokens (decode), the weight is the 128-row MMA operand and the
+// tokens are the N dimension (16..64): D[feature, token], one TMEM lane per output feature. Above, the tokens
+// are the 128-row operand and 256 weight rows the N dimension: D[token, feature], so a thread owns a run of
+// consecutive features of one token and stores vectors. For SwiGLU the gate and up tiles accumulate side by
+// side in TMEM, so one thread holds both values of a feature.
 //
-// Every wait on an mbarrier is bounded; on a timeout the kernel records
-// CUCA_ERR_WAIT_TIMEOUT, lets copies in flight land, frees its TMEM and returns.
+// Work is cut in units of one 64-wide K step of one tile. With plenty of tiles, CTAs take whole tiles in
+// turn. With few tiles (decode: 32 to 1002 tiles of 64 K steps on 148 SMs) the units are dealt out evenly
+// ("stream-K"): a CTA's share may start and end inside a tile; partial tiles go to a workspace and the last CTA
+// to arrive adds the parts in K order (the result does not depend on arrival order) and runs the epilogue.
+//
+// The kernel is a programmatic dependent: it requests its first ring of weight tiles before waiting for its
+// predecessor, since weights are never written. Every wait on an mbarrier is bounded; on a timeout the kernel
+// records CUCA_ERR_WAIT_TIMEOUT, every role stops, copies in flight land, TMEM is freed and the kernel returns.
 #include "common.cuh"
 #include <cuda.h>
 #include <mutex>
@@ -30,9 +32,10 @@
 
 namespace {
 
-constexpr int TILE_N = 128;  // weight rows (output features) per CTA = TMEM lanes
+constexpr int TILE_A = 128;  // rows of the MMA's M operand = TMEM lanes
 constexpr int TILE_K = 64;   // bf16 elements per stage row = 128 bytes = one swizzle span
 constexpr int UMMA_K = 16;
+constexpr int NTHREADS = 192;  // warp 0 producer, warp 1 MMA, warps 2..5 epilogue
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -62,18 +65,28 @@ __device__ __forceinline__ unsigned long long global_ns() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait: false (and the error word set) if the phase did not complete in WAIT_LIMIT_NS.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err) {
+// Bounded wait: false if the phase did not complete in WAIT_LIMIT_NS (the error word is set) or if another
+// role of this CTA gave up (`abort` is set).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, volatile int* abort) {
   if (mbar_try_wait(bar, parity)) return true;
   unsigned long long t0 = global_ns();
+  unsigned spins = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if (global_ns() - t0 > WAIT_LIMIT_NS) {
-      if (err) atomicExch(err, CUCA_ERR_WAIT_TIMEOUT);
-      return false;
+    if ((++spins & 63u) == 0) {
+      if (*abort) return false;
+      if (global_ns() - t0 > WAIT_LIMIT_NS) {
+        if (err) atomicExch(err, CUCA_ERR_WAIT_TIMEOUT);
+        *abort = 1;
+        return false;
+      }
     }
   }
   return true;
 }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -133,8 +146,9 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
 }
 // Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128, N = n.
 __host__ __device__ constexpr uint32_t instr_desc(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_N >> 4) << 24);
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_A >> 4) << 24);
 }
+
 
 struct Params {
   void* out;
@@ -146,71 +160,177 @@ struct Params {
   int ldo;
   int epilogue;
   int out_f32;
-  int splits;
-  int ksteps_per_split;
+  int tiles_a;   // tiles along the 128-row operand
+  int tiles;     // all tiles
+  int ksteps;    // K steps per tile
+  int stream_k;  // 1: units dealt out evenly; 0: whole tiles in turn
+  int max_parts; // workspace slots per tile
 };
 
-template <int BN, bool DUAL>
+// SWAP: weight rows on the 128 lanes, BN tokens as columns. Otherwise tokens on the lanes, 256 weight rows
+// (SwiGLU: 128 gate + 128 up) as columns.
+template <int BN, bool DUAL, bool SWAP>
 struct Cfg {
-  static constexpr int W_BYTES = TILE_N * TILE_K * 2 * (DUAL ? 2 : 1);
-  static constexpr int X_BYTES = BN * TILE_K * 2;
-  static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
-  // decode-sized tiles keep under half of an SM's shared memory, so the CTAs of the next contraction can move
-  // in and prefetch their weights while this one drains; prefill-sized tiles take most of it
-  static constexpr int SMEM_BUDGET = (BN <= 64 ? 108 : 200) * 1024;
+  static constexpr int A_BYTES = TILE_A * TILE_K * 2 * ((SWAP && DUAL) ? 2 : 1);
+  static constexpr int B_ROWS = SWAP ? BN : 256;
+  static constexpr int B_BYTES = B_ROWS * TILE_K * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  // decode-sized stages keep under half of an SM's shared memory, so the CTAs of the next contraction can move
+  // in and prefetch their weights while this one drains; prefill-sized stages take most of it
+  static constexpr int SMEM_BUDGET = (SWAP ? ((BN == 64 && DUAL) ? 124 : 108) : 200) * 1024;
   static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) > 8 ? 8 : (SMEM_BUDGET / STAGE_BYTES);
-  static constexpr int NCOLS = BN * (DUAL ? 2 : 1);
-  static constexpr int TMEM_COLS = NCOLS < 32 ? 32 : NCOLS;
-  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+  static constexpr int MMA_N = SWAP ? BN : 256;                    // N of one tcgen05.mma
+  static constexpr int NCOLS = SWAP ? BN * (DUAL ? 2 : 1) : 256;   // accumulator columns of one tile
+  static constexpr int TMEM_COLS = 2 * NCOLS < 32 ? 32 : 2 * NCOLS;  // two accumulators
+  static constexpr int OUT_COLS = SWAP ? BN : (DUAL ? 128 : 256);  // output columns of one tile
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 512 /*barriers*/;
+};
+
+// One CTA's run of work: segments (tile, K steps [ks0, ks1)) in the order every role walks them.
+struct Segment {
+  int tile, ks0, ks1, part, nparts;
+};
+struct SegmentWalk {
+  const Params& p;
+  long long u, u_end;   // stream-K: unit cursor
+  int tile_cursor;      // whole tiles: next tile
+  __device__ SegmentWalk(const Params& prm) : p(prm) {
+    const long long U = (long long)p.tiles * p.ksteps, G = gridDim.x;
+    u = (long long)blockIdx.x * U / G;
+    u_end = ((long long)blockIdx.x + 1) * U / G;
+    tile_cursor = blockIdx.x;
+  }
+  __device__ bool next(Segment& s) {
+    if (!p.stream_k) {
+      if (tile_cursor >= p.tiles) return false;
+      s.tile = tile_cursor; s.ks0 = 0; s.ks1 = p.ksteps; s.part = 0; s.nparts = 1;
+      tile_cursor += gridDim.x;
+      return true;
+    }
+    if (u >= u_end) return false;
+    const long long K = p.ksteps, U = (long long)p.tiles * K, G = gridDim.x;
+    s.tile = (int)(u / K);
+    s.ks0 = (int)(u % K);
+    long long left = u_end - u;
+    s.ks1 = (int)((K - s.ks0 < left) ? K : s.ks0 + left);
+    u += s.ks1 - s.ks0;
+    // CTAs whose share touches this tile: first .. last
+    long long t0 = (long long)s.tile * K, t1 = t0 + K;
+    int first = (int)(((t0 + 1) * G + U - 1) / U) - 1;
+    int last = (int)((t1 * G + U - 1) / U) - 1;
+    s.part = (int)blockIdx.x - first;
+    s.nparts = last - first + 1;
+    return true;
+  }
 };
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + __expf(-g)) * u; }
 
-template <bool DUAL>
-__device__ __forceinline__ void write_out(const Params& p, int n, int m, float v, float u) {
-  if (m >= p.M || n >= p.N) return;
-  size_t o = (size_t)m * p.ldo + n;
-  if (DUAL) {
-    ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(silu_mul(v, u));
-    return;
+// ---- epilogue of 16 accumulator columns held by one thread (TMEM lane `lane_row` of tile rows a0.., columns c..)
+template <int BN, bool DUAL, bool SWAP>
+__device__ __forceinline__ void store16(const Params& p, int a0, int b0, int lane_row, int c, const float (&v)[16],
+                                        const float (&u)[16]) {
+  if (SWAP) {
+    // lane = feature, columns = tokens
+    const int n = a0 + lane_row;
+    if (n >= p.N) return;
+    const float bias = (!DUAL && p.bias) ? __bfloat162float(p.bias[n]) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int m = b0 + c + j;
+      if (m >= p.M) break;
+      const size_t o = (size_t)m * p.ldo + n;
+      if (DUAL) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(silu_mul(v[j], u[j]));
+      else if (p.epilogue == EPI_RESIDUAL) atomicAdd((float*)p.out + o, v[j] + bias);  // result unused: a fire-and-forget
+                                                                                       // add; one thread owns the element
+      else if (p.out_f32) ((float*)p.out)[o] = v[j] + bias;
+      else ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v[j] + bias);
+    }
+  } else {
+    // lane = token, columns = 16 consecutive features
+    const int m = a0 + lane_row;
+    if (m >= p.M) return;
+    const int n = b0 + c;
+    if (n >= p.N) return;
+    float r[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) r[j] = DUAL ? silu_mul(v[j], u[j]) : v[j];
+    const size_t o = (size_t)m * p.ldo + n;
+    const bool full = n + 16 <= p.N;
+    if (!DUAL && p.bias) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) if (n + j < p.N) r[j] += __bfloat162float(p.bias[n + j]);
+    }
+    if (p.epilogue == EPI_RESIDUAL || p.out_f32) {
+      float* dst = (float*)p.out + o;
+      const bool vec = full && ((((size_t)dst) & 15) == 0);
+      if (vec) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float4 x = make_float4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+          if (p.epilogue == EPI_RESIDUAL) {
+            float4 old = *reinterpret_cast<float4*>(dst + 4 * q);
+            x.x += old.x; x.y += old.y; x.z += old.z; x.w += old.w;
+          }
+          *reinterpret_cast<float4*>(dst + 4 * q) = x;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (n + j < p.N) dst[j] = (p.epilogue == EPI_RESIDUAL ? dst[j] : 0.f) + r[j];
+      }
+    } else {
+      __nv_bfloat16* dst = (__nv_bfloat16*)p.out + o;
+      const bool vec = full && ((((size_t)dst) & 15) == 0);
+      if (vec) {
+        uint4 lo, hi;
+        __nv_bfloat162 t;
+        t = __floats2bfloat162_rn(r[0], r[1]); lo.x = *reinterpret_cast<uint32_t*>(&t);
+        t = __floats2bfloat162_rn(r[2], r[3]); lo.y = *reinterpret_cast<uint32_t*>(&t);
+        t = __floats2bfloat162_rn(r[4], r[5]); lo.z = *reinterpret_cast<uint32_t*>(&t);
+        t = __floats2bfloat162_rn(r[6], r[7]); lo.w = *reinterpret_cast<uint32_t*>(&t);
+        t = __floats2bfloat162_rn(r[8], r[9]); hi.x = *reinterpret_cast<uint32_t*>(&t);
+        t = __floats2bfloat162_rn(r[10], r[11]); hi.y = *reinterpret_cast<uint32_t*>(&t);
+        t = __floats2bfloat162_rn(r[12], r[13]); hi.z = *reinterpret_cast<uint32_t*>(&t);
+        t = __floats2bfloat162_rn(r[14], r[15]); hi.w = *reinterpret_cast<uint32_t*>(&t);
+        *reinterpret_cast<uint4*>(dst) = lo;
+        *reinterpret_cast<uint4*>(dst + 8) = hi;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) if (n + j < p.N) dst[j] = __float2bfloat16_rn(r[j]);
+      }
+    }
   }
-  if (p.bias) v += __bfloat162float(p.bias[n]);
-  if (p.epilogue == EPI_RESIDUAL) atomicAdd((float*)p.out + o, v);  // result unused: a fire-and-forget reduction;
-                                                                   // one CTA owns each element, so the sum is exact
-  else if (p.out_f32) ((float*)p.out)[o] = v;
-  else ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v);
 }
 
-template <int BN, bool DUAL>
-__global__ void __launch_bounds__(128, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const Params p) {
-  using C = Cfg<BN, DUAL>;
+template <int BN, bool DUAL, bool SWAP>
+__global__ void __launch_bounds__(NTHREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
+  using C = Cfg<BN, DUAL, SWAP>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* full = (uint64_t*)(smem + C::STAGES * C::STAGE_BYTES);
   uint64_t* empty = full + C::STAGES;
-  uint64_t* accum_full = empty + C::STAGES;
-  uint32_t* tmem_slot = (uint32_t*)(accum_full + 1);
-  int* flag = (int*)(tmem_slot + 1);
+  uint64_t* tmem_full = empty + C::STAGES;   // [2]
+  uint64_t* tmem_empty = tmem_full + 2;      // [2]
+  uint32_t* tmem_slot = (uint32_t*)(tmem_empty + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  int* last_flag = (int*)(tmem_slot + 2);
+  volatile int* seg_ok = (volatile int*)(tmem_slot + 3);  // [2]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * TILE_N;
-  const int m0 = blockIdx.y * BN;
-  const int split = blockIdx.z;
-  const int total_ksteps = (p.K + TILE_K - 1) / TILE_K;
-  const int ks_begin = split * p.ksteps_per_split;
-  int ks_end = ks_begin + p.ksteps_per_split;
-  if (ks_end > total_ksteps) ks_end = total_ksteps;
-  const int nk = ks_end - ks_begin;
-
   pdl_trigger();
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(accum_full, 1);
-    *flag = 0;
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    *last_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -221,145 +341,183 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  bool ok = true;
+
+  // rows of the two operands in global memory for a tile: the 128-row operand (A) and the column operand (B)
+  auto tile_origin = [&](int tile, int& a0, int& b0) {
+    a0 = (tile % p.tiles_a) * TILE_A;
+    b0 = (tile / p.tiles_a) * C::OUT_COLS;
+  };
+  // weights and activations of one stage: which is which depends on the orientation
+  auto load_weights = [&](uint8_t* st, uint64_t* bar, int a0, int b0, int kc) {
+    if (SWAP) {
+      tma_load_2d(st, &tmA, bar, kc, a0);
+      if (DUAL) tma_load_2d(st + TILE_A * TILE_K * 2, &tmA, bar, kc, p.N + a0);
+    } else {
+      tma_load_2d(st + C::A_BYTES, &tmB, bar, kc, b0);
+      tma_load_2d(st + C::A_BYTES + 128 * TILE_K * 2, &tmB, bar, kc, DUAL ? p.N + b0 : b0 + 128);
+    }
+  };
+  auto load_activations = [&](uint8_t* st, uint64_t* bar, int a0, int b0, int kc) {
+    if (SWAP) tma_load_2d(st + C::A_BYTES, &tmB, bar, kc, b0);
+    else tma_load_2d(st, &tmA, bar, kc, a0);
+  };
 
   if (warp == 0 && lane == 0) {
-    // ------------------------------------------------ producer: TMA loads into the stage ring
-    // Weights are never written by a kernel, so the first ring of weight tiles is requested before waiting
-    // for the predecessor; activations only after it.
-    const int pre = nk < C::STAGES ? nk : C::STAGES;
-    for (int i = 0; i < pre; ++i) {
-      uint8_t* st = smem + i * C::STAGE_BYTES;
-      mbar_expect_tx(&full[i], C::STAGE_BYTES);
-      int kc = (ks_begin + i) * TILE_K;
-      tma_load_2d(st, &tmW, &full[i], kc, n0);
-      if (DUAL) tma_load_2d(st + TILE_N * TILE_K * 2, &tmW, &full[i], kc, p.N + n0);
+    // ------------------------------------------------ producer
+    // the first ring of weight tiles is requested before waiting for the predecessor kernel
+    {
+      SegmentWalk pre(p);
+      Segment s;
+      int it = 0;
+      while (it < C::STAGES && pre.next(s)) {
+        int a0, b0;
+        tile_origin(s.tile, a0, b0);
+        for (int ks = s.ks0; ks < s.ks1 && it < C::STAGES; ++ks, ++it) {
+          mbar_expect_tx(&full[it], C::STAGE_BYTES);
+          load_weights(smem + it * C::STAGE_BYTES, &full[it], a0, b0, ks * TILE_K);
+        }
+      }
     }
     pdl_wait();
-    for (int i = 0; i < pre; ++i)
-      tma_load_2d(smem + i * C::STAGE_BYTES + C::W_BYTES, &tmX, &full[i], (ks_begin + i) * TILE_K, m0);
-    for (int i = pre; i < nk; ++i) {
-      int s = i % C::STAGES;
-      uint32_t ph = (i / C::STAGES) & 1;
-      if (!mbar_wait(&empty[s], ph ^ 1, p.err)) { ok = false; break; }
-      uint8_t* st = smem + s * C::STAGE_BYTES;
-      mbar_expect_tx(&full[s], C::STAGE_BYTES);
-      int kc = (ks_begin + i) * TILE_K;
-      tma_load_2d(st, &tmW, &full[s], kc, n0);
-      if (DUAL) tma_load_2d(st + TILE_N * TILE_K * 2, &tmW, &full[s], kc, p.N + n0);
-      tma_load_2d(st + C::W_BYTES, &tmX, &full[s], kc, m0);
+    SegmentWalk walk(p);
+    Segment s;
+    int it = 0;
+    bool ok = true;
+    while (ok && walk.next(s)) {
+      int a0, b0;
+      tile_origin(s.tile, a0, b0);
+      for (int ks = s.ks0; ks < s.ks1; ++ks, ++it) {
+        const int st = it % C::STAGES;
+        uint8_t* sp = smem + st * C::STAGE_BYTES;
+        if (it >= C::STAGES) {
+          if (!mbar_wait(&empty[st], ((it / C::STAGES) & 1) ^ 1, p.err, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(&full[st], C::STAGE_BYTES);
+          load_weights(sp, &full[st], a0, b0, ks * TILE_K);
+        }
+        load_activations(sp, &full[st], a0, b0, ks * TILE_K);
+      }
     }
   } else if (warp == 1 && lane == 0) {
-    pdl_wait();
     // ------------------------------------------------ MMA issuer
-    constexpr uint32_t idesc = instr_desc(BN);
-    for (int i = 0; i < nk; ++i) {
-      int s = i % C::STAGES;
-      uint32_t ph = (i / C::STAGES) & 1;
-      if (!mbar_wait(&full[s], ph, p.err)) { ok = false; break; }
-      tc_fence_after();
-      uint32_t wa = smem_u32(smem + s * C::STAGE_BYTES);
-      uint64_t adesc = smem_desc(wa);
-      uint64_t adesc2 = smem_desc(wa + TILE_N * TILE_K * 2);
-      uint64_t bdesc = smem_desc(wa + C::W_BYTES);
-#pragma unroll
-      for (int k = 0; k < TILE_K / UMMA_K; ++k) {
-        uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
-        uint64_t koff = (uint64_t)(k * UMMA_K * 2 >> 4);
-        umma_bf16(tmem_base, adesc + koff, bdesc + koff, idesc, acc);
-        if (DUAL) umma_bf16(tmem_base + BN, adesc2 + koff, bdesc + koff, idesc, acc);
-      }
-      umma_commit(&empty[s]);
-    }
-    umma_commit(accum_full);
-  } else {
     pdl_wait();
+    constexpr uint32_t idesc = instr_desc(C::MMA_N);
+    SegmentWalk walk(p);
+    Segment s;
+    int it = 0, seg = 0;
+    bool ok = true;
+    while (ok && walk.next(s)) {
+      const int buf = seg & 1;
+      if (!mbar_wait(&tmem_empty[buf], ((seg >> 1) & 1) ^ 1, p.err, abort_flag)) break;
+      tc_fence_after();
+      const uint32_t acc = tmem_base + buf * C::NCOLS;
+      for (int ks = s.ks0; ks < s.ks1; ++ks, ++it) {
+        const int st = it % C::STAGES;
+        if (!mbar_wait(&full[st], (it / C::STAGES) & 1, p.err, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + st * C::STAGE_BYTES);
+        const uint64_t adesc = smem_desc(sa);
+        const uint64_t adesc2 = smem_desc(sa + TILE_A * TILE_K * 2);
+        const uint64_t bdesc = smem_desc(sa + C::A_BYTES);
+#pragma unroll
+        for (int k = 0; k < TILE_K / UMMA_K; ++k) {
+          const uint32_t accumulate = (ks > s.ks0 || k > 0) ? 1u : 0u;
+          const uint64_t koff = (uint64_t)(k * UMMA_K * 2 >> 4);
+          umma_bf16(acc, adesc + koff, bdesc + koff, idesc, accumulate);
+          if (SWAP && DUAL) umma_bf16(acc + BN, adesc2 + koff, bdesc + koff, idesc, accumulate);
+        }
+        umma_commit(&empty[st]);
+      }
+      if (ok) umma_commit(&tmem_full[buf]);
+      ++seg;
+    }
+  } else if (warp >= 2) {
+    // ------------------------------------------------ epilogue: four warps, one TMEM lane per thread
+    pdl_wait();
+    const int quarter = warp & 3;               // the TMEM lanes this warp may read
+    const int lane_row = quarter * 32 + lane;   // row of the 128-row operand
+    const int eidx = (warp - 2) * 32 + lane;    // 0..127 among the epilogue threads
+    SegmentWalk walk(p);
+    Segment s;
+    int seg = 0;
+    while (walk.next(s)) {
+      const int buf = seg & 1;
+      // one thread waits and tells the others, so all 128 leave the loop together (they share named barriers)
+      if (eidx == 0) seg_ok[buf] = mbar_wait(&tmem_full[buf], (seg >> 1) & 1, p.err, abort_flag) ? 1 : 0;
+      epilogue_sync();
+      if (!seg_ok[buf]) break;
+      tc_fence_after();
+      int a0, b0;
+      tile_origin(s.tile, a0, b0);
+      const uint32_t acc = tmem_base + buf * C::NCOLS + ((uint32_t)(quarter * 32) << 16);
+      if (s.nparts == 1) {
+#pragma unroll 1
+        for (int c = 0; c < C::OUT_COLS; c += 16) {
+          float v[16], u[16];
+          tmem_ld16(acc + c, v);
+          if (DUAL) tmem_ld16(acc + (SWAP ? BN : 128) + c, u);
+          store16<BN, DUAL, SWAP>(p, a0, b0, lane_row, c, v, u);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+      } else {
+        // a part of a tile: park it in the workspace, [tile][part][column][lane]
+        float* ws = p.workspace + ((size_t)s.tile * p.max_parts + s.part) * C::NCOLS * TILE_A;
+#pragma unroll 1
+        for (int c = 0; c < C::NCOLS; c += 16) {
+          float v[16];
+          tmem_ld16(acc + c, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) ws[(size_t)(c + j) * TILE_A + lane_row] = v[j];
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[buf]);  // the accumulator is free while the parts are added
+        __threadfence();
+        epilogue_sync();
+        if (eidx == 0) *last_flag = (atomicAdd(&p.counters[s.tile], 1) == s.nparts - 1) ? 1 : 0;
+        epilogue_sync();
+        const bool last = *last_flag != 0;
+        epilogue_sync();  // everyone has read the flag before a later segment rewrites it
+        if (last) {
+          __threadfence();
+          const float* base = p.workspace + (size_t)s.tile * p.max_parts * C::NCOLS * TILE_A + lane_row;
+#pragma unroll 1
+          for (int c = 0; c < C::OUT_COLS; c += 16) {
+            float v[16], u[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = u[j] = 0.f;
+            // parts in K order: the sum does not depend on who arrived last; two parts' loads in flight at once
+            for (int q0 = 0; q0 < s.nparts; q0 += 2) {
+              float a[2][16], b[2][16];
+#pragma unroll
+              for (int qq = 0; qq < 2; ++qq) {
+                const bool live = q0 + qq < s.nparts;
+                const float* part = base + (size_t)(q0 + qq) * C::NCOLS * TILE_A;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  a[qq][j] = live ? __ldcg(part + (size_t)(c + j) * TILE_A) : 0.f;
+                  if (DUAL) b[qq][j] = live ? __ldcg(part + (size_t)((SWAP ? BN : 128) + c + j) * TILE_A) : 0.f;
+                }
+              }
+#pragma unroll
+              for (int qq = 0; qq < 2; ++qq)
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  v[j] += a[qq][j];
+                  if (DUAL) u[j] += b[qq][j];
+                }
+            }
+            store16<BN, DUAL, SWAP>(p, a0, b0, lane_row, c, v, u);
+          }
+          if (eidx == 0) p.counters[s.tile] = 0;  // ready for the next launch
+        }
+      }
+      ++seg;
+    }
   }
   __syncwarp();
-
-  // ---------------------------------------------------- epilogue: all four warps, one TMEM lane per thread
-  if (nk > 0 && !mbar_wait(accum_full, 0, p.err)) ok = false;
-  tc_fence_after();
-  if (!ok) atomicExch(flag, 1);
-  __syncthreads();
-  const bool failed = *flag != 0;
-  const int feature = n0 + warp * 32 + lane;
-  const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-
-  if (!failed) {
-    if (p.splits == 1) {
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 16) {
-        float v[16], u[16];
-        if (nk > 0) {
-          tmem_ld16(lane_addr + c, v);
-          if (DUAL) tmem_ld16(lane_addr + BN + c, u);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = u[j] = 0.f;
-        }
-#pragma unroll
-        for (int j = 0; j < 16; ++j) write_out<DUAL>(p, feature, m0 + c + j, v[j], DUAL ? u[j] : 0.f);
-      }
-    } else {
-      // partial tile -> workspace[tile][split][column][lane]; the last CTA of the tile reduces in split order
-      const int tile = blockIdx.y * gridDim.x + blockIdx.x;
-      float* ws = p.workspace + ((size_t)tile * p.splits + split) * C::NCOLS * TILE_N;
-#pragma unroll 1
-      for (int c = 0; c < C::NCOLS; c += 16) {
-        float v[16];
-        if (nk > 0) tmem_ld16(lane_addr + c, v);
-        else {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = 0.f;
-        }
-#pragma unroll
-        for (int j = 0; j < 16; ++j) ws[(size_t)(c + j) * TILE_N + threadIdx.x] = v[j];
-      }
-      __threadfence();
-      __syncthreads();
-      if (threadIdx.x == 0) {
-        int arrived = atomicAdd(&p.counters[tile], 1);
-        *flag = (arrived == p.splits - 1) ? 2 : 0;
-      }
-      __syncthreads();
-      if (*flag == 2) {
-        __threadfence();
-        const float* base = p.workspace + (size_t)tile * p.splits * C::NCOLS * TILE_N;
-#pragma unroll 1
-        for (int c = 0; c < BN; c += 8) {
-          if (m0 + c >= p.M) break;
-          float v[8], u[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) v[j] = u[j] = 0.f;
-          // split order: the sum does not depend on who arrived last; four splits' loads are in flight at once
-          for (int s0 = 0; s0 < p.splits; s0 += 4) {
-            float a[4][8], b[4][8];
-#pragma unroll
-            for (int ss = 0; ss < 4; ++ss) {
-              const bool live = s0 + ss < p.splits;
-              const float* part = base + (size_t)(s0 + ss) * C::NCOLS * TILE_N + threadIdx.x;
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                a[ss][j] = live ? __ldcg(part + (size_t)(c + j) * TILE_N) : 0.f;
-                if (DUAL) b[ss][j] = live ? __ldcg(part + (size_t)(BN + c + j) * TILE_N) : 0.f;
-              }
-            }
-#pragma unroll
-            for (int ss = 0; ss < 4; ++ss)
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                v[j] += a[ss][j];
-                if (DUAL) u[j] += b[ss][j];
-              }
-          }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) write_out<DUAL>(p, feature, m0 + c + j, v[j], u[j]);
-        }
-        if (threadIdx.x == 0) p.counters[tile] = 0;  // ready for the next launch
-      }
-    }
-  } else {
+  if (*abort_flag) {
     // let copies in flight land before the shared memory is handed to another CTA
     unsigned long long t0 = global_ns();
     while (global_ns() - t0 < 2000000ull) { }
@@ -442,19 +600,20 @@ bool tensor_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_t stride, 
   return true;
 }
 
-template <int BN, bool DUAL>
-int launch_tc(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p, dim3 grid, cudaStream_t stream) {
-  using C = Cfg<BN, DUAL>;
+template <int BN, bool DUAL, bool SWAP>
+int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, int grid, cudaStream_t stream) {
+  using C = Cfg<BN, DUAL, SWAP>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, DUAL, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         C::SMEM);
     if (e != cudaSuccess) {
       cuca_set_error("gemm_tc: cannot reserve %d bytes of shared memory: %s", C::SMEM, cudaGetErrorString(e));
       return 2;
     }
     configured = true;
   }
-  cuca_launch(gemm_tc_kernel<BN, DUAL>, grid, dim3(128), C::SMEM, stream, true, tmW, tmX, p);
+  cuca_launch(gemm_tc_kernel<BN, DUAL, SWAP>, dim3(grid), dim3(NTHREADS), C::SMEM, stream, true, tmA, tmB, p);
   CUCA_CHECK_LAUNCH("gemm_tc");
   return 0;
 }
@@ -469,8 +628,8 @@ CUCA_API int cuca_gemm_tc_supported(const void* A, const void* W, int M, int N, 
   return 1;
 }
 
-// out = epilogue(A[M,K] W[N,K]^T), bf16 operands. workspace/counters: scratch for split-K
-// (ws_bytes of 32-bit partials; n_counters zeroed ints, left zeroed). max_splits <= 1 disables split-K.
+// out = epilogue(A[M,K] W[N,K]^T), bf16 operands. workspace/counters: scratch for tiles split along K
+// (ws_bytes of 32-bit partials; n_counters zeroed ints, left zeroed). max_splits <= 1: whole tiles only.
 CUCA_API int cuca_gemm_tc(const void* A, const void* W, const void* bias, void* out, int out_dtype, int M, int N,
                           int K, int lda, int ldo, int epilogue, void* workspace, size_t ws_bytes, int* counters,
                           int n_counters, int max_splits, int* err, cudaStream_t stream) {
@@ -479,42 +638,53 @@ CUCA_API int cuca_gemm_tc(const void* A, const void* W, const void* bias, void* 
   CUCA_REQUIRE(epilogue != EPI_RESIDUAL || out_dtype == CUCA_F32, "gemm_tc: the residual stream is 32-bit");
   CUCA_REQUIRE(epilogue != EPI_SWIGLU || (bias == nullptr && out_dtype == CUCA_BF16), "gemm_tc: SwiGLU writes bf16, no bias");
   const bool dual = epilogue == EPI_SWIGLU;
-  int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
-  // more, narrower token tiles when the wide ones would leave SMs idle (the weight tile is re-read from L2)
-  while (bn > 64 && ((N + TILE_N - 1) / TILE_N) * ((M + bn - 1) / bn) < device_sms()) bn >>= 1;
-  CUtensorMap tmW, tmX;
-  CUCA_REQUIRE(tensor_map(W, (uint64_t)N * (dual ? 2 : 1), K, K, TILE_N, &tmW), "gemm_tc: weight tensor map failed");
-  CUCA_REQUIRE(tensor_map(A, M, K, lda, bn, &tmX), "gemm_tc: activation tensor map failed");
-  dim3 grid((N + TILE_N - 1) / TILE_N, (M + bn - 1) / bn, 1);
-  const int tiles = grid.x * grid.y;
-  const int ksteps = (K + TILE_K - 1) / TILE_K;
-  int splits = 1;
-  if (workspace && counters && max_splits > 1 && tiles < device_sms() && bn <= 64) {
-    splits = device_sms() / tiles;
-    if (splits > max_splits) splits = max_splits;
-    if (splits > ksteps / 4) splits = ksteps / 4;  // at least four K steps per CTA
-    size_t per_tile = (size_t)(dual ? 2 : 1) * bn * TILE_N * sizeof(float);
-    while (splits > 1 && (per_tile * tiles * splits > ws_bytes)) --splits;
-    if (tiles > n_counters || splits < 1) splits = 1;
+  const bool swap = M <= 64;
+  const int bn = M <= 16 ? 16 : M <= 32 ? 32 : 64;
+  const uint64_t w_rows = (uint64_t)N * (dual ? 2 : 1);
+  CUtensorMap tmA, tmB;
+  if (swap) {
+    CUCA_REQUIRE(tensor_map(W, w_rows, K, K, TILE_A, &tmA), "gemm_tc: weight tensor map failed");
+    CUCA_REQUIRE(tensor_map(A, M, K, lda, bn, &tmB), "gemm_tc: activation tensor map failed");
+  } else {
+    CUCA_REQUIRE(tensor_map(A, M, K, lda, TILE_A, &tmA), "gemm_tc: activation tensor map failed");
+    CUCA_REQUIRE(tensor_map(W, w_rows, K, K, 128, &tmB), "gemm_tc: weight tensor map failed");
   }
   Params p;
   p.out = out; p.bias = (const __nv_bfloat16*)bias; p.workspace = (float*)workspace; p.counters = counters;
   p.err = err; p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.epilogue = epilogue; p.out_f32 = out_dtype == CUCA_F32;
-  p.splits = splits;
-  p.ksteps_per_split = (ksteps + splits - 1) / splits;
-  // every split must own at least one K step
-  while (splits > 1 && (splits - 1) * p.ksteps_per_split >= ksteps) {
-    --splits;
-    p.splits = splits;
-    p.ksteps_per_split = (ksteps + splits - 1) / splits;
+  const int out_cols = swap ? bn : (dual ? 128 : 256);
+  const int ncols = swap ? bn * (dual ? 2 : 1) : 256;
+  p.tiles_a = swap ? (N + TILE_A - 1) / TILE_A : (M + TILE_A - 1) / TILE_A;
+  const int tiles_b = swap ? (M + bn - 1) / bn : (N + out_cols - 1) / out_cols;
+  p.tiles = p.tiles_a * tiles_b;
+  p.ksteps = (K + TILE_K - 1) / TILE_K;
+  const int sms = device_sms();
+  const long long units = (long long)p.tiles * p.ksteps;
+  int grid = p.tiles < sms ? p.tiles : sms;
+  p.stream_k = 0;
+  p.max_parts = 1;
+  if (workspace && counters && max_splits > 1 && p.tiles < 2 * sms && p.tiles <= n_counters && p.ksteps >= 2) {
+    // deal the K steps out evenly; every CTA gets at least two
+    long long g = units / 2 < sms ? units / 2 : sms;
+    if (p.tiles % sms != 0) {     // whole tiles in turn would leave SMs idle
+      long long per = units / g;  // smallest share
+      int parts = (int)((p.ksteps + per - 1) / per) + 1;
+      size_t need = (size_t)p.tiles * parts * ncols * TILE_A * sizeof(float);
+      if (g >= 1 && need <= ws_bytes) {
+        p.stream_k = 1;
+        p.max_parts = parts;
+        grid = (int)g;
+      }
+    }
   }
-  grid.z = splits;
-#define GO(BN_)                                                                  \
-  case BN_:                                                                      \
-    return dual ? launch_tc<BN_, true>(tmW, tmX, p, grid, stream) : launch_tc<BN_, false>(tmW, tmX, p, grid, stream);
-  switch (bn) {
-    GO(16) GO(32) GO(64) GO(128) GO(256)
+#define GO(BN_)                                                                                       \
+  case BN_:                                                                                           \
+    return dual ? launch_tc<BN_, true, true>(tmA, tmB, p, grid, stream)                               \
+                : launch_tc<BN_, false, true>(tmA, tmB, p, grid, stream);
+  if (swap) {
+    switch (bn) { GO(16) GO(32) GO(64) }
   }
 #undef GO
-  return 1;
+  return dual ? launch_tc<256, true, false>(tmA, tmB, p, grid, stream)
+              : launch_tc<256, false, false>(tmA, tmB, p, grid, stream);
 }
