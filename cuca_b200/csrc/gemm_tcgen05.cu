@@ -25,6 +25,7 @@
 #include <mutex>
 #include <unordered_map>
 #include <string.h>
+#include <stdlib.h>
 
 #define EPI_STORE 0
 #define EPI_RESIDUAL 1
@@ -92,6 +93,11 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
       : "memory");
+}
+// Bring a tile of the tensor into L2 without a destination in shared memory.
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int c0, int c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1)
+               : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst)), "r"(ncols)
@@ -165,6 +171,8 @@ struct Params {
   int ksteps;    // K steps per tile
   int stream_k;  // 1: units dealt out evenly; 0: whole tiles in turn
   int max_parts; // workspace slots per tile
+  int l2_ahead;  // weight tiles requested into L2 beyond the ring before the predecessor has finished
+  int late_trigger;  // 1: dependents may move in once this CTA's stream is fully requested; 0: at once
 };
 
 // SWAP: weight rows on the 128 lanes, BN tokens as columns. Otherwise tokens on the lanes, 256 weight rows
@@ -183,6 +191,9 @@ struct Cfg {
   static constexpr int NCOLS = SWAP ? BN * (DUAL ? 2 : 1) : 256;   // accumulator columns of one tile
   static constexpr int TMEM_COLS = 2 * NCOLS < 32 ? 32 : 2 * NCOLS;  // two accumulators
   static constexpr int OUT_COLS = SWAP ? BN : (DUAL ? 128 : 256);  // output columns of one tile
+  // weight tiles requested into L2 beyond the shared-memory ring before the predecessor has finished (decode
+  // only): about what the memory system delivers while the predecessor drains and reduces its partial tiles
+  static constexpr int L2_AHEAD = SWAP ? (1024 * 1024) / A_BYTES : 0;  // upper bound of Params::l2_ahead
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 512 /*barriers*/;
 };
 
@@ -319,7 +330,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   volatile int* seg_ok = (volatile int*)(tmem_slot + 3);  // [2]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  pdl_trigger();
+  // With late_trigger the producer and MMA threads call pdl_trigger() only when their stream is fully requested,
+  // so the next kernel's CTAs move in (and request their own weights) while this kernel drains, not while it
+  // still streams; everyone else calls it now.
+  if (!p.late_trigger || !((warp == 0 || warp == 1) && lane == 0)) pdl_trigger();
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(&full[s], 1);
@@ -357,6 +371,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tma_load_2d(st + C::A_BYTES + 128 * TILE_K * 2, &tmB, bar, kc, DUAL ? p.N + b0 : b0 + 128);
     }
   };
+  auto prefetch_weights = [&](int a0, int b0, int kc) {
+    if (SWAP) {
+      tma_prefetch_2d(&tmA, kc, a0);
+      if (DUAL) tma_prefetch_2d(&tmA, kc, p.N + a0);
+    } else {
+      tma_prefetch_2d(&tmB, kc, b0);
+      tma_prefetch_2d(&tmB, kc, DUAL ? p.N + b0 : b0 + 128);
+    }
+  };
   auto load_activations = [&](uint8_t* st, uint64_t* bar, int a0, int b0, int kc) {
     if (SWAP) tma_load_2d(st + C::A_BYTES, &tmB, bar, kc, b0);
     else tma_load_2d(st, &tmA, bar, kc, a0);
@@ -369,12 +392,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       SegmentWalk pre(p);
       Segment s;
       int it = 0;
-      while (it < C::STAGES && pre.next(s)) {
+      const int ahead = C::STAGES + (p.l2_ahead < C::L2_AHEAD ? p.l2_ahead : C::L2_AHEAD);
+      while (it < ahead && pre.next(s)) {
         int a0, b0;
         tile_origin(s.tile, a0, b0);
-        for (int ks = s.ks0; ks < s.ks1 && it < C::STAGES; ++ks, ++it) {
-          mbar_expect_tx(&full[it], C::STAGE_BYTES);
-          load_weights(smem + it * C::STAGE_BYTES, &full[it], a0, b0, ks * TILE_K);
+        for (int ks = s.ks0; ks < s.ks1 && it < ahead; ++ks, ++it) {
+          if (it < C::STAGES) {
+            mbar_expect_tx(&full[it], C::STAGE_BYTES);
+            load_weights(smem + it * C::STAGE_BYTES, &full[it], a0, b0, ks * TILE_K);
+          } else {
+            prefetch_weights(a0, b0, ks * TILE_K);  // beyond the ring: into L2
+          }
         }
       }
     }
@@ -397,6 +425,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         load_activations(sp, &full[st], a0, b0, ks * TILE_K);
       }
     }
+    if (p.late_trigger) pdl_trigger();
   } else if (warp == 1 && lane == 0) {
     // ------------------------------------------------ MMA issuer
     pdl_wait();
@@ -430,6 +459,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (ok) umma_commit(&tmem_full[buf]);
       ++seg;
     }
+    if (p.late_trigger) pdl_trigger();
   } else if (warp >= 2) {
     // ------------------------------------------------ epilogue: four warps, one TMEM lane per thread
     pdl_wait();
@@ -658,22 +688,40 @@ CUCA_API int cuca_gemm_tc(const void* A, const void* W, const void* bias, void* 
   const int tiles_b = swap ? (M + bn - 1) / bn : (N + out_cols - 1) / out_cols;
   p.tiles = p.tiles_a * tiles_b;
   p.ksteps = (K + TILE_K - 1) / TILE_K;
+  static int env_l2 = -1, env_late = -1;
+  if (env_l2 < 0) {
+    const char* e = getenv("CUCA_GEMM_L2_AHEAD");
+    env_l2 = e ? atoi(e) : 0;
+    e = getenv("CUCA_GEMM_LATE_TRIGGER");
+    env_late = e ? atoi(e) : 0;
+  }
+  p.l2_ahead = env_l2;
+  p.late_trigger = env_late;
   const int sms = device_sms();
   const long long units = (long long)p.tiles * p.ksteps;
   int grid = p.tiles < sms ? p.tiles : sms;
   p.stream_k = 0;
   p.max_parts = 1;
-  if (workspace && counters && max_splits > 1 && p.tiles < 2 * sms && p.tiles <= n_counters && p.ksteps >= 2) {
-    // deal the K steps out evenly; every CTA gets at least two
+  if (workspace && counters && max_splits > 1 && p.tiles < 2 * sms && p.tiles <= n_counters && p.ksteps >= 2 &&
+      p.tiles % sms != 0) {  // whole tiles in turn would leave SMs idle
+    // Deal the K steps out. If a whole number of CTAs per tile fills most of the GPU, every CTA gets one even
+    // slice of one tile (one accumulator drain each); else the units are dealt out evenly across tile borders.
     long long g = units / 2 < sms ? units / 2 : sms;
-    if (p.tiles % sms != 0) {     // whole tiles in turn would leave SMs idle
-      long long per = units / g;  // smallest share
-      int parts = (int)((p.ksteps + per - 1) / per) + 1;
-      size_t need = (size_t)p.tiles * parts * ncols * TILE_A * sizeof(float);
-      if (g >= 1 && need <= ws_bytes) {
-        p.stream_k = 1;
-        p.max_parts = parts;
-        grid = (int)g;
+    const int per_tile = sms / p.tiles;  // CTAs per tile if slices stay inside tiles
+    if (per_tile >= 1 && (long long)per_tile * p.tiles * 4 >= 3LL * sms && p.ksteps >= 2 * per_tile)
+      g = (long long)per_tile * p.tiles;
+    if (g > p.tiles || swap) {
+      if (g == p.tiles) {
+        grid = p.tiles;  // one CTA per tile, nothing to add up
+      } else {
+        long long per = units / g;  // smallest share
+        int parts = (int)((p.ksteps + per - 1) / per) + 1;
+        size_t need = (size_t)p.tiles * parts * ncols * TILE_A * sizeof(float);
+        if (g >= 1 && need <= ws_bytes) {
+          p.stream_k = 1;
+          p.max_parts = parts;
+          grid = (int)g;
+        }
       }
     }
   }
