@@ -146,7 +146,7 @@ def main() -> int:
     layers = cfg["num_hidden_layers"]
     pk = peaks()
     max_batch = args.batch if args.no_points else max(64, args.batch)
-    per_request = PROMPT + 2 * (args.steps + args.warmup) + 64
+    per_request = PROMPT + 2 * (args.steps + args.warmup) + 64 + 2 * (-(-max(64, args.batch) * PROMPT // PREFILL_TOKENS))
     kv_tokens = max(CONTEXT + 16, max_batch * (-(-per_request // 16) * 16) + PREFILL_TOKENS + 64)
     t0 = time.perf_counter()
     model = LocalModel.load(LocalModelConfig(
@@ -194,10 +194,19 @@ def main() -> int:
 
     # ------------------------------------------------------------ decode, device only: K captured steps
     def decode_device(batch, steps, warmup):
-        seqs = [sched.submit(Request(p, max_tokens=2 * (steps + warmup) + 8, temperature=0.0))
+        # requests that finish their prompt early decode while the others are still being prefilled: give every
+        # request room for that, and never spin if the scheduler stops making progress
+        turns_needed = -(-batch * PROMPT // sched.cfg.max_step_tokens) + 2
+        seqs = [sched.submit(Request(p, max_tokens=2 * (steps + warmup) + turns_needed + 8, temperature=0.0))
                 for p in prompts(batch, PROMPT)]
-        while any(s.phase != DECODE for s in seqs):
-            sched.turn()
+        for _ in range(4 * turns_needed + 16):
+            if all(s.phase == DECODE for s in seqs):
+                break
+            if sched.turn() == 0:
+                break
+        if not all(s.phase == DECODE for s in seqs):
+            raise RuntimeError("bench: the prompts did not all reach the decode phase: "
+                               + ", ".join(sorted({s.phase for s in seqs})))
         tokens = [s.pending for s in seqs]
         hist = backend.burst(seqs, tokens, warmup)
         tokens = hist[-1].tolist()
@@ -235,16 +244,20 @@ def main() -> int:
     launches_per_step = getattr(g8, "launches", 0)
 
     # ------------------------------------------------------------ decode, end to end through generate()
+    # Requests whose prompt is done decode while later prompts are still prefilled; the clock runs on the LAST
+    # request's tokens, which are all produced by steps that decode the whole batch, and every request gets
+    # enough tokens to still be running then.
     stamps = []
+    turns = -(-args.batch * PROMPT // sched.cfg.max_step_tokens) + 2
+    last_id = sched._next_id + args.batch - 1
 
     def on_token(seq, tok):
-        if seq.id == first_id[0]:
+        if seq.id == last_id:
             stamps.append(time.perf_counter())
 
-    first_id = [sched._next_id]
     ps = prompts(args.batch, PROMPT)
     w = time.perf_counter()
-    model.generate(ps, max_tokens=args.warmup + args.steps + 1, temperature=0.0, on_token=on_token)
+    model.generate(ps, max_tokens=args.warmup + args.steps + 1 + turns, temperature=0.0, on_token=on_token)
     windows.append((w, time.perf_counter()))
     e2e_s = stamps[args.warmup + args.steps] - stamps[args.warmup]
     bucket = g8.bucket

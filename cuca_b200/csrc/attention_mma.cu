@@ -39,6 +39,7 @@ struct AttnParams {
   float scale_log2e;
   int window;
   int chunk;             // decode: key positions per split (multiple of 64); 0: each row divides its own length
+  int slots;             // decode, chunk 0: CTAs the GPU holds at once (for the choice of chunks per row)
   float* part;           // decode: [rows][nh][splits][D + 2] partial (acc, m, l)
   int* counters;         // decode: [rows][nkv], zero before and after
   int* err;
@@ -103,6 +104,7 @@ attn_mma_kernel(const AttnParams p) {
   int row_token[2], row_head[2], row_pos[2];  // per owned MMA row (g, g + 8): token row, query head, position
   bool row_ok[2];
   int dec_row = 0, P = 0, warp_pmax = 0;
+  int n_used = gridDim.x;  // decode: chunks this row really uses
   if (DECODE) {
     dec_row = p.rows ? p.rows[blockIdx.z] : blockIdx.z;
     seq = p.seq_of_row[dec_row];
@@ -110,12 +112,25 @@ attn_mma_kernel(const AttnParams p) {
     P = p.positions[dec_row];
     kvh = blockIdx.y;
     int lo = (p.window > 0 && P - (p.window - 1) > 0) ? P - (p.window - 1) : 0;
-    // chunk 0: every row spreads its own keys evenly (in tiles of 64) over the gridDim.x chunks
+    // chunk 0: every row picks how many of the gridDim.x chunks it uses from its own length, so that the tiles
+    // of 64 keys on the critical path (rounds of CTAs the GPU needs, times tiles per chunk) are fewest, and
+    // spreads its keys evenly over them; the other chunks of the row are empty
     int chunk = p.chunk;
     if (chunk == 0) {
-      int tiles = (P + TILE) / TILE;
-      chunk = ((tiles + (int)gridDim.x - 1) / (int)gridDim.x) * TILE;
+      const int tiles = (P + TILE) / TILE;
+      const int pairs = (int)(gridDim.y * gridDim.z);
+      const int nmax = min((int)gridDim.x, tiles);
+      int best = 1, best_cost = 0x7fffffff;
+      for (int n = 1; n <= nmax; ++n) {
+        int rounds = (pairs * n + p.slots - 1) / p.slots;
+        // a CTA costs about three tiles' time before and after its own tiles; the merge a little more
+        int cost = rounds * ((tiles + n - 1) / n + 3) * 8 + (n > 1 ? 2 : 0);
+        if (cost < best_cost) { best_cost = cost; best = n; }
+      }
+      n_used = best;
+      chunk = ((tiles + best - 1) / best) * TILE;
     }
+    if ((int)blockIdx.x >= n_used) return;
     range_lo = max(lo, (int)blockIdx.x * chunk);
     range_hi = min(P + 1, ((int)blockIdx.x + 1) * chunk);
 #pragma unroll
@@ -228,59 +243,79 @@ attn_mma_kernel(const AttnParams p) {
     const __nv_bfloat16* ks = smem + (size_t)stage * 2 * S::TILE_ELEMS;
     const __nv_bfloat16* vs = ks + S::TILE_ELEMS;
 
-    // decode: this warp owns keys [16 warp, 16 warp + 16) of the tile; prefill: all four sub-tiles
-    const int sub_begin = DECODE ? warp : 0, sub_end = DECODE ? warp + 1 : TILE / 16;
-#pragma unroll 1
-    for (int sub = sub_begin; sub < sub_end; ++sub) {
-      const int kp0 = start + sub * 16;
-      if (kp0 >= range_hi || kp0 + 16 <= range_lo) continue;
-      if (!DECODE && kp0 > warp_pmax) continue;  // every row of this warp lies before these keys (causal)
-      // ---- S = Q K^T for 16 keys: two n-tiles of 8 keys
-      float s[2][4];
+    // decode: this warp owns keys [16 warp, 16 warp + 16) of the tile and updates its softmax per 16 keys;
+    // prefill: every warp takes all 64 keys of the tile in one softmax update
+    constexpr int SUBS = DECODE ? 1 : TILE / 16;   // 16-key groups per update
+    constexpr int NT = 2 * SUBS;                    // 8-key n-tiles per update
+    const int sub0 = DECODE ? warp : 0;
+    const int kp0 = start + sub0 * 16;              // first key of this update
+    bool active = kp0 < range_hi && kp0 + 16 * SUBS > range_lo;
+    if (!DECODE && kp0 > warp_pmax) active = false;  // every row of this warp lies before these keys (causal)
+    if (active) {
+      // ---- S = Q K^T
+      float s[NT][4];
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
+      for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int c = 0; c < 4; ++c) s[nt][c] = 0.f;
+      // K steps outermost: consecutive MMAs go to different accumulators, so none waits for the one before it
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
-        uint32_t b[4];
-        int mat = lane >> 3, r = lane & 7;
-        int key = sub * 16 + (mat >> 1) * 8 + r;
-        int dim = kk * 16 + (mat & 1) * 8;
-        ldsm_x4(b, smem_u32(ks + key * S::RS + dim));
-        mma_bf16(s[0], qf[kk], b[0], b[1]);
-        mma_bf16(s[1], qf[kk], b[2], b[3]);
+#pragma unroll
+        for (int sub = 0; sub < SUBS; ++sub) {
+          uint32_t b[4];
+          int mat = lane >> 3, r = lane & 7;
+          int key = (sub0 + sub) * 16 + (mat >> 1) * 8 + r;
+          int dim = kk * 16 + (mat & 1) * 8;
+          ldsm_x4(b, smem_u32(ks + key * S::RS + dim));
+          mma_bf16(s[2 * sub], qf[kk], b[0], b[1]);
+          mma_bf16(s[2 * sub + 1], qf[kk], b[2], b[3]);
+        }
       }
-      // ---- scale, mask, online softmax (per row: g and g + 8)
-      float pmat[2][4];
+      // ---- scale, mask, online softmax (per row: g and g + 8). Tiles that every row of the warp sees whole
+      // (the bulk of a long prompt) skip the per-key tests.
+      bool whole = !DECODE && kp0 >= range_lo && kp0 + 16 * SUBS <= range_hi && kp0 + 16 * SUBS - 1 <= warp_pmax - 15 &&
+                   (p.window <= 0 || kp0 >= warp_pmax - (p.window - 1));
+      uint32_t pa[SUBS][4];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        int lo_row = (p.window > 0 && row_pos[h] - (p.window - 1) > 0) ? row_pos[h] - (p.window - 1) : 0;
         float mx = -INFINITY;
+        if (whole) {
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
+          for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            int kp = kp0 + nt * 8 + 2 * t + e;
-            bool ok = row_ok[h] && kp <= row_pos[h] && kp >= lo_row && kp >= range_lo && kp < range_hi;
-            float v = ok ? s[nt][2 * h + e] * p.scale_log2e : -INFINITY;
-            s[nt][2 * h + e] = v;
-            mx = fmaxf(mx, v);
-          }
+            for (int e = 0; e < 2; ++e) {
+              float v = s[nt][2 * h + e] * p.scale_log2e;
+              s[nt][2 * h + e] = v;
+              mx = fmaxf(mx, v);
+            }
+        } else {
+          int lo_row = (p.window > 0 && row_pos[h] - (p.window - 1) > 0) ? row_pos[h] - (p.window - 1) : 0;
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              int kp = kp0 + nt * 8 + 2 * t + e;
+              bool ok = row_ok[h] && kp <= row_pos[h] && kp >= lo_row && kp >= range_lo && kp < range_hi;
+              float v = ok ? s[nt][2 * h + e] * p.scale_log2e : -INFINITY;
+              s[nt][2 * h + e] = v;
+              mx = fmaxf(mx, v);
+            }
+        }
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
         float m_new = fmaxf(st.m[h], mx);
         float corr = (m_new == -INFINITY) ? 1.f : exp2f(st.m[h] - m_new);
         float sum = 0.f;
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            float v = s[nt][2 * h + e];
-            float pv = (v == -INFINITY) ? 0.f : exp2f(v - m_new);
-            pmat[nt][2 * h + e] = pv;
-            sum += pv;
-          }
+        for (int nt = 0; nt < NT; ++nt) {
+          float v0 = s[nt][2 * h], v1 = s[nt][2 * h + 1];
+          float p0 = (v0 == -INFINITY) ? 0.f : exp2f(v0 - m_new);
+          float p1 = (v1 == -INFINITY) ? 0.f : exp2f(v1 - m_new);
+          sum += p0 + p1;
+          // the accumulator layout of S is the A-operand layout of P: n-tile 2 sub is k 0..7, 2 sub + 1 is k 8..15
+          pa[nt >> 1][(nt & 1) * 2 + h] = pack_bf16(p0, p1);
+        }
         st.l[h] = st.l[h] * corr + sum;
         st.m[h] = m_new;
 #pragma unroll
@@ -289,21 +324,19 @@ attn_mma_kernel(const AttnParams p) {
           st.acc[j][2 * h + 1] *= corr;
         }
       }
-      // ---- O += P V: P is the A operand (16 rows x 16 keys), V tiles are read transposed
-      uint32_t pa[4];
-      pa[0] = pack_bf16(pmat[0][0], pmat[0][1]);
-      pa[1] = pack_bf16(pmat[0][2], pmat[0][3]);
-      pa[2] = pack_bf16(pmat[1][0], pmat[1][1]);
-      pa[3] = pack_bf16(pmat[1][2], pmat[1][3]);
+      // ---- O += P V: P is the A operand (16 rows x 16 keys per step), V tiles are read transposed
 #pragma unroll
-      for (int j = 0; j < D / 8; j += 2) {
-        uint32_t b[4];
-        int mat = lane >> 3, r = lane & 7;
-        int key = sub * 16 + (mat & 1) * 8 + r;
-        int dim = j * 8 + (mat >> 1) * 8;
-        ldsm_x4_trans(b, smem_u32(vs + key * S::RS + dim));
-        mma_bf16(st.acc[j], pa, b[0], b[1]);
-        mma_bf16(st.acc[j + 1], pa, b[2], b[3]);
+      for (int sub = 0; sub < SUBS; ++sub) {
+#pragma unroll
+        for (int j = 0; j < D / 8; j += 2) {
+          uint32_t b[4];
+          int mat = lane >> 3, r = lane & 7;
+          int key = (sub0 + sub) * 16 + (mat & 1) * 8 + r;
+          int dim = j * 8 + (mat >> 1) * 8;
+          ldsm_x4_trans(b, smem_u32(vs + key * S::RS + dim));
+          mma_bf16(st.acc[j], pa[sub], b[0], b[1]);
+          mma_bf16(st.acc[j + 1], pa[sub], b[2], b[3]);
+        }
       }
     }
     if (look_ahead) s_rowoff[ti & 1][threadIdx.x] = next_off;  // read last for tile ti, one iteration ago
@@ -351,7 +384,7 @@ attn_mma_kernel(const AttnParams p) {
     }
   }
   __syncthreads();
-  const int n_splits = gridDim.x;
+  const int n_splits = gridDim.x;  // layout of the scratch; the row uses the first n_used of them
   // scratch and counters are indexed by the ordinal of the decode row in this launch
   float* part_row = p.part + ((size_t)blockIdx.z * p.nh + (size_t)kvh * G) * n_splits * FR;
   for (int idx = threadIdx.x; idx < G * D; idx += NTHREADS) {
@@ -367,7 +400,7 @@ attn_mma_kernel(const AttnParams p) {
       L += src[D + 1] * f;
       O += src[dim] * f;
     }
-    if (n_splits == 1) {
+    if (n_used == 1) {
       p.out[(size_t)dec_row * p.out_stride + (size_t)(kvh * G + item) * D + dim] =
           __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
     } else {
@@ -376,13 +409,13 @@ attn_mma_kernel(const AttnParams p) {
       if (dim == 0) { dst[D] = M; dst[D + 1] = L; }
     }
   }
-  if (n_splits == 1) return;
+  if (n_used == 1) return;
   __threadfence();
   __syncthreads();
   __shared__ int last;
   if (threadIdx.x == 0) {
     int arrived = atomicAdd(&p.counters[blockIdx.z * p.nkv + kvh], 1);
-    last = arrived == n_splits - 1;
+    last = arrived == n_used - 1;
   }
   __syncthreads();
   if (!last) return;
@@ -394,7 +427,7 @@ attn_mma_kernel(const AttnParams p) {
   for (int qd = threadIdx.x; qd < G * MAXS; qd += NTHREADS) {
     int item = qd / MAXS, sidx = qd % MAXS;
     float ms = -INFINITY, ls = 0.f;
-    if (sidx < n_splits) {
+    if (sidx < n_used) {
       const float* src = part_row + ((size_t)item * n_splits + sidx) * FR;
       ms = __ldcg(src + D);
       ls = __ldcg(src + D + 1);
@@ -406,9 +439,9 @@ attn_mma_kernel(const AttnParams p) {
   if (threadIdx.x < G) {
     int item = threadIdx.x;
     float M = -INFINITY;
-    for (int sidx = 0; sidx < n_splits; ++sidx) M = fmaxf(M, s_m[item][sidx]);
+    for (int sidx = 0; sidx < n_used; ++sidx) M = fmaxf(M, s_m[item][sidx]);
     float L = 0.f;
-    for (int sidx = 0; sidx < n_splits; ++sidx) {  // chunk order: independent of which CTA came last
+    for (int sidx = 0; sidx < n_used; ++sidx) {  // chunk order: independent of which CTA came last
       float f = (s_m[item][sidx] == -INFINITY) ? 0.f : exp2f(s_m[item][sidx] - M);
       L += s_f[item][sidx] * f;
       s_f[item][sidx] = f;
@@ -421,7 +454,7 @@ attn_mma_kernel(const AttnParams p) {
     const float* src0 = part_row + (size_t)item * n_splits * FR + dim;
     float v[MAXS];
 #pragma unroll
-    for (int sidx = 0; sidx < MAXS; ++sidx) v[sidx] = sidx < n_splits ? __ldcg(src0 + (size_t)sidx * FR) : 0.f;
+    for (int sidx = 0; sidx < MAXS; ++sidx) v[sidx] = sidx < n_used ? __ldcg(src0 + (size_t)sidx * FR) : 0.f;
     float O = 0.f;
 #pragma unroll
     for (int sidx = 0; sidx < MAXS; ++sidx) O += v[sidx] * s_f[item][sidx];
@@ -490,6 +523,13 @@ CUCA_API int cuca_attention_decode(const void* q, int q_stride, void* out, int o
                                    const int* seq_of_row, const int* tables, int table_stride, const int* rows,
                                    int n_rows, int nh, int nkv, int d, float scale, int window, int chunk,
                                    int n_splits, float* part, int* counters, int* err, cudaStream_t stream) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int smem_cta = 2 * 2 * TILE * (d + 8) * 2 + 2048;
+  int per_sm = (227 * 1024) / smem_cta;
+  if (per_sm < 1) per_sm = 1;
+  if (per_sm > 8) per_sm = 8;
   if (n_rows == 0) return 0;
   CUCA_REQUIRE(cuca_attention_mma_supported(nh, nkv, d, q_stride, out_stride), "attention_decode: unsupported shape "
                "(heads %d/%d, head size %d)", nh, nkv, d);
@@ -503,7 +543,7 @@ CUCA_API int cuca_attention_decode(const void* q, int q_stride, void* out, int o
   p.tables = tables; p.table_stride = table_stride; p.positions = positions; p.seq_of_row = seq_of_row;
   p.rows = rows; p.tile_row0 = nullptr; p.tile_nrows = nullptr; p.nh = nh; p.nkv = nkv;
   p.scale_log2e = scale * 1.4426950408889634f; p.window = window; p.chunk = chunk; p.part = part;
-  p.counters = counters; p.err = err;
+  p.counters = counters; p.err = err; p.slots = sms * per_sm;
   return dispatch<true>(d, p, dim3(n_splits, nkv, n_rows), stream);
 }
 
@@ -524,7 +564,7 @@ CUCA_API int cuca_attention_prefill(const void* q, int q_stride, void* out, int 
   p.tables = tables; p.table_stride = table_stride; p.positions = positions; p.seq_of_row = seq_of_row;
   p.rows = nullptr; p.tile_row0 = tile_row0; p.tile_nrows = tile_nrows; p.nh = nh; p.nkv = nkv;
   p.scale_log2e = scale * 1.4426950408889634f; p.window = window; p.chunk = 0; p.part = nullptr;
-  p.counters = nullptr; p.err = err;
+  p.counters = nullptr; p.err = err; p.slots = 1;
   return dispatch<false>(d, p, dim3(n_tiles, nh), stream);
 }
 

@@ -17,7 +17,7 @@ import torch
 from ..kernels import ops
 from .step import AttentionPlan, StepBatch
 
-LEN_BUCKET = 1024
+LEN_BUCKET = 512
 MAX_HISTORY = 1024
 
 
@@ -45,7 +45,8 @@ class DecodeGraph:
         self.pinned = torch.zeros(3 * bucket, dtype=torch.int32).pin_memory()
         self.pinned_np = self.pinned.numpy()
         nkv = max((g.n_kv_heads for g in core.groups), default=1)
-        chunking = ops.decode_chunking(bucket, nkv, max_len)
+        hd = max((g.head_dim for g in core.groups), default=128)
+        chunking = ops.decode_chunking(bucket, nkv, max_len, hd)
         self.batch = StepBatch(
             n_rows=bucket, n_seqs=bucket, tokens=self.tokens, positions=self.positions,
             seq_of_row=self.slot_of_row, slots=self.slot_of_row, logit_rows=self.logit_rows, n_logit_rows=bucket,

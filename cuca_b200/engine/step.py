@@ -54,11 +54,11 @@ class AttentionPlan:
     n_tiles: int
     fixed_chunking: Optional[tuple] = None  # (chunk, n_splits) frozen for a captured graph
 
-    def chunk(self, n_kv_heads: int):
+    def chunk(self, n_kv_heads: int, head_dim: int = 128):
         if self.fixed_chunking is not None:
             return self.fixed_chunking
         from ..kernels.ops import decode_chunking
-        return decode_chunking(self.n_decode, n_kv_heads, self.max_len)
+        return decode_chunking(self.n_decode, n_kv_heads, self.max_len, head_dim)
 
 
 @dataclass

@@ -171,13 +171,23 @@ def attention_mma_supported(n_heads, n_kv_heads, head_dim, q_stride, out_stride)
     return bool(lib.cuca_attention_mma_supported(n_heads, n_kv_heads, head_dim, q_stride, out_stride))
 
 
-def decode_chunking(n_rows: int, n_kv_heads: int, max_len: int, cta_slots: int = 444):
-    """(chunk, n_splits) of the decode attention. chunk 0: every row spreads its own keys evenly over n_splits
-    chunks; n_splits is what fills the GPU once (three CTAs per SM fit) for this many rows, at most one chunk per
-    tile of 64 keys of the longest row and at most 32."""
+def decode_chunking(n_rows: int, n_kv_heads: int, max_len: int, head_dim: int = 128, sms: int = 148):
+    """(chunk, n_splits) of the decode attention. chunk 0: every row spreads its own keys evenly over the
+    chunks it uses (the kernel repeats this choice per row from the row's own length, never above n_splits).
+    n_splits minimises the time on the critical path in units of one 64-key tile: rounds of CTAs the GPU needs
+    (a CTA holds two stages of a key and a value tile in shared memory) times (tiles per chunk + about three
+    tiles' worth of fixed work per CTA); at most 32 and at most one chunk per tile of the longest row."""
     tiles = max(1, -(-max_len // 64))
-    n_splits = max(1, min(32, tiles, cta_slots // max(1, n_rows * n_kv_heads)))
-    return 0, n_splits
+    smem = 2 * 2 * 64 * (head_dim + 8) * 2 + 2048
+    slots = sms * max(1, min(8, (227 * 1024) // smem))
+    pairs = max(1, n_rows * n_kv_heads)
+    best, best_cost = 1, None
+    for n in range(1, min(32, tiles) + 1):
+        rounds = -(-pairs * n // slots)
+        cost = rounds * (-(-tiles // n) + 3) * 8 + (2 if n > 1 else 0)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = n, cost
+    return 0, best
 
 
 def attention_decode(q, q_stride, out, kpool, vpool, positions, seq_of_row, tables, rows, n_rows, n_heads,
@@ -211,7 +221,7 @@ def attention(qkv, out, cache, step, n_heads, n_kv_heads, head_dim, scale, windo
         if plan.n_decode:
             attention_decode(qkv, qkv.stride(0), out, cache.k, cache.v, step.positions, step.seq_of_row,
                              cache.tables, plan.decode_rows, plan.n_decode, n_heads, n_kv_heads, head_dim, scale,
-                             window, plan.chunk(n_kv_heads)[0], plan.chunk(n_kv_heads)[1], err)
+                             window, plan.chunk(n_kv_heads, head_dim)[0], plan.chunk(n_kv_heads, head_dim)[1], err)
         if plan.n_tiles:
             attention_prefill(qkv, qkv.stride(0), out, cache.k, cache.v, step.positions, step.seq_of_row,
                               cache.tables, plan.tile_row0, plan.tile_nrows, plan.n_tiles, n_heads, n_kv_heads,
