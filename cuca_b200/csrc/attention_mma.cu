@@ -18,6 +18,7 @@
 namespace {
 
 constexpr int TILE = 64;      // keys per shared-memory tile
+constexpr int STAGES = 3;     // tiles in the shared-memory ring: two in flight while one is computed
 constexpr int NTHREADS = 128;
 
 struct AttnParams {
@@ -78,7 +79,7 @@ template <int D>
 struct Smem {
   static constexpr int RS = D + 8;  // row stride in elements: 16 bytes of padding
   static constexpr int TILE_ELEMS = TILE * RS;
-  static constexpr int BYTES = 2 /*stages*/ * 2 /*k, v*/ * TILE_ELEMS * 2;
+  static constexpr int BYTES = STAGES * 2 /*k, v*/ * TILE_ELEMS * 2;
 };
 
 // One warp's state over its 16 MMA rows: thread (g, t) holds rows g and g + 8.
@@ -194,7 +195,7 @@ attn_mma_kernel(const AttnParams p) {
 
   // Row offsets of a tile's 64 keys in the pools (-1: masked or without a page), one tile ahead of the copies:
   // the page-table lookups of tile i + 2 are in flight while tile i is computed, so no copy waits on one.
-  __shared__ long long s_rowoff[2][TILE];
+  __shared__ long long s_rowoff[STAGES][TILE];
   const int bs_shift = __ffs(p.bs) - 1, bs_mask = p.bs - 1;
   auto row_offset = [&](int tile_index) -> long long {
     int kp = (first_tile + tile_index) * TILE + (int)threadIdx.x;
@@ -209,7 +210,7 @@ attn_mma_kernel(const AttnParams p) {
   auto load_tile = [&](int stage, int tile_index) {
     __nv_bfloat16* ks = smem + (size_t)stage * 2 * S::TILE_ELEMS;
     __nv_bfloat16* vs = ks + S::TILE_ELEMS;
-    const long long* ro = s_rowoff[tile_index & 1];
+    const long long* ro = s_rowoff[tile_index % STAGES];
     constexpr int CH = D / 8;  // 16-byte chunks per row
 #pragma unroll
     for (int idx = threadIdx.x; idx < TILE * CH; idx += NTHREADS) {
@@ -222,23 +223,26 @@ attn_mma_kernel(const AttnParams p) {
     }
   };
   if (threadIdx.x < TILE) {
-    if (n_tiles > 0) s_rowoff[0][threadIdx.x] = row_offset(0);
-    if (n_tiles > 1) s_rowoff[1][threadIdx.x] = row_offset(1);
+#pragma unroll
+    for (int i = 0; i < STAGES; ++i)
+      if (i < n_tiles) s_rowoff[i][threadIdx.x] = row_offset(i);
   }
   __syncthreads();
-
-  if (n_tiles > 0) load_tile(0, 0);
-  cp_async_commit();
+#pragma unroll
+  for (int i = 0; i < STAGES - 1; ++i) {
+    if (i < n_tiles) load_tile(i, i);
+    cp_async_commit();
+  }
 
   for (int ti = 0; ti < n_tiles; ++ti) {
-    const int stage = ti & 1;
-    if (ti + 1 < n_tiles) load_tile(stage ^ 1, ti + 1);
+    const int stage = ti % STAGES;
+    if (ti + STAGES - 1 < n_tiles) load_tile((ti + STAGES - 1) % STAGES, ti + STAGES - 1);
     cp_async_commit();
-    cp_async_wait<1>();
+    cp_async_wait<STAGES - 1>();
     __syncthreads();
     long long next_off = -1;
-    const bool look_ahead = threadIdx.x < TILE && ti + 2 < n_tiles;
-    if (look_ahead) next_off = row_offset(ti + 2);
+    const bool look_ahead = threadIdx.x < TILE && ti + STAGES < n_tiles;
+    if (look_ahead) next_off = row_offset(ti + STAGES);
     const int start = (first_tile + ti) * TILE;
     const __nv_bfloat16* ks = smem + (size_t)stage * 2 * S::TILE_ELEMS;
     const __nv_bfloat16* vs = ks + S::TILE_ELEMS;
@@ -339,7 +343,7 @@ attn_mma_kernel(const AttnParams p) {
         }
       }
     }
-    if (look_ahead) s_rowoff[ti & 1][threadIdx.x] = next_off;  // read last for tile ti, one iteration ago
+    if (look_ahead) s_rowoff[ti % STAGES][threadIdx.x] = next_off;  // this slot was last read to request tile ti
     __syncthreads();  // the stage is overwritten by the load issued in the next iteration
   }
   cp_async_wait<0>();
@@ -526,7 +530,7 @@ CUCA_API int cuca_attention_decode(const void* q, int q_stride, void* out, int o
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int smem_cta = 2 * 2 * TILE * (d + 8) * 2 + 2048;
+  const int smem_cta = STAGES * 2 * TILE * (d + 8) * 2 + 2048;
   int per_sm = (227 * 1024) / smem_cta;
   if (per_sm < 1) per_sm = 1;
   if (per_sm > 8) per_sm = 8;

@@ -175,10 +175,10 @@ def decode_chunking(n_rows: int, n_kv_heads: int, max_len: int, head_dim: int = 
     """(chunk, n_splits) of the decode attention. chunk 0: every row spreads its own keys evenly over the
     chunks it uses (the kernel repeats this choice per row from the row's own length, never above n_splits).
     n_splits minimises the time on the critical path in units of one 64-key tile: rounds of CTAs the GPU needs
-    (a CTA holds two stages of a key and a value tile in shared memory) times (tiles per chunk + about three
+    (a CTA holds three stages of a key and a value tile in shared memory) times (tiles per chunk + about three
     tiles' worth of fixed work per CTA); at most 32 and at most one chunk per tile of the longest row."""
     tiles = max(1, -(-max_len // 64))
-    smem = 2 * 2 * 64 * (head_dim + 8) * 2 + 2048
+    smem = 3 * 2 * 64 * (head_dim + 8) * 2 + 2048  # three stages of a key and a value tile
     slots = sms * max(1, min(8, (227 * 1024) // smem))
     pairs = max(1, n_rows * n_kv_heads)
     best, best_cost = 1, None
