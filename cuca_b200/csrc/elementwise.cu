@@ -62,32 +62,85 @@ CUCA_API int cuca_embed(const void* table, int table_dtype, const int* tokens, f
 }
 
 // ---------------------------------------------------------------- RMSNorm
-// One block of 256 threads per output row; the reduction order depends only
-// on E, so a row's result does not depend on what else is in the batch.
-template <typename TW, typename TO>
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
+// One block per output row. Every thread takes four consecutive values at a time and the block is as wide as
+// the row needs (up to 1024 threads), so all loads of a row are in flight together. The reduction order depends
+// only on E, so a row's result does not depend on what else is in the batch.
+static inline int norm_block(int E) {
+  int t = ((E + 3) / 4 + 31) / 32 * 32;
+  return t < 32 ? 32 : (t > 1024 ? 1024 : t);
+}
+
+__device__ __forceinline__ float block_sum_1024(float s, float* red) {
+  s = warp_sum(s);
+  const int nw = (blockDim.x + 31) >> 5;
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  float tot = 0.f;
+  for (int i = 0; i < nw; ++i) tot += red[i];
+  return tot;
+}
+
+// PARTIAL: x[row] += sum over slices first (written back), see below.
+template <typename TW, typename TO, bool PARTIAL>
+__global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ partial, int n_slices,
+                               size_t slice_stride, const TW* __restrict__ w, TO* __restrict__ out,
                                const int* __restrict__ rows, int E, float eps) {
-  __shared__ float red[8];
+  __shared__ float red[32];
   pdl_trigger();
   pdl_wait();
   int orow = blockIdx.x;
   int irow = rows ? rows[orow] : orow;
   if (irow < 0) return;
-  const float* xr = x + (size_t)irow * E;
-  float s = 0.f;
-  for (int i = threadIdx.x; i < E; i += 256) {
-    float v = xr[i];
-    s = fmaf(v, v, s);
-  }
-  s = warp_sum(s);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
-  __syncthreads();
-  float tot = 0.f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) tot += red[i];
-  float r = rsqrtf(tot / (float)E + eps);
+  float* xr = x + (size_t)irow * E;
+  const float* pr = PARTIAL ? partial + (size_t)irow * E : nullptr;
   TO* o = out + (size_t)orow * E;
-  for (int i = threadIdx.x; i < E; i += 256) o[i] = from_f32<TO>(xr[i] * r * to_f32(w[i]));
+  float s = 0.f;
+  const bool vec = (E & 3) == 0 && (((size_t)xr) & 15) == 0 && (!PARTIAL || ((((size_t)pr) | (slice_stride * 4)) & 15) == 0);
+  if (vec) {
+    const int nvec = E >> 2;
+    // at most two rounds for rows up to 8192 wide: keep the values in registers between the two passes
+    float4 keep[2];
+    int kept = 0;
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+      float4 v = reinterpret_cast<const float4*>(xr)[i];
+      if (PARTIAL) {
+        for (int k0 = 0; k0 < n_slices; k0 += 4) {  // four slices' loads in flight at once, added in slice order
+          float4 q[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            q[u] = k0 + u < n_slices ? __ldcg(reinterpret_cast<const float4*>(pr + (k0 + u) * slice_stride) + i)
+                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) { v.x += q[u].x; v.y += q[u].y; v.z += q[u].z; v.w += q[u].w; }
+        }
+        reinterpret_cast<float4*>(xr)[i] = v;
+      }
+      s = fmaf(v.x, v.x, s); s = fmaf(v.y, v.y, s); s = fmaf(v.z, v.z, s); s = fmaf(v.w, v.w, s);
+      if (kept < 2) keep[kept] = v;
+      ++kept;
+    }
+    float r = rsqrtf(block_sum_1024(s, red) / (float)E + eps);
+    int round = 0;
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x, ++round) {
+      float4 v = round < 2 ? keep[round] : reinterpret_cast<const float4*>(xr)[i];
+      const int e = i << 2;
+      o[e] = from_f32<TO>(v.x * r * to_f32(w[e]));
+      o[e + 1] = from_f32<TO>(v.y * r * to_f32(w[e + 1]));
+      o[e + 2] = from_f32<TO>(v.z * r * to_f32(w[e + 2]));
+      o[e + 3] = from_f32<TO>(v.w * r * to_f32(w[e + 3]));
+    }
+  } else {
+    for (int i = threadIdx.x; i < E; i += blockDim.x) {
+      float v = xr[i];
+      if (PARTIAL) {
+        for (int k = 0; k < n_slices; ++k) v += __ldcg(pr + k * slice_stride + i);
+        xr[i] = v;
+      }
+      s = fmaf(v, v, s);
+    }
+    float r = rsqrtf(block_sum_1024(s, red) / (float)E + eps);
+    for (int i = threadIdx.x; i < E; i += blockDim.x) o[i] = from_f32<TO>(xr[i] * r * to_f32(w[i]));
+  }
 }
 
 // out[r] = x[rows ? rows[r] : r] * rsqrt(mean(x^2) + eps) * w
@@ -95,8 +148,10 @@ CUCA_API int cuca_rmsnorm(const float* x, const void* w, int w_dtype, void* out,
                           const int* rows, int n_rows, int E, float eps, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   CUCA_REQUIRE(E > 0, "rmsnorm: bad width %d", E);
-#define LAUNCH(TW, TO) \
-  cuca_launch(rmsnorm_kernel<TW, TO>, dim3(n_rows), dim3(256), 0, stream, true, x, (const TW*)w, (TO*)out, rows, E, eps)
+  float* xm = const_cast<float*>(x);  // not written without PARTIAL
+#define LAUNCH(TW, TO)                                                                                          \
+  cuca_launch(rmsnorm_kernel<TW, TO, false>, dim3(n_rows), dim3(norm_block(E)), 0, stream, true, xm,            \
+              (const float*)nullptr, 0, (size_t)0, (const TW*)w, (TO*)out, rows, E, eps)
   if (w_dtype == CUCA_F32 && out_dtype == CUCA_F32) LAUNCH(float, float);
   else if (w_dtype == CUCA_F32 && out_dtype == CUCA_BF16) LAUNCH(float, __nv_bfloat16);
   else if (w_dtype == CUCA_BF16 && out_dtype == CUCA_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
@@ -238,5 +293,128 @@ CUCA_API int cuca_scatter_int(int* dst, const int* idx, const int* val, int n, l
   if (n == 0) return 0;
   scatter_int_kernel<<<(n + 255) / 256, 256, 0, stream>>>(dst, idx, val, n, limit);
   CUCA_CHECK_LAUNCH("scatter_int");
+  return 0;
+}
+
+// ---------------------------------------------------------------- consumers of partial sums (decode)
+// A contraction over few tokens is cut along K over several CTAs. Instead of adding the slices up itself (a
+// second pass through global memory at the end of a short kernel), it leaves them as [slice][row][feature]
+// 32-bit sums, and the next kernel, which reads every value anyway, adds them in slice order.
+
+// x[row] += sum over slices; out[orow] = RMSNorm(x[row]) * w (the RMSNorm kernel above with PARTIAL).
+CUCA_API int cuca_add_partials_rmsnorm(float* x, const float* partial, int n_slices, size_t slice_stride,
+                                       const float* w, void* out, int out_dtype, const int* rows, int n_rows, int E,
+                                       float eps, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  CUCA_REQUIRE(E > 0 && n_slices >= 1, "add_partials_rmsnorm: bad sizes");
+  if (out_dtype == CUCA_BF16)
+    cuca_launch(rmsnorm_kernel<float, __nv_bfloat16, true>, dim3(n_rows), dim3(norm_block(E)), 0, stream, true, x,
+                partial, n_slices, slice_stride, w, (__nv_bfloat16*)out, rows, E, eps);
+  else if (out_dtype == CUCA_F32)
+    cuca_launch(rmsnorm_kernel<float, float, true>, dim3(n_rows), dim3(norm_block(E)), 0, stream, true, x, partial,
+                n_slices, slice_stride, w, (float*)out, rows, E, eps);
+  else
+    CUCA_REQUIRE(false, "add_partials_rmsnorm: unknown dtype %d", out_dtype);
+  CUCA_CHECK_LAUNCH("add_partials_rmsnorm");
+  return 0;
+}
+
+// x += sum over slices: for a reader of the stream that does not add the slices itself.
+__global__ void add_partials_kernel(float* __restrict__ x, const float* __restrict__ partial, int n_slices,
+                                    size_t slice_stride, size_t total) {
+  pdl_trigger();
+  pdl_wait();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  float v = x[i];
+  for (int k = 0; k < n_slices; ++k) v += __ldcg(partial + k * slice_stride + i);
+  x[i] = v;
+}
+
+CUCA_API int cuca_add_partials(float* x, const float* partial, int n_slices, size_t slice_stride, size_t total,
+                               cudaStream_t stream) {
+  if (total == 0) return 0;
+  cuca_launch(add_partials_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, true, x, partial,
+              n_slices, slice_stride, total);
+  CUCA_CHECK_LAUNCH("add_partials");
+  return 0;
+}
+
+// The q/k/v projection arrives as partial sums [slice][row][(nh + 2 nkv) d]: add them (and the bias), rotate q
+// and k in 32-bit, write q as bf16 to q_out[row][nh d] and k, v to their pages.
+__global__ void rope_store_partial_kernel(const float* __restrict__ partial, int n_slices, size_t slice_stride,
+                                          const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ q_out,
+                                          const int* __restrict__ positions, const int* __restrict__ seq_of_row,
+                                          const int* __restrict__ tables, int table_stride,
+                                          const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                          int table_rows, int rot, __nv_bfloat16* __restrict__ kpool,
+                                          __nv_bfloat16* __restrict__ vpool, int n_blocks, int bs, int nh, int nkv,
+                                          int d, int* err) {
+  pdl_trigger();
+  pdl_wait();
+  int row = blockIdx.x;
+  int head = blockIdx.y;
+  int seq = seq_of_row[row];
+  if (seq < 0) return;
+  int pos = positions[row];
+  const size_t width = (size_t)(nh + 2 * nkv) * d;
+  const float* src = partial + (size_t)row * width + (size_t)head * d;
+  const __nv_bfloat16* b = bias ? bias + (size_t)head * d : nullptr;
+  auto value = [&](int i) {
+    float v = b ? __bfloat162float(b[i]) : 0.f;
+    for (int k0 = 0; k0 < n_slices; k0 += 4) {  // four slices' loads in flight at once, added in slice order
+      float q[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) q[u] = k0 + u < n_slices ? __ldcg(src + (k0 + u) * slice_stride + i) : 0.f;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v += q[u];
+    }
+    return v;
+  };
+  bool is_v = head >= nh + nkv;
+  bool is_k = !is_v && head >= nh;
+  __nv_bfloat16* dst;
+  if (is_k || is_v) {
+    int blk = pos >= 0 ? tables[(size_t)seq * table_stride + pos / bs] : -1;
+    if (blk < 0 || blk >= n_blocks) {
+      if (threadIdx.x == 0 && err) atomicExch(err, CUCA_ERR_BLOCK_RANGE);
+      return;
+    }
+    int kvh = is_k ? head - nh : head - nh - nkv;
+    dst = (is_k ? kpool : vpool) + (((size_t)blk * nkv + kvh) * bs + (pos % bs)) * d;
+  } else {
+    dst = q_out + (size_t)row * nh * d + (size_t)head * d;
+  }
+  if (is_v) {
+    for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = __float2bfloat16_rn(value(i));
+    return;
+  }
+  int half = rot / 2;
+  bool in_table = pos >= 0 && pos < table_rows;
+  if (!in_table && half > 0 && threadIdx.x == 0 && err) atomicExch(err, CUCA_ERR_TOKEN_RANGE);
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float c = in_table ? cos_t[(size_t)pos * half + i] : 1.f;
+    float s = in_table ? sin_t[(size_t)pos * half + i] : 0.f;
+    float a = value(i), bb = value(i + half);
+    dst[i] = __float2bfloat16_rn(a * c - bb * s);
+    dst[i + half] = __float2bfloat16_rn(a * s + bb * c);
+  }
+  for (int i = rot + threadIdx.x; i < d; i += blockDim.x) dst[i] = __float2bfloat16_rn(value(i));
+}
+
+CUCA_API int cuca_rope_store_partial(const float* partial, int n_slices, size_t slice_stride, const void* bias,
+                                     void* q_out, const int* positions, const int* seq_of_row, const int* tables,
+                                     int table_stride, const float* cos_t, const float* sin_t, int table_rows,
+                                     int rot, void* kpool, void* vpool, int n_blocks, int bs, int n_rows, int nh,
+                                     int nkv, int d, int* err, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  CUCA_REQUIRE(rot >= 0 && rot <= d && rot % 2 == 0, "rope_store_partial: rotary size %d does not fit head size %d", rot, d);
+  CUCA_REQUIRE(bs > 0 && nh > 0 && nkv >= 0 && d > 0 && n_slices >= 1, "rope_store_partial: bad sizes");
+  dim3 grid(n_rows, nh + 2 * nkv);
+  int threads = d / 2 >= 64 ? 64 : 32;
+  cuca_launch(rope_store_partial_kernel, grid, dim3(threads), 0, stream, true, partial, n_slices, slice_stride,
+              (const __nv_bfloat16*)bias, (__nv_bfloat16*)q_out, positions, seq_of_row, tables, table_stride, cos_t,
+              sin_t, table_rows, rot, (__nv_bfloat16*)kpool, (__nv_bfloat16*)vpool, n_blocks, bs, nh, nkv, d, err);
+  CUCA_CHECK_LAUNCH("rope_store_partial");
   return 0;
 }

@@ -30,6 +30,7 @@
 #define EPI_STORE 0
 #define EPI_RESIDUAL 1
 #define EPI_SWIGLU 2
+#define EPI_PARTIAL 3  // out = 32-bit [slices][M][N]: every K slice of a tile stores its partial sum, nothing is added up
 
 namespace {
 
@@ -169,7 +170,8 @@ struct Params {
   int tiles_a;   // tiles along the 128-row operand
   int tiles;     // all tiles
   int ksteps;    // K steps per tile
-  int stream_k;  // 1: units dealt out evenly; 0: whole tiles in turn
+  int stream_k;  // 0: whole tiles in turn; 1: units dealt out evenly; 2: per_tile even K slices of every tile
+  int per_tile;  // mode 2: CTAs per tile
   int max_parts; // workspace slots per tile
   int l2_ahead;  // weight tiles requested into L2 beyond the ring before the predecessor has finished
   int late_trigger;  // 1: dependents may move in once this CTA's stream is fully requested; 0: at once
@@ -183,10 +185,13 @@ struct Cfg {
   static constexpr int B_ROWS = SWAP ? BN : 256;
   static constexpr int B_BYTES = B_ROWS * TILE_K * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  // decode-sized stages keep under half of an SM's shared memory, so the CTAs of the next contraction can move
-  // in and prefetch their weights while this one drains; prefill-sized stages take most of it
-  static constexpr int SMEM_BUDGET = (SWAP ? ((BN == 64 && DUAL) ? 124 : 108) : 200) * 1024;
-  static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) > 8 ? 8 : (SMEM_BUDGET / STAGE_BYTES);
+  // deep rings in both orientations: the more weight bytes in flight, the closer the stream runs to the memory's
+  // rate (measured: 200 KB of stages beat 108 KB with room for the next kernel's CTAs)
+#ifndef CUCA_SWAP_SMEM_KB
+#define CUCA_SWAP_SMEM_KB 200
+#endif
+  static constexpr int SMEM_BUDGET = (SWAP ? ((BN == 64 && DUAL && CUCA_SWAP_SMEM_KB < 124) ? 124 : CUCA_SWAP_SMEM_KB) : 200) * 1024;
+  static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) > 12 ? 12 : (SMEM_BUDGET / STAGE_BYTES);
   static constexpr int MMA_N = SWAP ? BN : 256;                    // N of one tcgen05.mma
   static constexpr int NCOLS = SWAP ? BN * (DUAL ? 2 : 1) : 256;   // accumulator columns of one tile
   static constexpr int TMEM_COLS = 2 * NCOLS < 32 ? 32 : 2 * NCOLS;  // two accumulators
@@ -216,6 +221,17 @@ struct SegmentWalk {
       if (tile_cursor >= p.tiles) return false;
       s.tile = tile_cursor; s.ks0 = 0; s.ks1 = p.ksteps; s.part = 0; s.nparts = 1;
       tile_cursor += gridDim.x;
+      return true;
+    }
+    if (p.stream_k == 2) {
+      // one K slice of one tile per CTA
+      if (tile_cursor < 0) return false;
+      s.tile = (int)blockIdx.x / p.per_tile;
+      s.part = (int)blockIdx.x % p.per_tile;
+      s.nparts = p.per_tile;
+      s.ks0 = (int)((long long)s.part * p.ksteps / p.per_tile);
+      s.ks1 = (int)((long long)(s.part + 1) * p.ksteps / p.per_tile);
+      tile_cursor = -1;
       return true;
     }
     if (u >= u_end) return false;
@@ -479,7 +495,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int a0, b0;
       tile_origin(s.tile, a0, b0);
       const uint32_t acc = tmem_base + buf * C::NCOLS + ((uint32_t)(quarter * 32) << 16);
-      if (s.nparts == 1) {
+      if (SWAP && !DUAL && p.epilogue == EPI_PARTIAL) {
+        // this K slice's partial sums go out as they are, [slice][token][feature]; whoever reads them adds them up
+        float* dst = (float*)p.out + (size_t)s.part * p.M * p.ldo;
+        const int n = a0 + lane_row;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+          float v[16];
+          tmem_ld16(acc + c, v);
+          if (n < p.N) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (b0 + c + j < p.M) dst[(size_t)(b0 + c + j) * p.ldo + n] = v[j];
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+      } else if (s.nparts == 1) {
 #pragma unroll 1
         for (int c = 0; c < C::OUT_COLS; c += 16) {
           float v[16], u[16];
@@ -660,15 +693,16 @@ CUCA_API int cuca_gemm_tc_supported(const void* A, const void* W, int M, int N, 
 
 // out = epilogue(A[M,K] W[N,K]^T), bf16 operands. workspace/counters: scratch for tiles split along K
 // (ws_bytes of 32-bit partials; n_counters zeroed ints, left zeroed). max_splits <= 1: whole tiles only.
-CUCA_API int cuca_gemm_tc(const void* A, const void* W, const void* bias, void* out, int out_dtype, int M, int N,
-                          int K, int lda, int ldo, int epilogue, void* workspace, size_t ws_bytes, int* counters,
-                          int n_counters, int max_splits, int* err, cudaStream_t stream) {
+static int gemm_tc_impl(const void* A, const void* W, const void* bias, void* out, int out_dtype, int M, int N,
+                        int K, int lda, int ldo, int epilogue, void* workspace, size_t ws_bytes, int* counters,
+                        int n_counters, int max_splits, int* n_slices_out, int* err, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   if (!cuca_gemm_tc_supported(A, W, M, N, K, lda)) return 1;
   CUCA_REQUIRE(epilogue != EPI_RESIDUAL || out_dtype == CUCA_F32, "gemm_tc: the residual stream is 32-bit");
   CUCA_REQUIRE(epilogue != EPI_SWIGLU || (bias == nullptr && out_dtype == CUCA_BF16), "gemm_tc: SwiGLU writes bf16, no bias");
   const bool dual = epilogue == EPI_SWIGLU;
   const bool swap = M <= 64;
+  CUCA_REQUIRE(epilogue >= 0 && epilogue <= EPI_PARTIAL, "gemm_tc: unknown epilogue %d", epilogue);
   const int bn = M <= 16 ? 16 : M <= 32 ? 32 : 64;
   const uint64_t w_rows = (uint64_t)N * (dual ? 2 : 1);
   CUtensorMap tmA, tmB;
@@ -701,27 +735,46 @@ CUCA_API int cuca_gemm_tc(const void* A, const void* W, const void* bias, void* 
   const long long units = (long long)p.tiles * p.ksteps;
   int grid = p.tiles < sms ? p.tiles : sms;
   p.stream_k = 0;
+  p.per_tile = 1;
   p.max_parts = 1;
-  if (workspace && counters && max_splits > 1 && p.tiles < 2 * sms && p.tiles <= n_counters && p.ksteps >= 2 &&
-      p.tiles % sms != 0) {  // whole tiles in turn would leave SMs idle
-    // Deal the K steps out. If a whole number of CTAs per tile fills most of the GPU, every CTA gets one even
-    // slice of one tile (one accumulator drain each); else the units are dealt out evenly across tile borders.
-    long long g = units / 2 < sms ? units / 2 : sms;
-    const int per_tile = sms / p.tiles;  // CTAs per tile if slices stay inside tiles
-    if (per_tile >= 1 && (long long)per_tile * p.tiles * 4 >= 3LL * sms && p.ksteps >= 2 * per_tile)
-      g = (long long)per_tile * p.tiles;
-    if (g > p.tiles || swap) {
-      if (g == p.tiles) {
+  if (epilogue == EPI_PARTIAL) {
+    CUCA_REQUIRE(swap && out_dtype == CUCA_F32 && bias == nullptr && n_slices_out != nullptr,
+                 "gemm_tc: partial sums are for up to 64 tokens, 32-bit, without bias");
+    int per_tile = sms / p.tiles;
+    if (per_tile > max_splits) per_tile = max_splits;
+    if (per_tile > p.ksteps / 2) per_tile = p.ksteps / 2;
+    if (per_tile < 1) per_tile = 1;
+    if (p.tiles > sms) per_tile = 1;
+    *n_slices_out = per_tile;
+    if (p.tiles <= sms) {
+      p.stream_k = 2;
+      p.per_tile = per_tile;
+      grid = per_tile * p.tiles;
+    }
+  } else if (workspace && counters && max_splits > 1 && p.tiles < 2 * sms && p.tiles <= n_counters &&
+             p.ksteps >= 2 && p.tiles % sms != 0) {  // whole tiles in turn would leave SMs idle
+    // If a whole number of CTAs per tile fills most of the GPU, every CTA gets one even K slice of one tile (one
+    // accumulator drain each); else the K steps are dealt out evenly across tile borders.
+    const int per_tile = sms / p.tiles;
+    if (per_tile >= 1 && (long long)per_tile * p.tiles * 4 >= 3LL * sms && p.ksteps >= 2 * per_tile) {
+      size_t need = (size_t)p.tiles * per_tile * ncols * TILE_A * sizeof(float);
+      if (per_tile == 1) {
         grid = p.tiles;  // one CTA per tile, nothing to add up
-      } else {
-        long long per = units / g;  // smallest share
-        int parts = (int)((p.ksteps + per - 1) / per) + 1;
-        size_t need = (size_t)p.tiles * parts * ncols * TILE_A * sizeof(float);
-        if (g >= 1 && need <= ws_bytes) {
-          p.stream_k = 1;
-          p.max_parts = parts;
-          grid = (int)g;
-        }
+      } else if (need <= ws_bytes) {
+        p.stream_k = 2;
+        p.per_tile = per_tile;
+        p.max_parts = per_tile;
+        grid = per_tile * p.tiles;
+      }
+    } else {
+      long long g = units / 2 < sms ? units / 2 : sms;
+      long long per = units / g;  // smallest share
+      int parts = (int)((p.ksteps + per - 1) / per) + 1;
+      size_t need = (size_t)p.tiles * parts * ncols * TILE_A * sizeof(float);
+      if (g > p.tiles && need <= ws_bytes) {
+        p.stream_k = 1;
+        p.max_parts = parts;
+        grid = (int)g;
       }
     }
   }
@@ -735,4 +788,34 @@ CUCA_API int cuca_gemm_tc(const void* A, const void* W, const void* bias, void* 
 #undef GO
   return dual ? launch_tc<256, true, false>(tmA, tmB, p, grid, stream)
               : launch_tc<256, false, false>(tmA, tmB, p, grid, stream);
+}
+
+CUCA_API int cuca_gemm_tc(const void* A, const void* W, const void* bias, void* out, int out_dtype, int M, int N,
+                          int K, int lda, int ldo, int epilogue, void* workspace, size_t ws_bytes, int* counters,
+                          int n_counters, int max_splits, int* err, cudaStream_t stream) {
+  CUCA_REQUIRE(epilogue != EPI_PARTIAL, "gemm_tc: use cuca_gemm_tc_partial for partial sums");
+  return gemm_tc_impl(A, W, bias, out, out_dtype, M, N, K, lda, ldo, epilogue, workspace, ws_bytes, counters,
+                      n_counters, max_splits, nullptr, err, stream);
+}
+
+// How many K slices cuca_gemm_tc_partial will write for this shape (the first dimension of its output).
+CUCA_API int cuca_gemm_tc_partial_slices(int M, int N, int K, int max_slices) {
+  if (M > 64 || M <= 0 || N <= 0 || K <= 0) return 0;
+  const int sms = device_sms();
+  const int tiles = (N + TILE_A - 1) / TILE_A, ksteps = (K + TILE_K - 1) / TILE_K;
+  int per_tile = sms / tiles;
+  if (per_tile > max_slices) per_tile = max_slices;
+  if (per_tile > ksteps / 2) per_tile = ksteps / 2;
+  if (per_tile < 1 || tiles > sms) per_tile = 1;
+  return per_tile;
+}
+
+// partial[slice][M][N] (32-bit) = A[M, K slice] W[N, K slice]^T for up to 64 tokens: the K slices of a tile are
+// not added up here (no workspace, no counters, no second pass); the kernel that reads the result adds them in
+// slice order. *n_slices gets the number of slices written (cuca_gemm_tc_partial_slices of the same shape).
+CUCA_API int cuca_gemm_tc_partial(const void* A, const void* W, float* partial, int M, int N, int K, int lda,
+                                  int max_slices, int* n_slices, int* err, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  return gemm_tc_impl(A, W, nullptr, partial, CUCA_F32, M, N, K, lda, N, EPI_PARTIAL, nullptr, 0, nullptr, 0,
+                      max_slices, n_slices, err, stream);
 }

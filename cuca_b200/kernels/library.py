@@ -43,6 +43,12 @@ _SIGNATURES = {
                                _P],
     "cuca_decode_advance": [_P, _P, _P, _P, _P, _P, _I, _I, _P],
     "cuca_set_pdl": [_I],
+    "cuca_gemm_tc_partial_slices": [_I, _I, _I, _I],
+    "cuca_gemm_tc_partial": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P],
+    "cuca_add_partials_rmsnorm": [_P, _P, _I, c_size_t, _P, _P, _I, _P, _I, _I, _F, _P],
+    "cuca_add_partials": [_P, _P, _I, c_size_t, c_size_t, _P],
+    "cuca_rope_store_partial": [_P, _I, c_size_t, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I,
+                                _I, _I, _P, _P],
     "cuca_gemm_tc_supported": [_P, _P, _I, _I, _I, _I],
     "cuca_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, c_size_t, _P, _I, _I, _P, _P],
 }

@@ -261,3 +261,69 @@ def decode_advance(tokens, positions, slot_of_row, sampled, history, counter, ma
     lib = library.load()
     library.check(lib.cuca_decode_advance(_p(tokens), _p(positions), _p(slot_of_row), _p(sampled), _p(history),
                                           _p(counter), tokens.shape[0], int(max_steps), _stream()), "decode_advance")
+
+
+# ------------------------------------------------------------------ partial sums (decode)
+class PartialSums:
+    """The result of a contraction over few tokens, left as K slices: `data` is [slices, rows, features] in
+    32-bit; the kernel that reads it adds the slices in order (`add_partials_rmsnorm`, `rope_store_partial`)."""
+
+    __slots__ = ("data", "slices")
+
+    def __init__(self, data, slices):
+        self.data, self.slices = data, slices
+
+    @property
+    def slice_stride(self) -> int:
+        return self.data.stride(0)
+
+
+def gemm_partial_supported(a, w) -> bool:
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[0] <= 64
+            and gemm_tc_supported(a, w))
+
+
+def gemm_partial(a, w, err=None, max_slices=16) -> PartialSums:
+    """a @ w.T for up to 64 rows, as partial sums over K slices (see `PartialSums`)."""
+    _cuda(a, w)
+    lib = library.load()
+    M, K = a.shape
+    N = w.shape[0]
+    slices = lib.cuca_gemm_tc_partial_slices(M, N, K, max_slices)
+    if slices <= 0:
+        raise library.KernelError("gemm_partial: unsupported shape")
+    data = torch.empty(slices, M, N, dtype=torch.float32, device=a.device)
+    import ctypes
+    got = ctypes.c_int(0)
+    library.check(lib.cuca_gemm_tc_partial(_p(a), _p(w), _p(data), M, N, K, a.stride(0), max_slices,
+                                           ctypes.addressof(got), _p(err), _stream()), "gemm_partial")
+    if got.value != slices:
+        raise library.KernelError(f"gemm_partial: {got.value} slices written, {slices} expected")
+    return PartialSums(data, slices)
+
+
+def add_partials_rmsnorm(x, partial: PartialSums, weight, out, eps, rows=None) -> None:
+    """x += sum of the slices (rows named by `rows`, else all); out = RMSNorm(x) * weight."""
+    lib = library.load()
+    n = out.shape[0]
+    library.check(lib.cuca_add_partials_rmsnorm(_p(x), _p(partial.data), partial.slices, partial.slice_stride,
+                                                _p(weight), _p(out), dtype_code(out.dtype), _p(rows), n, x.shape[-1],
+                                                float(eps), _stream()), "add_partials_rmsnorm")
+
+
+def add_partials(x, partial: PartialSums) -> None:
+    lib = library.load()
+    library.check(lib.cuca_add_partials(_p(x), _p(partial.data), partial.slices, partial.slice_stride, x.numel(),
+                                        _stream()), "add_partials")
+
+
+def rope_store_partial(partial: PartialSums, bias, q_out, positions, seq_of_row, tables, cos, sin, rotary_dim, kpool,
+                       vpool, block_size, n_heads, n_kv_heads, head_dim, err) -> None:
+    lib = library.load()
+    n_blocks = kpool.shape[0] if kpool is not None else 0
+    table_rows = cos.shape[0] if cos is not None else 0
+    library.check(lib.cuca_rope_store_partial(
+        _p(partial.data), partial.slices, partial.slice_stride, _p(bias), _p(q_out), _p(positions), _p(seq_of_row),
+        _p(tables), tables.shape[1] if tables is not None else 0, _p(cos), _p(sin), table_rows, int(rotary_dim),
+        _p(kpool), _p(vpool), n_blocks, int(block_size), q_out.shape[0], n_heads, n_kv_heads, head_dim, _p(err),
+        _stream()), "rope_store_partial")

@@ -94,10 +94,14 @@ class Model:
     def forward(self, step, cache) -> torch.Tensor | None:
         """Run the step's rows through the model; logits [wanted rows, vocab] in 32-bit, or None."""
         x = torch.empty(step.n_rows, self.spec.width, dtype=torch.float32, device=self.rt.device)
+        self.rt.pending.clear()
         self.embedding.forward(step.tokens, x)
         for run in self.spec.schedule:
             self.blocks[run.layer].forward(x, step, cache.view(run.cache, step))
         if step.logit_rows is None or step.n_logit_rows == 0:
+            self.rt.pending.clear()
             return None
+        if not getattr(self.final_norm, "consumes_partials", False):
+            self.rt.flush(x)
         h = self.final_norm.forward(x, rows=step.logit_rows)
         return self.head.forward(h)

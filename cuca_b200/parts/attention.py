@@ -86,18 +86,26 @@ class PagedAttention(Mixer):
     def forward(self, h, stream, step, cache) -> None:
         nh, d = self.n_heads, self.head_dim
         nkv = 0 if self.shares_cache else self.n_kv_heads
-        qkv = self.rt.linear(h, self.w_qkv, bias=self.b_qkv)
         fused = self.position.fused_tables() if self.position is not None else None
-        if fused is None:
-            if self.position is not None:
-                self.position.apply(qkv, nh, nkv, d, step.positions)
-            cos = sin = None
-            rot = 0
-        else:
+        kpool, vpool = (None, None) if nkv == 0 else (cache.k, cache.v)
+        if fused is not None and self.rt.use_partials and ops.gemm_partial_supported(h, self.w_qkv):
+            # few tokens: the projection leaves its K slices unadded; rotate-and-store adds them in 32-bit
             cos, sin, rot = fused
-        ops.rope_store(qkv, step.positions, step.seq_of_row, cache.tables, cos, sin, rot,
-                       None if nkv == 0 else cache.k, None if nkv == 0 else cache.v, cache.block_size,
-                       nh, nkv, d, self.rt.err)
+            parts = ops.gemm_partial(h, self.w_qkv, self.rt.err)
+            q = self.rt.empty(h.shape[0], nh * d)
+            ops.rope_store_partial(parts, self.b_qkv, q, step.positions, step.seq_of_row, cache.tables, cos, sin, rot,
+                                   kpool, vpool, cache.block_size, nh, nkv, d, self.rt.err)
+        else:
+            q = self.rt.linear(h, self.w_qkv, bias=self.b_qkv)  # [rows, (nh + 2 nkv) d]; q is the head of each row
+            if fused is None:
+                if self.position is not None:
+                    self.position.apply(q, nh, nkv, d, step.positions)
+                cos = sin = None
+                rot = 0
+            else:
+                cos, sin, rot = fused
+            ops.rope_store(q, step.positions, step.seq_of_row, cache.tables, cos, sin, rot, kpool, vpool,
+                           cache.block_size, nh, nkv, d, self.rt.err)
         attn = self.rt.empty(h.shape[0], nh * d)
-        ops.attention(qkv, attn, cache, step, nh, self.n_kv_heads, d, self.scale, self.window, self.rt.err)
-        self.rt.linear(attn, self.w_o, out=stream, epilogue=ops.EPI_RESIDUAL, bias=self.b_o)
+        ops.attention(q, attn, cache, step, nh, self.n_kv_heads, d, self.scale, self.window, self.rt.err)
+        self.rt.linear_into_stream(attn, self.w_o, stream, bias=self.b_o)

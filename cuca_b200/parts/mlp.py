@@ -37,4 +37,4 @@ class SwiGLU(FeedForward):
 
     def forward(self, h, stream, step) -> None:
         act = self.rt.linear(h, self.w_gate_up, epilogue=ops.EPI_SWIGLU)
-        self.rt.linear(act, self.w_down, out=stream, epilogue=ops.EPI_RESIDUAL)
+        self.rt.linear_into_stream(act, self.w_down, stream)

@@ -25,8 +25,14 @@ class RMSNorm(Norm):
     def weight_bytes(self):
         return self.weight.numel() * self.weight.element_size()
 
+    consumes_partials = True  # adds the K slices a contraction left on the stream while it reads the stream
+
     def forward(self, x, rows=None):
         n = x.shape[0] if rows is None else rows.shape[0]
         out = self.rt.empty(n, self.width)
-        ops.rmsnorm(x, self.weight, out, self.eps, rows)
+        pending = self.rt.take_pending(x)
+        if pending is not None:
+            ops.add_partials_rmsnorm(x, pending, self.weight, out, self.eps, rows)
+        else:
+            ops.rmsnorm(x, self.weight, out, self.eps, rows)
         return out

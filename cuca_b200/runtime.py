@@ -33,6 +33,9 @@ class Runtime:
         library.load()
         torch.cuda.set_device(self.device)
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # residual streams whose last contraction left its K slices unadded (decode): stream address -> PartialSums
+        self.pending: dict = {}
+        self.use_partials = True
 
     # ---------------------------------------------------------------- helpers
     def empty(self, *shape, dtype=None) -> torch.Tensor:
@@ -45,6 +48,27 @@ class Runtime:
             out = self.empty(a.shape[0], n, dtype=out_dtype or self.dtype)
         ops.gemm(a, w, out, epilogue, bias, self.err)
         return out
+
+    # ---------------------------------------------------------------- partial sums on the residual stream
+    def linear_into_stream(self, a, w, stream, bias=None) -> None:
+        """stream += a @ w.T. Over few tokens the contraction is cut along K over the SMs and leaves its slices
+        unadded; the next reader of the stream (a norm) adds them while it reads, which spares the contraction a
+        second pass through memory at its end. `take_pending` / `flush` hand the slices over."""
+        if self.use_partials and bias is None and ops.gemm_partial_supported(a, w):
+            if stream.data_ptr() in self.pending:
+                self.flush(stream)
+            self.pending[stream.data_ptr()] = ops.gemm_partial(a, w, self.err)
+        else:
+            ops.gemm(a, w, stream, ops.EPI_RESIDUAL, bias, self.err)
+
+    def take_pending(self, stream):
+        return self.pending.pop(stream.data_ptr(), None)
+
+    def flush(self, stream) -> None:
+        """Add pending slices into the stream now (for a reader that does not add them itself)."""
+        ps = self.pending.pop(stream.data_ptr(), None)
+        if ps is not None:
+            ops.add_partials(stream, ps)
 
     def check_device_errors(self) -> None:
         """Read the error word (synchronises); raise if a kernel recorded a fault."""

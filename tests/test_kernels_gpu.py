@@ -327,3 +327,72 @@ def test_attention_prefill_mma(dev, nh, nkv, d, bs, window):
                               1.0 / math.sqrt(d), window)
         got = out[r].float().view(nh, d)
         assert torch.allclose(got, want, atol=2e-2, rtol=2e-2), (r, s, pos, float((got - want).abs().max()))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (8, 4096, 4096), (8, 6144, 4096), (3, 96, 96), (17, 331, 120),
+                                   (64, 512, 1024), (40, 2304, 512), (5, 128256 // 8, 256)])
+def test_gemm_partial_sums_and_their_readers(dev, M, N, K):
+    """The decode contraction that leaves its K slices unadded, and the kernels that add them while reading:
+    RMSNorm over the residual stream and rotate-and-store of the q/k/v projection."""
+    from cuca_b200.kernels import ops
+    from cuca_b200.parts.rope import rope_tables
+    g = torch.Generator(device=dev).manual_seed(M + N + K)
+    a = torch.randn(M, K, device=dev, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=dev, generator=g) / math.sqrt(K)).bfloat16()
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    assert ops.gemm_partial_supported(a, w)
+    ps = ops.gemm_partial(a, w, err)
+    assert ps.data.shape == (ps.slices, M, N) and int(err.item()) == 0
+    ref = a.float() @ w.float().T
+    assert torch.allclose(ps.data.sum(0), ref, atol=2e-3, rtol=2e-3)
+    if K >= 1024 and N <= 6144:
+        assert ps.slices > 1  # few tiles, long K: the SMs share the K range
+    # reader 1: x += slices; h = RMSNorm(x)
+    x = torch.randn(M, N, device=dev, generator=g)
+    wn = torch.randn(N, device=dev, generator=g)
+    want_x = x + ref
+    want_h = want_x * torch.rsqrt((want_x * want_x).mean(-1, keepdim=True) + 1e-5) * wn
+    h = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    ops.add_partials_rmsnorm(x, ps, wn, h, 1e-5)
+    assert torch.allclose(x, want_x, atol=2e-3, rtol=2e-3)
+    assert torch.allclose(h.float(), want_h, atol=3e-2, rtol=3e-2)
+    # reader 2: plain add
+    y = torch.zeros(M, N, device=dev)
+    ops.add_partials(y, ps)
+    assert torch.allclose(y, ref, atol=2e-3, rtol=2e-3)
+
+
+def test_rope_store_from_partial_sums(dev):
+    from cuca_b200.kernels import ops
+    from cuca_b200.parts.rope import rope_tables
+    nh, nkv, d, rot, bs, T = 6, 2, 32, 32, 8, 5
+    width = (nh + 2 * nkv) * d
+    cos, sin = rope_tables(64, rot, 10000.0)
+    cos, sin = cos.to(dev), sin.to(dev)
+    slices = torch.randn(3, T, width, device=dev)
+    bias = torch.randn(width, device=dev).bfloat16()
+    total = slices.sum(0) + bias.float()
+    positions = torch.tensor([0, 1, 2, 17, 18], dtype=torch.int32, device=dev)
+    seq = torch.tensor([0, 0, 0, 1, 1], dtype=torch.int32, device=dev)
+    tables = torch.full((2, 8), -1, dtype=torch.int32, device=dev)
+    tables[0, 0], tables[1, 2] = 3, 1
+    kpool = torch.zeros(5, nkv, bs, d, device=dev, dtype=torch.bfloat16)
+    vpool = torch.zeros_like(kpool)
+    q = torch.zeros(T, nh * d, device=dev, dtype=torch.bfloat16)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    ops.rope_store_partial(ops.PartialSums(slices, 3), bias, q, positions, seq, tables, cos, sin, rot, kpool, vpool, bs,
+                           nh, nkv, d, err)
+    assert int(err.item()) == 0
+
+    def rotate(x, p):
+        c, s = cos[p], sin[p]
+        a, b = x[:, :rot // 2], x[:, rot // 2:rot]
+        return torch.cat([a * c - b * s, a * s + b * c, x[:, rot:]], dim=1)
+
+    for r in range(T):
+        p, s = int(positions[r]), int(seq[r])
+        page, off = int(tables[s, p // bs]), p % bs
+        heads = total[r].view(nh + 2 * nkv, d)
+        assert torch.allclose(q[r].float().view(nh, d), rotate(heads[:nh], p), atol=3e-2, rtol=3e-2)
+        assert torch.allclose(kpool[page, :, off].float(), rotate(heads[nh:nh + nkv], p), atol=3e-2, rtol=3e-2)
+        assert torch.allclose(vpool[page, :, off].float(), heads[nh + nkv:], atol=3e-2, rtol=3e-2)
