@@ -74,7 +74,7 @@ class BlockPool:
         self._held = [False] * self.n_blocks
 
 
-@dataclass
+@dataclass(eq=False)  # identity: two requests with equal tables are still two requests
 class SeqBlocks:
     """One request's block tables (one per group) and how many positions it has cached."""
 

@@ -55,7 +55,7 @@ class Request:
     request_id: Optional[str] = None
 
 
-@dataclass
+@dataclass(eq=False)  # identity, not field-by-field equality: requests are looked up in lists every turn
 class Sequence_:
     request: Request
     id: int
@@ -86,7 +86,7 @@ class Sequence_:
         return self.phase == ENDED
 
 
-@dataclass
+@dataclass(eq=False)
 class Plan:
     """One request's share of the coming step."""
 
