@@ -1,0 +1,513 @@
+// Paged causal attention for prompt portions on the 5th-generation tensor cores (bfloat16, head size 128).
+//
+// A CTA takes up to 128 consecutive rows of one request and one query head and walks the request's keys in
+// tiles of 128 positions. Both contractions run as tcgen05.mma with accumulators in tensor memory:
+//
+//   S[128 rows, 128 keys]  = Q K^T        (Q and K tiles K-major in shared memory, loaded by TMA from the
+//                                          q buffer and straight from the pages through the block table)
+//   O[128 rows, head size] += P V         (P written to shared memory by the softmax threads as the K-major
+//                                          A operand; V tiles as loaded, i.e. the MN-major B operand)
+//
+// Warp 0 issues TMA, one thread of warp 1 issues the MMAs, warps 2..5 own one query row per thread (= one
+// TMEM lane): they read S with tcgen05.ld, scale, mask (causal, window), keep the running maximum and sum in
+// 32-bit, rescale O in tensor memory, and hand P back. Softmax and the tensor pipe alternate per tile.
+//
+// Every mbarrier wait is bounded; on a timeout the kernel records CUCA_ERR_WAIT_TIMEOUT, all roles stop, TMEM
+// is freed and the kernel returns.
+#include "common.cuh"
+#include <cuda.h>
+#include <math.h>
+#include <mutex>
+#include <unordered_map>
+
+namespace {
+
+constexpr int D = 128;        // head size
+constexpr int ROWS = 128;     // query rows per CTA = TMEM lanes
+constexpr int KEYS = 128;     // keys per tile
+constexpr int KV_STAGES = 2;
+constexpr int HALF_BYTES = 128 * 128;            // one [128 rows][64 elements] swizzled block: 16 KB
+constexpr int TILE_BYTES = 2 * HALF_BYTES;       // [2 halves of 64 columns][128 rows][128 B]
+constexpr int NTHREADS = 192;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+struct Params {
+  __nv_bfloat16* out;
+  int out_stride;
+  const int* tables;
+  int table_stride;
+  const int* positions;
+  const int* seq_of_row;
+  const int* tile_row0;
+  const int* tile_nrows;
+  int n_blocks, bs, nh, nkv;
+  float scale_log2e;
+  int window;
+  int* err;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, volatile int* abort) {
+  if (mbar_try_wait(bar, parity)) return true;
+  unsigned long long t0 = global_ns();
+  unsigned spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 63u) == 0) {
+      if (*abort) return false;
+      if (global_ns() - t0 > WAIT_LIMIT_NS) {
+        if (err) atomicExch(err, CUCA_ERR_WAIT_TIMEOUT);
+        *abort = 1;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void softmax_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr),
+        "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+}
+__device__ __forceinline__ float fast_exp2(float x) {  // ex2.approx: exp2(-inf) = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// as tmem_ld32 without the wait: several loads can be in flight before one tmem_ld_wait()
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile: rows of 128 bytes (64 bf16), 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// MN-major operand tile (the V tile as loaded: one key per 128-byte row of 64 head dimensions): 64 elements
+// of N contiguous, the next 64 at `lbo` bytes, 8-key groups `sbo` bytes apart.
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// bf16 x bf16 -> f32, M = 128, N = 128; b_mn: the B operand is MN-major
+__host__ __device__ constexpr uint32_t instr_desc(bool b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(128 >> 3) << 17) |
+         ((uint32_t)(128 >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+               const __grid_constant__ CUtensorMap tmV, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* q_s = smem;                                  // Q tile, 32 KB
+  uint8_t* p_s = smem + TILE_BYTES;                     // P tile, 32 KB
+  uint8_t* kv_s = smem + 2 * TILE_BYTES;                // KV_STAGES x (K tile + V tile)
+  uint64_t* bars = (uint64_t*)(kv_s + KV_STAGES * 2 * TILE_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;              // [KV_STAGES]
+  uint64_t* kv_empty = kv_full + KV_STAGES;  // [KV_STAGES]
+  uint64_t* s_full = kv_empty + KV_STAGES;   // S is in tensor memory
+  uint64_t* p_full = s_full + 1;             // P is in shared memory and O is rescaled (128 arrivals)
+  uint64_t* pv_done = p_full + 1;            // the P V contraction of a tile has finished
+  uint32_t* tmem_slot = (uint32_t*)(pv_done + 1);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_trigger();
+  pdl_wait();
+  const int tile = blockIdx.x, head = blockIdx.y;
+  const int row0 = p.tile_row0[tile], n_rows = p.tile_nrows[tile];
+  const int seq = p.seq_of_row[row0];
+  if (seq < 0) return;
+  const int pos0 = p.positions[row0];
+  const int kvh = head / (p.nh / p.nkv);
+  const int lo_min = (p.window > 0 && pos0 - (p.window - 1) > 0) ? pos0 - (p.window - 1) : 0;
+  const int hi = pos0 + n_rows;                       // keys [lo_min, hi) matter
+  const int first_tile = lo_min / KEYS;
+  const int n_tiles = (hi - 1) / KEYS - first_tile + 1;
+  const int* table = p.tables + (size_t)seq * p.table_stride;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 128);
+    mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
+
+  if (warp == 0 && lane == 0) {
+    // ------------------------------------------------ producer: Q once, then K and V tiles page by page
+    mbar_expect_tx(q_full, TILE_BYTES);
+    tma_load_2d(q_s, &tmQ, q_full, head * D, row0);
+    tma_load_2d(q_s + HALF_BYTES, &tmQ, q_full, head * D + 64, row0);
+    const int pages = KEYS / p.bs;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int s = j % KV_STAGES;
+      if (j >= KV_STAGES && !mbar_wait(&kv_empty[s], ((j / KV_STAGES) & 1) ^ 1, p.err, abort_flag)) break;
+      uint8_t* ks = kv_s + s * 2 * TILE_BYTES;
+      uint8_t* vs = ks + TILE_BYTES;
+      mbar_expect_tx(&kv_full[s], 2 * TILE_BYTES);
+      const int key0 = (first_tile + j) * KEYS;
+      for (int pg = 0; pg < pages; ++pg) {
+        int kp = key0 + pg * p.bs;
+        int blk = kp < hi ? table[kp / p.bs] : 0;
+        if (blk < 0 || blk >= p.n_blocks) {
+          // keys before the window may have given their page back; they are masked. Anything else is an error.
+          if (kp + p.bs > lo_min && kp < hi && p.err) atomicExch(p.err, CUCA_ERR_BLOCK_RANGE);
+          blk = 0;
+        }
+        const int grow = (blk * p.nkv + kvh) * p.bs;  // row of the page in the pool seen as [rows][D]
+        const int off = pg * p.bs * 128;              // bytes: bs rows of 128 B inside a half
+        tma_load_2d(ks + off, &tmK, &kv_full[s], 0, grow);
+        tma_load_2d(ks + HALF_BYTES + off, &tmK, &kv_full[s], 64, grow);
+        tma_load_2d(vs + off, &tmV, &kv_full[s], 0, grow);
+        tma_load_2d(vs + HALF_BYTES + off, &tmV, &kv_full[s], 64, grow);
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc_qk = instr_desc(false), idesc_pv = instr_desc(true);
+    bool ok = mbar_wait(q_full, 0, p.err, abort_flag);
+    for (int j = 0; ok && j < n_tiles; ++j) {
+      const int s = j % KV_STAGES;
+      if (!mbar_wait(&kv_full[s], (j / KV_STAGES) & 1, p.err, abort_flag)) break;
+      tc_fence_after();
+      const uint32_t qa = smem_u32(q_s), ka = smem_u32(kv_s + s * 2 * TILE_BYTES), va = ka + TILE_BYTES;
+      // S = Q K^T: 8 steps of 16 head dimensions; a step moves 32 bytes inside a 64-wide half
+#pragma unroll
+      for (int k = 0; k < D / 16; ++k) {
+        const uint32_t off = (k / 4) * HALF_BYTES + (k % 4) * 32;
+        umma_bf16(tmem_s, desc_kmajor(qa + off), desc_kmajor(ka + off), idesc_qk, k > 0);
+      }
+      umma_commit(s_full);
+      // O += P V once the softmax threads have written P and rescaled O
+      if (!mbar_wait(p_full, j & 1, p.err, abort_flag)) break;
+      tc_fence_after();
+      const uint32_t pa = smem_u32(p_s);
+#pragma unroll
+      for (int k = 0; k < KEYS / 16; ++k) {
+        // A = P[rows][keys] K-major: 16 keys = 32 bytes inside a 64-key half.
+        // B = V[keys][dims] MN-major: 16 keys = two 8-key groups of 1024 bytes; dims 64..127 in the second half.
+        const uint32_t aoff = (k / 4) * HALF_BYTES + (k % 4) * 32;
+        umma_bf16(tmem_o, desc_kmajor(pa + aoff), desc_mnmajor(va + k * 2048, HALF_BYTES, 1024), idesc_pv,
+                  (j > 0 || k > 0));
+      }
+      umma_commit(&kv_empty[s]);
+      umma_commit(pv_done);
+    }
+  } else if (warp >= 2) {
+    // ------------------------------------------------ softmax: one query row per thread
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
+    const bool row_ok = r < n_rows;
+    const int row_pos = pos0 + r;
+    const int row_lo = (p.window > 0 && row_pos - (p.window - 1) > 0) ? row_pos - (p.window - 1) : 0;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      // the tcgen05.ld/st below are warp-wide: a warp leaves the loop together or not at all
+      if (!__all_sync(0xffffffffu, mbar_wait(s_full, j & 1, p.err, abort_flag))) { ok = false; break; }
+      tc_fence_after();
+      const int key0 = (first_tile + j) * KEYS;
+      const bool whole = key0 >= lo_min && key0 + KEYS - 1 <= pos0 && (p.window <= 0 || key0 >= pos0 + ROWS - 1 - (p.window - 1));
+      // pass 1: the whole row of scores in one round trip to tensor memory, then scale, mask, maximum
+      uint32_t raw[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32_nowait(tmem_s + lane_bits + c * 32, raw[c]);
+      tmem_ld_wait();
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float v = __uint_as_float(raw[c][i]) * p.scale_log2e;
+          if (!whole) {
+            int kp = key0 + c * 32 + i;
+            if (!(row_ok && kp <= row_pos && kp >= row_lo)) v = -INFINITY;
+          }
+          raw[c][i] = __float_as_uint(v);
+          mx4[i & 3] = fmaxf(mx4[i & 3], v);
+        }
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // The running maximum only moves when the new one exceeds it by more than 8 (in log2 units): values up to
+      // 2^8 above the reference are exact enough in 32-bit sums, and O is rescaled far less often.
+      float m_new = m;
+      if (mx > m + 8.f || m == -INFINITY) m_new = fmaxf(m, mx);
+      const float corr = (m_new == -INFINITY || m == m_new) ? 1.f : fast_exp2(m - m_new);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      // the previous P V must have finished before O is rescaled and P is overwritten
+      if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(pv_done, (j - 1) & 1, p.err, abort_flag))) { ok = false; break; }
+      tc_fence_after();
+      // pass 2: P = exp2(s - m) as bf16 into shared memory (K-major, 128-byte swizzle), row sum
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint8_t* half = p_s + (c / 2) * HALF_BYTES + r * 128;
+#pragma unroll
+        for (int q8 = 0; q8 < 4; ++q8) {   // 8 keys = 16 bytes = one swizzle chunk
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float pa_ = fast_exp2(__uint_as_float(raw[c][q8 * 8 + 2 * e]) - m_use);
+            float pb_ = fast_exp2(__uint_as_float(raw[c][q8 * 8 + 2 * e + 1]) - m_use);
+            sum4[e] += pa_ + pb_;
+            __nv_bfloat162 t2 = __floats2bfloat162_rn(pa_, pb_);
+            w[e] = *reinterpret_cast<uint32_t*>(&t2);
+          }
+          const int chunk = (c % 2) * 4 + q8;                 // 16-byte chunk inside the 128-byte row
+          *reinterpret_cast<uint4*>(half + ((chunk ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      l = l * corr + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      m = m_new;
+      // rescale O (not yet written on the first tile).
+      // tcgen05.ld/st are warp-wide: the whole warp rescales if any of its rows moved its maximum
+      if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          float o[32];
+          tmem_ld32(tmem_o + lane_bits + c * 32, o);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] *= corr;
+          tmem_st32(tmem_o + lane_bits + c * 32, o);
+        }
+        tmem_st_wait();
+      }
+      tc_fence_before();
+      fence_async_smem();   // P was written through the generic proxy; the tensor core reads it through the async one
+      mbar_arrive(p_full);
+    }
+    if (ok && __all_sync(0xffffffffu, mbar_wait(pv_done, (n_tiles - 1) & 1, p.err, abort_flag))) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* dst = p.out + (size_t)(row0 + r) * p.out_stride + (size_t)head * D;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        float o[32];
+        tmem_ld32(tmem_o + lane_bits + c * 32, o);  // warp-wide: every lane reads, only rows of the tile store
+        if (row_ok) {
+          uint32_t w[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            __nv_bfloat162 t2 = __floats2bfloat162_rn(o[2 * i] * inv, o[2 * i + 1] * inv);
+            w[i] = *reinterpret_cast<uint32_t*>(&t2);
+          }
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4)
+            *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = make_uint4(w[4 * q4], w[4 * q4 + 1], w[4 * q4 + 2], w[4 * q4 + 3]);
+        }
+      }
+    }
+  }
+  __syncwarp();
+  if (*abort_flag) {
+    unsigned long long t0 = global_ns();
+    while (global_ns() - t0 < 2000000ull) { }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 256);
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)ptr;
+  });
+  return fn;
+}
+struct Key {
+  const void* ptr; uint64_t rows, cols, stride; uint32_t box_rows;
+  bool operator==(const Key& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && stride == o.stride && box_rows == o.box_rows; }
+};
+struct KeyHash { size_t operator()(const Key& k) const { return ((size_t)k.ptr * 1000003u) ^ (k.rows * 31 + k.cols * 17 + k.stride * 7 + k.box_rows); } };
+
+// [rows][cols] bf16 with `stride` elements between rows; box = box_rows x 64 columns, 128-byte swizzle
+bool tensor_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_t stride, uint32_t box_rows, CUtensorMap* out) {
+  static std::unordered_map<Key, CUtensorMap, KeyHash> cache;
+  static std::mutex mu;
+  Key key{ptr, rows, cols, stride, box_rows};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return true; }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {stride * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (cache.size() > 1024) cache.clear();
+  cache.emplace(key, m);
+  *out = m;
+  return true;
+}
+
+}  // namespace
+
+// 1 if the tcgen05 prefill attention takes this shape: head size 128, pages of 8..128 positions (a power of
+// two), rows of the q buffer and the pools 16-byte aligned.
+CUCA_API int cuca_attention_tc_supported(int nh, int nkv, int d, int bs, int q_stride, int out_stride, const void* q,
+                                         const void* kpool, const void* vpool) {
+  if (d != D || nkv <= 0 || nh % nkv != 0) return 0;
+  if (bs < 8 || bs > KEYS || (bs & (bs - 1)) != 0) return 0;
+  if (q_stride % 8 != 0 || out_stride % 8 != 0) return 0;
+  if (((uintptr_t)q & 15) || ((uintptr_t)kpool & 15) || ((uintptr_t)vpool & 15)) return 0;
+  return 1;
+}
+
+// Prefill form on tcgen05: tile i covers rows tile_row0[i] .. +tile_nrows[i]-1 (at most 128 consecutive rows of
+// one request). q: [n_rows_total][q_stride] with the rotated query heads first; out: [..][out_stride].
+CUCA_API int cuca_attention_prefill_tc(const void* q, int q_stride, int n_rows_total, void* out, int out_stride,
+                                       const void* kpool, const void* vpool, int n_blocks, int bs,
+                                       const int* positions, const int* seq_of_row, const int* tables,
+                                       int table_stride, const int* tile_row0, const int* tile_nrows, int n_tiles,
+                                       int nh, int nkv, int d, float scale, int window, int* err,
+                                       cudaStream_t stream) {
+  if (n_tiles == 0) return 0;
+  CUCA_REQUIRE(cuca_attention_tc_supported(nh, nkv, d, bs, q_stride, out_stride, q, kpool, vpool),
+               "attention_prefill_tc: unsupported shape (heads %d/%d, head size %d, page %d)", nh, nkv, d, bs);
+  CUCA_REQUIRE(nh <= 65535, "attention_prefill_tc: too many heads");
+  CUtensorMap tmQ, tmK, tmV;
+  CUCA_REQUIRE(tensor_map(q, n_rows_total, (uint64_t)nh * d, q_stride, ROWS, &tmQ), "attention_prefill_tc: q tensor map failed");
+  const uint64_t pool_rows = (uint64_t)n_blocks * nkv * bs;
+  CUCA_REQUIRE(tensor_map(kpool, pool_rows, d, d, bs, &tmK), "attention_prefill_tc: key tensor map failed");
+  CUCA_REQUIRE(tensor_map(vpool, pool_rows, d, d, bs, &tmV), "attention_prefill_tc: value tensor map failed");
+  Params p;
+  p.out = (__nv_bfloat16*)out; p.out_stride = out_stride; p.tables = tables; p.table_stride = table_stride;
+  p.positions = positions; p.seq_of_row = seq_of_row; p.tile_row0 = tile_row0; p.tile_nrows = tile_nrows;
+  p.n_blocks = n_blocks; p.bs = bs; p.nh = nh; p.nkv = nkv; p.scale_log2e = scale * 1.4426950408889634f;
+  p.window = window; p.err = err;
+  const int smem = 2 * TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    CUCA_REQUIRE(e == cudaSuccess, "attention_prefill_tc: cannot reserve %d bytes of shared memory: %s", smem,
+                 cudaGetErrorString(e));
+    configured = true;
+  }
+  cuca_launch(attn_tc_kernel, dim3(n_tiles, nh), dim3(NTHREADS), smem, stream, true, tmQ, tmK, tmV, p);
+  CUCA_CHECK_LAUNCH("attention_prefill_tc");
+  return 0;
+}

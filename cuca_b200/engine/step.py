@@ -53,6 +53,9 @@ class AttentionPlan:
     tile_nrows: Optional[torch.Tensor]
     n_tiles: int
     fixed_chunking: Optional[tuple] = None  # (chunk, n_splits) frozen for a captured graph
+    tile128_row0: Optional[torch.Tensor] = None  # the same portions cut into tiles of up to 128 rows (tcgen05 form)
+    tile128_nrows: Optional[torch.Tensor] = None
+    n_tiles128: int = 0
 
     def chunk(self, n_kv_heads: int, head_dim: int = 128):
         if self.fixed_chunking is not None:
@@ -168,7 +171,7 @@ class Stepper:
             row += t
         T, S, R = row, len(entries), len(logit_rows)
         # attention plan: single-token requests are decode rows, longer portions are cut into tiles of 64 rows
-        decode_rows, tile_row0, tile_nrows, max_len = [], [], [], 1
+        decode_rows, tile_row0, tile_nrows, big_row0, big_nrows, max_len = [], [], [], [], [], 1
         r0 = 0
         for start, t in zip(starts, counts):
             if t == 1:
@@ -178,11 +181,17 @@ class Stepper:
                 for off in range(0, t, 64):
                     tile_row0.append(r0 + off)
                     tile_nrows.append(min(64, t - off))
+                for off in range(0, t, 128):
+                    big_row0.append(r0 + off)
+                    big_nrows.append(min(128, t - off))
             r0 += t
         # heavy tiles (late positions see most keys) first
         order = sorted(range(len(tile_row0)), key=lambda i: -positions[tile_row0[i]])
         tile_row0 = [tile_row0[i] for i in order]
         tile_nrows = [tile_nrows[i] for i in order]
+        order = sorted(range(len(big_row0)), key=lambda i: -positions[big_row0[i]])
+        big_row0 = [big_row0[i] for i in order]
+        big_nrows = [big_nrows[i] for i in order]
         identity = len(decode_rows) == T
         # page-table entries that changed since they were last uploaded
         upd_idx, upd_val = [[] for _ in self.pools.groups], [[] for _ in self.pools.groups]
@@ -195,7 +204,7 @@ class Stepper:
                     upd_val[gi].extend(table[lo:])
                     e.blocks.dirty_from[gi] = len(table)
         parts = [tokens, positions, slot_of_row, slots, logit_rows, [] if identity else decode_rows, tile_row0,
-                 tile_nrows]
+                 tile_nrows, big_row0, big_nrows]
         n_fixed = len(parts)
         for gi in range(len(self.pools.groups)):
             parts += [upd_idx[gi], upd_val[gi]]
@@ -216,7 +225,10 @@ class Stepper:
                                "positions": positions},
                          attention_plan=AttentionPlan(None if identity else views[5], len(decode_rows), max_len,
                                                       views[6] if tile_row0 else None,
-                                                      views[7] if tile_row0 else None, len(tile_row0)))
+                                                      views[7] if tile_row0 else None, len(tile_row0),
+                                                      tile128_row0=views[8] if big_row0 else None,
+                                                      tile128_nrows=views[9] if big_row0 else None,
+                                                      n_tiles128=len(big_row0)))
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run one step; returns logits [wanted, vocab] (32-bit, on the device) or None if nothing is wanted."""

@@ -43,6 +43,9 @@ _SIGNATURES = {
                                _P],
     "cuca_decode_advance": [_P, _P, _P, _P, _P, _P, _I, _I, _P],
     "cuca_set_pdl": [_I],
+    "cuca_attention_tc_supported": [_I, _I, _I, _I, _I, _I, _P, _P, _P],
+    "cuca_attention_prefill_tc": [_P, _I, _I, _P, _I, _P, _P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I,
+                                  _P, _P],
     "cuca_gemm_tc_partial_slices": [_I, _I, _I, _I],
     "cuca_gemm_tc_partial": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P],
     "cuca_add_partials_rmsnorm": [_P, _P, _I, c_size_t, _P, _P, _I, _P, _I, _I, _F, _P],

@@ -151,6 +151,7 @@ def gemm(a, w, out, epilogue=EPI_STORE, bias=None, err=None) -> None:
 
 
 _attn_scratch: dict = {}
+USE_TC_ATTENTION = True  # prompt portions through the tcgen05 attention where the shape allows
 
 
 def attention_scratch(device, floats: int, counters: int):
@@ -209,6 +210,22 @@ def attention_prefill(q, q_stride, out, kpool, vpool, positions, seq_of_row, tab
         n_kv_heads, head_dim, float(scale), int(window or 0), _p(err), _stream()), "attention_prefill")
 
 
+def attention_tc_supported(q, out, kpool, vpool, n_heads, n_kv_heads, head_dim) -> bool:
+    lib = library.load()
+    return bool(lib.cuca_attention_tc_supported(n_heads, n_kv_heads, head_dim, kpool.shape[2], q.stride(0),
+                                                out.stride(0), _p(q), _p(kpool), _p(vpool)))
+
+
+def attention_prefill_tc(q, out, kpool, vpool, positions, seq_of_row, tables, tile_row0, tile_nrows, n_tiles,
+                         n_heads, n_kv_heads, head_dim, scale, window, err) -> None:
+    """Prefill attention on tcgen05; tiles of up to 128 consecutive rows of one request."""
+    lib = library.load()
+    library.check(lib.cuca_attention_prefill_tc(
+        _p(q), q.stride(0), q.shape[0], _p(out), out.stride(0), _p(kpool), _p(vpool), kpool.shape[0], kpool.shape[2],
+        _p(positions), _p(seq_of_row), _p(tables), tables.shape[1], _p(tile_row0), _p(tile_nrows), n_tiles, n_heads,
+        n_kv_heads, head_dim, float(scale), int(window or 0), _p(err), _stream()), "attention_prefill_tc")
+
+
 def attention(qkv, out, cache, step, n_heads, n_kv_heads, head_dim, scale, window, err) -> None:
     """Paged causal attention of every row of the step; q is the head of each `qkv` row. bfloat16 with head
     sizes 16..128 in steps of 16 runs on tensor cores: single-token requests through the split-key decode form,
@@ -223,9 +240,15 @@ def attention(qkv, out, cache, step, n_heads, n_kv_heads, head_dim, scale, windo
                              cache.tables, plan.decode_rows, plan.n_decode, n_heads, n_kv_heads, head_dim, scale,
                              window, plan.chunk(n_kv_heads, head_dim)[0], plan.chunk(n_kv_heads, head_dim)[1], err)
         if plan.n_tiles:
-            attention_prefill(qkv, qkv.stride(0), out, cache.k, cache.v, step.positions, step.seq_of_row,
-                              cache.tables, plan.tile_row0, plan.tile_nrows, plan.n_tiles, n_heads, n_kv_heads,
-                              head_dim, scale, window, err)
+            if plan.n_tiles128 and USE_TC_ATTENTION and attention_tc_supported(qkv, out, cache.k, cache.v, n_heads,
+                                                                               n_kv_heads, head_dim):
+                attention_prefill_tc(qkv, out, cache.k, cache.v, step.positions, step.seq_of_row, cache.tables,
+                                     plan.tile128_row0, plan.tile128_nrows, plan.n_tiles128, n_heads, n_kv_heads,
+                                     head_dim, scale, window, err)
+            else:
+                attention_prefill(qkv, qkv.stride(0), out, cache.k, cache.v, step.positions, step.seq_of_row,
+                                  cache.tables, plan.tile_row0, plan.tile_nrows, plan.n_tiles, n_heads, n_kv_heads,
+                                  head_dim, scale, window, err)
         return
     attention_generic(qkv, qkv.stride(0), out, cache.k, cache.v, step.positions, step.seq_of_row, cache.tables,
                       n_heads, n_kv_heads, head_dim, scale, window, err)

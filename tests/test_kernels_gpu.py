@@ -396,3 +396,46 @@ def test_rope_store_from_partial_sums(dev):
         assert torch.allclose(q[r].float().view(nh, d), rotate(heads[:nh], p), atol=3e-2, rtol=3e-2)
         assert torch.allclose(kpool[page, :, off].float(), rotate(heads[nh:nh + nkv], p), atol=3e-2, rtol=3e-2)
         assert torch.allclose(vpool[page, :, off].float(), heads[nh + nkv:], atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("nh,nkv,bs,window", [(4, 2, 16, None), (8, 8, 32, None), (8, 2, 16, 150), (2, 1, 8, None),
+                                              (3, 1, 64, 40)])
+def test_attention_prefill_tcgen05(dev, nh, nkv, bs, window):
+    """Prefill attention on tcgen05 (head size 128): portions that start at position 0 and in the middle of a
+    request, tiles of 128 rows and ragged tails, several key tiles, against 32-bit attention."""
+    from cuca_b200.kernels import ops
+    d, dtype = 128, torch.bfloat16
+    lens = [5, 128, 200, 390, 131]
+    starts = [0, 0, 33, 129, 129]
+    k, v, kpool, vpool, tables = _paged_setup(dev, dtype, lens, nh, nkv, d, bs,
+                                              n_blocks=sum(-(-l // bs) for l in lens) + 3, seed=6)
+    g = torch.Generator(device=dev).manual_seed(8)
+    pos_list, seq_list, tile_row0, tile_nrows = [], [], [], []
+    for s, (l, st) in enumerate(zip(lens, starts)):
+        r0 = len(pos_list)
+        n = l - st
+        pos_list += list(range(st, l))
+        seq_list += [s] * n
+        for off in range(0, n, 128):
+            tile_row0.append(r0 + off)
+            tile_nrows.append(min(128, n - off))
+    T = len(pos_list)
+    width = (nh + 2 * nkv) * d  # q is the head of a wider row, as in the engine
+    qkv = torch.randn(T, width, device=dev, generator=g).to(dtype)
+    positions = torch.tensor(pos_list, dtype=torch.int32, device=dev)
+    seq = torch.tensor(seq_list, dtype=torch.int32, device=dev)
+    out = torch.zeros(T, nh * d, device=dev, dtype=dtype)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    assert ops.attention_tc_supported(qkv, out, kpool, vpool, nh, nkv, d)
+    ops.attention_prefill_tc(qkv, out, kpool, vpool, positions, seq, tables,
+                             torch.tensor(tile_row0, dtype=torch.int32, device=dev),
+                             torch.tensor(tile_nrows, dtype=torch.int32, device=dev), len(tile_row0), nh, nkv, d,
+                             1.0 / math.sqrt(d), window, err)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    for r in range(T):
+        s, pos = seq_list[r], pos_list[r]
+        want = _ref_attention(qkv[r, :nh * d].float().view(nh, d), k[s].to(dtype).float(), v[s].to(dtype).float(), pos,
+                              1.0 / math.sqrt(d), window)
+        got = out[r].float().view(nh, d)
+        assert torch.allclose(got, want, atol=2e-2, rtol=2e-2), (r, s, pos, float((got - want).abs().max()))
