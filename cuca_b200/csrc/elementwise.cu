@@ -168,52 +168,64 @@ CUCA_API int cuca_rmsnorm(const float* x, const void* w, int w_dtype, void* out,
 // the layer owns no keys, only q is rotated):
 // pool[block][kv head][row in block][d], block = table[seq][pos / bs].
 template <typename T>
-__global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
-                                  const int* __restrict__ seq_of_row, const int* __restrict__ tables,
-                                  int table_stride, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                                  int table_rows, int rot, T* __restrict__ kpool, T* __restrict__ vpool,
-                                  int n_blocks, int bs, int nh, int nkv, int d, int* err) {
+__global__ void __launch_bounds__(256)
+rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                  const int* __restrict__ seq_of_row, const int* __restrict__ tables,
+                  int table_stride, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                  int table_rows, int rot, T* __restrict__ kpool, T* __restrict__ vpool,
+                  int n_blocks, int bs, int nh, int nkv, int d, int* err) {
+  // one block per row; its threads walk all heads of the row: rotated pairs, pass-through values, v copies
   pdl_trigger();
   pdl_wait();
-  int row = blockIdx.x;
-  int head = blockIdx.y;  // 0..nh-1 q, nh..nh+nkv-1 k, then v
-  int seq = seq_of_row[row];
+  const int row = blockIdx.x;
+  const int seq = seq_of_row[row];
   if (seq < 0) return;
-  int pos = positions[row];
-  T* src = qkv + (size_t)row * (nh + 2 * nkv) * d + (size_t)head * d;
-  bool is_v = head >= nh + nkv;
-  bool is_k = !is_v && head >= nh;
-  T* dst = nullptr;
-  if (is_k || is_v) {
+  const int pos = positions[row];
+  const int half = rot / 2;
+  T* base = qkv + (size_t)row * (nh + 2 * nkv) * d;
+  long long page_off = -1;  // offset of this position's row in a pool, per kv head add kvh * bs * d
+  if (nkv > 0) {
     int blk = pos >= 0 ? tables[(size_t)seq * table_stride + pos / bs] : -1;
     if (blk < 0 || blk >= n_blocks) {
       if (threadIdx.x == 0 && err) atomicExch(err, CUCA_ERR_BLOCK_RANGE);
-      return;
-    }
-    int kvh = is_k ? head - nh : head - nh - nkv;
-    dst = (is_k ? kpool : vpool) + (((size_t)blk * nkv + kvh) * bs + (pos % bs)) * d;
-  }
-  if (is_v) {
-    for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = src[i];
-    return;
-  }
-  int half = rot / 2;
-  bool in_table = pos >= 0 && pos < table_rows;
-  if (!in_table && half > 0 && threadIdx.x == 0 && err) atomicExch(err, CUCA_ERR_TOKEN_RANGE);
-  for (int i = threadIdx.x; i < half; i += blockDim.x) {
-    float c = in_table ? cos_t[(size_t)pos * half + i] : 1.f;
-    float s = in_table ? sin_t[(size_t)pos * half + i] : 0.f;
-    float a = to_f32(src[i]), b = to_f32(src[i + half]);
-    T ra = from_f32<T>(a * c - b * s);
-    T rb = from_f32<T>(a * s + b * c);
-    if (is_k) {
-      if (dst) { dst[i] = ra; dst[i + half] = rb; }
     } else {
-      src[i] = ra; src[i + half] = rb;
+      page_off = ((long long)blk * nkv * bs + (pos % bs)) * d;
     }
   }
-  if (is_k && dst)
-    for (int i = rot + threadIdx.x; i < d; i += blockDim.x) dst[i] = src[i];
+  const bool in_table = pos >= 0 && pos < table_rows;
+  if (!in_table && half > 0 && threadIdx.x == 0 && err) atomicExch(err, CUCA_ERR_TOKEN_RANGE);
+  const float* cr = cos_t + (size_t)(in_table ? pos : 0) * half;
+  const float* sr = sin_t + (size_t)(in_table ? pos : 0) * half;
+  // q and k heads: `half` rotated pairs + (d - rot) values that pass through
+  const int per_head = half + (d - rot);
+  const int qk_items = (nh + nkv) * per_head;
+  for (int idx = threadIdx.x; idx < qk_items; idx += blockDim.x) {
+    const int head = idx / per_head, i = idx % per_head;
+    T* src = base + (size_t)head * d;
+    T* dst = nullptr;  // k heads go to their page; q heads are rotated in place
+    const bool is_k = head >= nh;
+    if (is_k) {
+      if (page_off < 0) continue;
+      dst = kpool + page_off + (size_t)(head - nh) * bs * d;
+    }
+    if (i < half) {
+      float c = in_table ? cr[i] : 1.f, sn = in_table ? sr[i] : 0.f;
+      float a = to_f32(src[i]), b = to_f32(src[i + half]);
+      T ra = from_f32<T>(a * c - b * sn), rb = from_f32<T>(a * sn + b * c);
+      if (is_k) { dst[i] = ra; dst[i + half] = rb; }
+      else { src[i] = ra; src[i + half] = rb; }
+    } else if (is_k) {
+      const int e = rot + (i - half);
+      dst[e] = src[e];
+    }
+  }
+  if (nkv > 0 && page_off >= 0) {
+    const T* vsrc = base + (size_t)(nh + nkv) * d;
+    for (int idx = threadIdx.x; idx < nkv * d; idx += blockDim.x) {
+      const int kvh = idx / d, e = idx % d;
+      vpool[page_off + (size_t)kvh * bs * d + e] = vsrc[idx];
+    }
+  }
 }
 
 CUCA_API int cuca_rope_store(void* qkv, int dtype, const int* positions, const int* seq_of_row,
@@ -223,8 +235,8 @@ CUCA_API int cuca_rope_store(void* qkv, int dtype, const int* positions, const i
   if (n_rows == 0) return 0;
   CUCA_REQUIRE(rot >= 0 && rot <= d && rot % 2 == 0, "rope_store: rotary size %d does not fit head size %d", rot, d);
   CUCA_REQUIRE(bs > 0 && nh > 0 && nkv >= 0 && d > 0, "rope_store: bad sizes");
-  dim3 grid(n_rows, nh + 2 * nkv);
-  int threads = d / 2 >= 64 ? 64 : 32;
+  dim3 grid(n_rows);
+  int threads = 256;
   if (dtype == CUCA_F32)
     cuca_launch(rope_store_kernel<float>, grid, dim3(threads), 0, stream, true, (float*)qkv, positions, seq_of_row,
                 tables, table_stride, cos_t, sin_t, table_rows, rot, (float*)kpool, (float*)vpool, n_blocks, bs, nh,
