@@ -80,8 +80,25 @@ __device__ __forceinline__ float block_sum_1024(float s, float* red) {
   return tot;
 }
 
+// four consecutive outputs with one store where the address allows it
+__device__ __forceinline__ void store4(float* o, float a, float b, float c, float d) {
+  if ((((size_t)o) & 15) == 0) *reinterpret_cast<float4*>(o) = make_float4(a, b, c, d);
+  else { o[0] = a; o[1] = b; o[2] = c; o[3] = d; }
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* o, float a, float b, float c, float d) {
+  if ((((size_t)o) & 7) == 0) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    *reinterpret_cast<uint2*>(o) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+  } else {
+    o[0] = __float2bfloat16_rn(a); o[1] = __float2bfloat16_rn(b); o[2] = __float2bfloat16_rn(c); o[3] = __float2bfloat16_rn(d);
+  }
+}
+
 // PARTIAL: x[row] += sum over slices first (written back), see below.
-template <typename TW, typename TO, bool PARTIAL>
+// VL: value groups per thread and round. A block of B threads with VL groups each does exactly the arithmetic
+// of a block of B * VL threads with one group each (thread t plays the lanes t, t + B, ...: the same warp
+// shuffles, the same order across warps), so many-row launches can use narrow blocks with bit-equal results.
+template <typename TW, typename TO, bool PARTIAL, int VL>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ partial, int n_slices,
                                size_t slice_stride, const TW* __restrict__ w, TO* __restrict__ out,
                                const int* __restrict__ rows, int E, float eps) {
@@ -98,10 +115,9 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
   const bool vec = (E & 3) == 0 && (((size_t)xr) & 15) == 0 && (!PARTIAL || ((((size_t)pr) | (slice_stride * 4)) & 15) == 0);
   if (vec) {
     const int nvec = E >> 2;
-    // at most two rounds for rows up to 8192 wide: keep the values in registers between the two passes
-    float4 keep[2];
-    int kept = 0;
-    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    // One value group (four floats) per thread and round. The first two rounds (rows up to 8192 wide) stay in
+    // registers between the two passes; wider rows are read again.
+    auto take = [&](int i) {
       float4 v = reinterpret_cast<const float4*>(xr)[i];
       if (PARTIAL) {
         for (int k0 = 0; k0 < n_slices; k0 += 4) {  // four slices' loads in flight at once, added in slice order
@@ -116,18 +132,43 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
         reinterpret_cast<float4*>(xr)[i] = v;
       }
       s = fmaf(v.x, v.x, s); s = fmaf(v.y, v.y, s); s = fmaf(v.z, v.z, s); s = fmaf(v.w, v.w, s);
-      if (kept < 2) keep[kept] = v;
-      ++kept;
-    }
-    float r = rsqrtf(block_sum_1024(s, red) / (float)E + eps);
-    int round = 0;
-    for (int i = threadIdx.x; i < nvec; i += blockDim.x, ++round) {
-      float4 v = round < 2 ? keep[round] : reinterpret_cast<const float4*>(xr)[i];
+      return v;
+    };
+    auto put = [&](int i, float4 v, float r) {
       const int e = i << 2;
-      o[e] = from_f32<TO>(v.x * r * to_f32(w[e]));
-      o[e + 1] = from_f32<TO>(v.y * r * to_f32(w[e + 1]));
-      o[e + 2] = from_f32<TO>(v.z * r * to_f32(w[e + 2]));
-      o[e + 3] = from_f32<TO>(v.w * r * to_f32(w[e + 3]));
+      const float w0 = to_f32(w[e]), w1 = to_f32(w[e + 1]), w2 = to_f32(w[e + 2]), w3 = to_f32(w[e + 3]);
+      store4(o + e, v.x * r * w0, v.y * r * w1, v.z * r * w2, v.w * r * w3);
+    };
+    const int VB = blockDim.x * VL;  // virtual block width
+    float4 v0[VL], v1[VL];
+    float sk[VL];
+#pragma unroll
+    for (int k = 0; k < VL; ++k) {
+      const int i0 = threadIdx.x + blockDim.x * k, i1 = i0 + VB;
+      s = 0.f;
+      v0[k] = v1[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i0 < nvec) v0[k] = take(i0);
+      if (i1 < nvec) v1[k] = take(i1);
+      for (int i = i1 + VB; i < nvec; i += VB) take(i);
+      sk[k] = s;
+    }
+    // reduction in the order of the virtual block: warp sums, then the warps in ascending order
+    const int real_warps = blockDim.x >> 5;
+#pragma unroll
+    for (int k = 0; k < VL; ++k) {
+      float wsum = warp_sum(sk[k]);
+      if ((threadIdx.x & 31) == 0) red[(threadIdx.x >> 5) + real_warps * k] = wsum;
+    }
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < real_warps * VL; ++i) tot += red[i];
+    const float r = rsqrtf(tot / (float)E + eps);
+#pragma unroll
+    for (int k = 0; k < VL; ++k) {
+      const int i0 = threadIdx.x + blockDim.x * k, i1 = i0 + VB;
+      if (i0 < nvec) put(i0, v0[k], r);
+      if (i1 < nvec) put(i1, v1[k], r);
+      for (int i = i1 + VB; i < nvec; i += VB) put(i, reinterpret_cast<const float4*>(xr)[i], r);
     }
   } else {
     for (int i = threadIdx.x; i < E; i += blockDim.x) {
@@ -149,9 +190,17 @@ CUCA_API int cuca_rmsnorm(const float* x, const void* w, int w_dtype, void* out,
   if (n_rows == 0) return 0;
   CUCA_REQUIRE(E > 0, "rmsnorm: bad width %d", E);
   float* xm = const_cast<float*>(x);  // not written without PARTIAL
+  // many rows: a quarter of the threads per block, four value groups each (bit-equal to the wide block)
+  const bool narrow = norm_block(E) == 1024 && n_rows >= 64 && (E & 3) == 0;
 #define LAUNCH(TW, TO)                                                                                          \
-  cuca_launch(rmsnorm_kernel<TW, TO, false>, dim3(n_rows), dim3(norm_block(E)), 0, stream, true, xm,            \
-              (const float*)nullptr, 0, (size_t)0, (const TW*)w, (TO*)out, rows, E, eps)
+  do {                                                                                                          \
+    if (narrow)                                                                                                 \
+      cuca_launch(rmsnorm_kernel<TW, TO, false, 4>, dim3(n_rows), dim3(256), 0, stream, true, xm,               \
+                  (const float*)nullptr, 0, (size_t)0, (const TW*)w, (TO*)out, rows, E, eps);                   \
+    else                                                                                                        \
+      cuca_launch(rmsnorm_kernel<TW, TO, false, 1>, dim3(n_rows), dim3(norm_block(E)), 0, stream, true, xm,     \
+                  (const float*)nullptr, 0, (size_t)0, (const TW*)w, (TO*)out, rows, E, eps);                   \
+  } while (0)
   if (w_dtype == CUCA_F32 && out_dtype == CUCA_F32) LAUNCH(float, float);
   else if (w_dtype == CUCA_F32 && out_dtype == CUCA_BF16) LAUNCH(float, __nv_bfloat16);
   else if (w_dtype == CUCA_BF16 && out_dtype == CUCA_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
@@ -320,10 +369,10 @@ CUCA_API int cuca_add_partials_rmsnorm(float* x, const float* partial, int n_sli
   if (n_rows == 0) return 0;
   CUCA_REQUIRE(E > 0 && n_slices >= 1, "add_partials_rmsnorm: bad sizes");
   if (out_dtype == CUCA_BF16)
-    cuca_launch(rmsnorm_kernel<float, __nv_bfloat16, true>, dim3(n_rows), dim3(norm_block(E)), 0, stream, true, x,
+    cuca_launch(rmsnorm_kernel<float, __nv_bfloat16, true, 1>, dim3(n_rows), dim3(norm_block(E)), 0, stream, true, x,
                 partial, n_slices, slice_stride, w, (__nv_bfloat16*)out, rows, E, eps);
   else if (out_dtype == CUCA_F32)
-    cuca_launch(rmsnorm_kernel<float, float, true>, dim3(n_rows), dim3(norm_block(E)), 0, stream, true, x, partial,
+    cuca_launch(rmsnorm_kernel<float, float, true, 1>, dim3(n_rows), dim3(norm_block(E)), 0, stream, true, x, partial,
                 n_slices, slice_stride, w, (float*)out, rows, E, eps);
   else
     CUCA_REQUIRE(false, "add_partials_rmsnorm: unknown dtype %d", out_dtype);

@@ -439,3 +439,18 @@ def test_attention_prefill_tcgen05(dev, nh, nkv, bs, window):
                               1.0 / math.sqrt(d), window)
         got = out[r].float().view(nh, d)
         assert torch.allclose(got, want, atol=2e-2, rtol=2e-2), (r, s, pos, float((got - want).abs().max()))
+
+
+def test_rmsnorm_many_rows_equals_few_rows_to_the_bit(dev):
+    """Launches with many rows use narrower blocks; a row's bits must not depend on that."""
+    from cuca_b200.kernels import ops
+    for E in (4096, 5120, 8192):
+        x = torch.randn(200, E, device=dev) * 2
+        w = torch.randn(E, device=dev)
+        many = torch.empty(200, E, device=dev)
+        ops.rmsnorm(x, w, many, 1e-5)
+        few = torch.empty(3, E, device=dev)
+        ops.rmsnorm(x[100:103].contiguous(), w, few, 1e-5)
+        assert torch.equal(many[100:103], few)
+        ref = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + 1e-5) * w
+        assert torch.allclose(many, ref, atol=1e-5, rtol=1e-5)
