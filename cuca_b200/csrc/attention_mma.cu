@@ -44,6 +44,15 @@ struct AttnParams {
   float* part;           // decode: [rows][nh][splits][D + 2] partial (acc, m, l)
   int* counters;         // decode: [rows][nkv], zero before and after
   int* err;
+  // decode with the projection's K slices as input: the kernel adds them, rotates q and k and stores k and v itself
+  const float* partial;  // [slices][rows][(nh + 2 nkv) D] 32-bit; row layout q heads, k heads, v heads
+  int n_slices;
+  size_t slice_stride;   // floats between slices
+  const __nv_bfloat16* bias;  // [(nh + 2 nkv) D] or null
+  const float* cos_t;    // [table_rows][rot / 2]
+  const float* sin_t;
+  int table_rows, rot;
+  int has_kv;            // 0: the layer reads another layer's pages and has only q
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -80,6 +89,9 @@ struct Smem {
   static constexpr int RS = D + 8;  // row stride in elements: 16 bytes of padding
   static constexpr int TILE_ELEMS = TILE * RS;
   static constexpr int BYTES = STAGES * 2 /*k, v*/ * TILE_ELEMS * 2;
+  // fused form: the 16 query rows, then the new key and the new value of the row
+  static constexpr int Q_ELEMS = 16 * RS;
+  static constexpr int FUSED_BYTES = BYTES + (Q_ELEMS + 2 * D) * 2;
 };
 
 // One warp's state over its 16 MMA rows: thread (g, t) holds rows g and g + 8.
@@ -89,9 +101,10 @@ struct WarpState {
   float m[2], l[2];
 };
 
-template <int D, bool DECODE>
+template <int D, bool DECODE, bool FUSED>
 __global__ void __launch_bounds__(NTHREADS)
 attn_mma_kernel(const AttnParams p) {
+  static_assert(!FUSED || DECODE, "only the decode form takes the projection's K slices");
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   using S = Smem<D>;
@@ -171,7 +184,7 @@ attn_mma_kernel(const AttnParams p) {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       uint32_t lo = 0, hi = 0;
-      if (row_ok[h]) {
+      if (!FUSED && row_ok[h]) {
         const __nv_bfloat16* qp = p.q + (size_t)row_token[h] * p.q_stride + (size_t)row_head[h] * D + ks * 16 + 2 * t;
         lo = *reinterpret_cast<const uint32_t*>(qp);
         hi = *reinterpret_cast<const uint32_t*>(qp + 8);
@@ -197,9 +210,12 @@ attn_mma_kernel(const AttnParams p) {
   // the page-table lookups of tile i + 2 are in flight while tile i is computed, so no copy waits on one.
   __shared__ long long s_rowoff[STAGES][TILE];
   const int bs_shift = __ffs(p.bs) - 1, bs_mask = p.bs - 1;
+  // fused form: the CTA whose keys include the row's own position makes that key and value itself
+  const bool owner = FUSED && p.has_kv && P >= range_lo && P < range_hi;
   auto row_offset = [&](int tile_index) -> long long {
     int kp = (first_tile + tile_index) * TILE + (int)threadIdx.x;
     if (kp < range_lo || kp >= range_hi) return -1;
+    if (owner && kp == P) return -1;  // comes from registers, not from the page
     int blk = table[kp >> bs_shift];
     if (blk < 0 || blk >= p.n_blocks) {
       if (p.err) atomicExch(p.err, CUCA_ERR_BLOCK_RANGE);
@@ -234,6 +250,74 @@ attn_mma_kernel(const AttnParams p) {
     cp_async_commit();
   }
 
+  // ---------------------------------------------------------------- fused form: q (and k, v) from the K slices
+  __nv_bfloat16* q_s = smem + (size_t)STAGES * 2 * S::TILE_ELEMS;  // [16][RS]: the group's rotated query heads
+  __nv_bfloat16* k_new = q_s + S::Q_ELEMS;                          // [D] rotated key of the row's own position
+  __nv_bfloat16* v_new = k_new + D;                                 // [D] its value
+  if (FUSED) {
+    const size_t width = (size_t)(p.nh + (p.has_kv ? 2 * p.nkv : 0)) * D;
+    const float* prow = p.partial + (size_t)dec_row * width;
+    auto value = [&](int col) -> float {
+      float v = p.bias ? __bfloat162float(p.bias[col]) : 0.f;
+      for (int k0 = 0; k0 < p.n_slices; k0 += 4) {  // four slices' loads in flight at once, added in slice order
+        float x[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) x[u] = k0 + u < p.n_slices ? __ldcg(prow + (size_t)(k0 + u) * p.slice_stride + col) : 0.f;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v += x[u];
+      }
+      return v;
+    };
+    const int half = p.rot / 2;
+    const bool in_table = P >= 0 && P < p.table_rows;
+    if (!in_table && half > 0 && threadIdx.x == 0 && p.err) atomicExch(p.err, CUCA_ERR_TOKEN_RANGE);
+    // per head: `half` rotated pairs (i, i + half), then the values beyond the rotary part as they are
+    const int units = D - half;
+    const int heads_here = G + (owner ? 1 : 0);
+    for (int idx = threadIdx.x; idx < heads_here * units; idx += NTHREADS) {
+      const int hh = idx / units, u = idx % units;
+      const int col0 = hh < G ? (kvh * G + hh) * D : (p.nh + kvh) * D;
+      __nv_bfloat16* dst = hh < G ? q_s + hh * S::RS : k_new;
+      if (u < half) {
+        const float c = in_table ? p.cos_t[(size_t)P * half + u] : 1.f;
+        const float sn = in_table ? p.sin_t[(size_t)P * half + u] : 0.f;
+        const float a = value(col0 + u), b = value(col0 + u + half);
+        dst[u] = __float2bfloat16_rn(a * c - b * sn);
+        dst[u + half] = __float2bfloat16_rn(a * sn + b * c);
+      } else {
+        dst[u + half] = __float2bfloat16_rn(value(col0 + u + half));
+      }
+    }
+    if (owner)
+      for (int i = threadIdx.x; i < D; i += NTHREADS)
+        v_new[i] = __float2bfloat16_rn(value((p.nh + p.nkv + kvh) * D + i));
+    for (int idx = threadIdx.x; idx < (16 - G) * D; idx += NTHREADS)
+      q_s[(G + idx / D) * S::RS + idx % D] = __float2bfloat16_rn(0.f);
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const __nv_bfloat16* qp = q_s + (g + 8 * h) * S::RS + ks * 16 + 2 * t;
+        qf[ks][h] = *reinterpret_cast<const uint32_t*>(qp);
+        qf[ks][2 + h] = *reinterpret_cast<const uint32_t*>(qp + 8);
+      }
+    if (owner) {
+      // the page keeps the new key and value for the steps to come
+      const int blk = table[P >> bs_shift];
+      if (blk < 0 || blk >= p.n_blocks) {
+        if (threadIdx.x == 0 && p.err) atomicExch(p.err, CUCA_ERR_BLOCK_RANGE);
+      } else {
+        const size_t off = ((((size_t)blk * p.nkv + kvh) << bs_shift) + (P & bs_mask)) * D;
+        for (int i = threadIdx.x; i < 2 * (D / 8); i += NTHREADS) {
+          const int which = i / (D / 8), ch = i % (D / 8);
+          __nv_bfloat16* pool = const_cast<__nv_bfloat16*>(which ? p.vpool : p.kpool);
+          *reinterpret_cast<uint4*>(pool + off + ch * 8) = *reinterpret_cast<const uint4*>((which ? v_new : k_new) + ch * 8);
+        }
+      }
+    }
+  }
+
   for (int ti = 0; ti < n_tiles; ++ti) {
     const int stage = ti % STAGES;
     if (ti + STAGES - 1 < n_tiles) load_tile((ti + STAGES - 1) % STAGES, ti + STAGES - 1);
@@ -246,6 +330,16 @@ attn_mma_kernel(const AttnParams p) {
     const int start = (first_tile + ti) * TILE;
     const __nv_bfloat16* ks = smem + (size_t)stage * 2 * S::TILE_ELEMS;
     const __nv_bfloat16* vs = ks + S::TILE_ELEMS;
+    if (owner && P >= start && P < start + TILE) {
+      // the row's own key and value take their place in the tile (the copy left zeros there)
+      const int key = P - start;
+      for (int i = threadIdx.x; i < 2 * (D / 8); i += NTHREADS) {
+        const int which = i / (D / 8), ch = i % (D / 8);
+        __nv_bfloat16* dst = const_cast<__nv_bfloat16*>(which ? vs : ks) + key * S::RS + ch * 8;
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>((which ? v_new : k_new) + ch * 8);
+      }
+      __syncthreads();
+    }
 
     // decode: this warp owns keys [16 warp, 16 warp + 16) of the tile and updates its softmax per 16 keys;
     // prefill: every warp takes all 64 keys of the tile in one softmax update
@@ -467,38 +561,38 @@ attn_mma_kernel(const AttnParams p) {
   if (threadIdx.x == 0) p.counters[blockIdx.z * p.nkv + kvh] = 0;
 }
 
-template <int D, bool DECODE>
+template <int D, bool DECODE, bool FUSED>
 int launch(const AttnParams& p, dim3 grid, cudaStream_t stream) {
-  int smem = Smem<D>::BYTES;
+  int smem = FUSED ? Smem<D>::FUSED_BYTES : Smem<D>::BYTES;
   if (DECODE) {
     int need = 4 * 16 * (D + 2) * (int)sizeof(float);
     if (need > smem) smem = need;
   }
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_mma_kernel<D, DECODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_mma_kernel<D, DECODE, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) {
       cuca_set_error("attention: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
       return 2;
     }
     configured = true;
   }
-  cuca_launch(attn_mma_kernel<D, DECODE>, grid, dim3(NTHREADS), smem, stream, true, p);
+  cuca_launch(attn_mma_kernel<D, DECODE, FUSED>, grid, dim3(NTHREADS), smem, stream, true, p);
   CUCA_CHECK_LAUNCH("attention_mma");
   return 0;
 }
 
-template <bool DECODE>
+template <bool DECODE, bool FUSED = false>
 int dispatch(int d, const AttnParams& p, dim3 grid, cudaStream_t stream) {
   switch (d) {
-    case 16: return launch<16, DECODE>(p, grid, stream);
-    case 32: return launch<32, DECODE>(p, grid, stream);
-    case 48: return launch<48, DECODE>(p, grid, stream);
-    case 64: return launch<64, DECODE>(p, grid, stream);
-    case 80: return launch<80, DECODE>(p, grid, stream);
-    case 96: return launch<96, DECODE>(p, grid, stream);
-    case 112: return launch<112, DECODE>(p, grid, stream);
-    case 128: return launch<128, DECODE>(p, grid, stream);
+    case 16: return launch<16, DECODE, FUSED>(p, grid, stream);
+    case 32: return launch<32, DECODE, FUSED>(p, grid, stream);
+    case 48: return launch<48, DECODE, FUSED>(p, grid, stream);
+    case 64: return launch<64, DECODE, FUSED>(p, grid, stream);
+    case 80: return launch<80, DECODE, FUSED>(p, grid, stream);
+    case 96: return launch<96, DECODE, FUSED>(p, grid, stream);
+    case 112: return launch<112, DECODE, FUSED>(p, grid, stream);
+    case 128: return launch<128, DECODE, FUSED>(p, grid, stream);
   }
   cuca_set_error("attention_mma: head size %d is not one of 16, 32, ..., 128", d);
   return 1;
@@ -519,14 +613,23 @@ CUCA_API size_t cuca_attention_decode_scratch(int n_rows, int nh, int d, int n_s
   return (size_t)n_rows * nh * n_splits * (d + 2);
 }
 
-// Decode form: one query row per entry of `rows` (null: rows 0..n_rows-1), keys split in chunks of `chunk`
-// positions (a multiple of 64), `n_splits` chunks cover every row's keys (n_splits * chunk > largest position).
-// chunk = 0: each row divides its own keys evenly over the n_splits chunks, whatever its length.
-CUCA_API int cuca_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* kpool,
-                                   const void* vpool, int n_blocks, int bs, const int* positions,
-                                   const int* seq_of_row, const int* tables, int table_stride, const int* rows,
-                                   int n_rows, int nh, int nkv, int d, float scale, int window, int chunk,
-                                   int n_splits, float* part, int* counters, int* err, cudaStream_t stream) {
+namespace {
+// What the fused form adds to the decode form's arguments.
+struct FusedInput {
+  const float* partial;
+  int n_slices;
+  size_t slice_stride;
+  const void* bias;
+  const float* cos_t;
+  const float* sin_t;
+  int table_rows, rot, has_kv;
+};
+
+int attention_decode_impl(const void* q, int q_stride, const FusedInput* fused, void* out, int out_stride,
+                          const void* kpool, const void* vpool, int n_blocks, int bs, const int* positions,
+                          const int* seq_of_row, const int* tables, int table_stride, const int* rows, int n_rows,
+                          int nh, int nkv, int d, float scale, int window, int chunk, int n_splits, float* part,
+                          int* counters, int* err, cudaStream_t stream) {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -548,7 +651,51 @@ CUCA_API int cuca_attention_decode(const void* q, int q_stride, void* out, int o
   p.rows = rows; p.tile_row0 = nullptr; p.tile_nrows = nullptr; p.nh = nh; p.nkv = nkv;
   p.scale_log2e = scale * 1.4426950408889634f; p.window = window; p.chunk = chunk; p.part = part;
   p.counters = counters; p.err = err; p.slots = sms * per_sm;
-  return dispatch<true>(d, p, dim3(n_splits, nkv, n_rows), stream);
+  p.partial = nullptr; p.n_slices = 0; p.slice_stride = 0; p.bias = nullptr; p.cos_t = p.sin_t = nullptr;
+  p.table_rows = 0; p.rot = 0; p.has_kv = 0;
+  if (!fused) return dispatch<true, false>(d, p, dim3(n_splits, nkv, n_rows), stream);
+  CUCA_REQUIRE(fused->partial && fused->n_slices >= 1, "attention_decode_fused: no projection slices");
+  CUCA_REQUIRE(fused->rot >= 0 && fused->rot <= d && fused->rot % 2 == 0,
+               "attention_decode_fused: rotary size %d does not fit head size %d", fused->rot, d);
+  CUCA_REQUIRE(fused->rot == 0 || (fused->cos_t && fused->sin_t), "attention_decode_fused: no rotation tables");
+  CUCA_REQUIRE(d % 8 == 0 && ((uintptr_t)kpool & 15) == 0 && ((uintptr_t)vpool & 15) == 0,
+               "attention_decode_fused: pages must be 16-byte aligned");
+  p.partial = fused->partial; p.n_slices = fused->n_slices; p.slice_stride = fused->slice_stride;
+  p.bias = (const __nv_bfloat16*)fused->bias; p.cos_t = fused->cos_t; p.sin_t = fused->sin_t;
+  p.table_rows = fused->table_rows; p.rot = fused->rot; p.has_kv = fused->has_kv;
+  return dispatch<true, true>(d, p, dim3(n_splits, nkv, n_rows), stream);
+}
+}  // namespace
+
+// Decode form: one query row per entry of `rows` (null: rows 0..n_rows-1), keys split in chunks of `chunk`
+// positions (a multiple of 64), `n_splits` chunks cover every row's keys (n_splits * chunk > largest position).
+// chunk = 0: each row divides its own keys evenly over the n_splits chunks, whatever its length.
+CUCA_API int cuca_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* kpool,
+                                   const void* vpool, int n_blocks, int bs, const int* positions,
+                                   const int* seq_of_row, const int* tables, int table_stride, const int* rows,
+                                   int n_rows, int nh, int nkv, int d, float scale, int window, int chunk,
+                                   int n_splits, float* part, int* counters, int* err, cudaStream_t stream) {
+  return attention_decode_impl(q, q_stride, nullptr, out, out_stride, kpool, vpool, n_blocks, bs, positions,
+                               seq_of_row, tables, table_stride, rows, n_rows, nh, nkv, d, scale, window, chunk,
+                               n_splits, part, counters, err, stream);
+}
+
+// The decode form fed by the unadded K slices of the stacked q/k/v projection, partial[slice][row][(nh + 2 nkv) d]
+// (has_kv = 0: [nh d], a layer that reads another layer's pages): every CTA adds the slices of its group's query
+// heads in slice order (plus bias) and rotates them (pairs (i, i + rot/2) by the tables' row of the position);
+// the CTA whose keys include the row's own position does the same for that key, takes the value, stores both
+// in the page and uses them from shared memory. One launch instead of rotate-and-store plus attention.
+CUCA_API int cuca_attention_decode_fused(const float* partial, int n_slices, size_t slice_stride, const void* bias,
+                                         const float* cos_t, const float* sin_t, int table_rows, int rot, int has_kv,
+                                         void* out, int out_stride, void* kpool, void* vpool, int n_blocks, int bs,
+                                         const int* positions, const int* seq_of_row, const int* tables,
+                                         int table_stride, const int* rows, int n_rows, int nh, int nkv, int d,
+                                         float scale, int window, int chunk, int n_splits, float* part, int* counters,
+                                         int* err, cudaStream_t stream) {
+  FusedInput f{partial, n_slices, slice_stride, bias, cos_t, sin_t, table_rows, rot, has_kv};
+  return attention_decode_impl(nullptr, 2, &f, out, out_stride, kpool, vpool, n_blocks, bs, positions, seq_of_row,
+                               tables, table_stride, rows, n_rows, nh, nkv, d, scale, window, chunk, n_splits, part,
+                               counters, err, stream);
 }
 
 // Prefill form: tile i covers rows tile_row0[i] .. +tile_nrows[i]-1 (at most 64 consecutive rows of one request).
@@ -569,7 +716,9 @@ CUCA_API int cuca_attention_prefill(const void* q, int q_stride, void* out, int 
   p.rows = nullptr; p.tile_row0 = tile_row0; p.tile_nrows = tile_nrows; p.nh = nh; p.nkv = nkv;
   p.scale_log2e = scale * 1.4426950408889634f; p.window = window; p.chunk = 0; p.part = nullptr;
   p.counters = nullptr; p.err = err; p.slots = 1;
-  return dispatch<false>(d, p, dim3(n_tiles, nh), stream);
+  p.partial = nullptr; p.n_slices = 0; p.slice_stride = 0; p.bias = nullptr; p.cos_t = p.sin_t = nullptr;
+  p.table_rows = 0; p.rot = 0; p.has_kv = 0;
+  return dispatch<false, false>(d, p, dim3(n_tiles, nh), stream);
 }
 
 // ---------------------------------------------------------------------------------------------------------

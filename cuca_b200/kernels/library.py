@@ -39,6 +39,8 @@ _SIGNATURES = {
     "cuca_attention_mma_supported": [_I, _I, _I, _I, _I],
     "cuca_attention_decode": [_P, _I, _P, _I, _P, _P, _I, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _I, _I, _I,
                               _P, _P, _P, _P],
+    "cuca_attention_decode_fused": [_P, _I, c_size_t, _P, _P, _P, _I, _I, _I, _P, _I, _P, _P, _I, _I, _P, _P, _P, _I,
+                                    _P, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P, _P, _P],
     "cuca_attention_prefill": [_P, _I, _P, _I, _P, _P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _P,
                                _P],
     "cuca_decode_advance": [_P, _P, _P, _P, _P, _P, _I, _I, _P],

@@ -201,6 +201,30 @@ def attention_decode(q, q_stride, out, kpool, vpool, positions, seq_of_row, tabl
         float(scale), int(window or 0), chunk, n_splits, _p(part), _p(cnt), _p(err), _stream()), "attention_decode")
 
 
+def attention_decode_fused(partial, bias, cos, sin, rotary_dim, has_kv, out, kpool, vpool, positions, seq_of_row, tables,
+                           rows, n_rows, n_heads, n_kv_heads, head_dim, scale, window, chunk, n_splits, err) -> None:
+    """The decode form fed by the stacked q/k/v projection's unadded K slices (`PartialSums`): adds them, rotates
+    q and k, stores k and v in the pages and attends, in one launch. Every row of the step is a single token."""
+    lib = library.load()
+    part, cnt = attention_scratch(out.device, n_rows * n_heads * n_splits * (head_dim + 2), n_rows * n_kv_heads)
+    library.check(lib.cuca_attention_decode_fused(
+        _p(partial.data), partial.slices, partial.slice_stride, _p(bias), _p(cos), _p(sin),
+        cos.shape[0] if cos is not None else 0, int(rotary_dim), int(bool(has_kv)), _p(out), out.stride(0), _p(kpool),
+        _p(vpool), kpool.shape[0], kpool.shape[2], _p(positions), _p(seq_of_row), _p(tables), tables.shape[1], _p(rows),
+        n_rows, n_heads, n_kv_heads, head_dim, float(scale), int(window or 0), chunk, n_splits, _p(part), _p(cnt),
+        _p(err), _stream()), "attention_decode_fused")
+
+
+def attention_decode_fused_supported(step, cache, out_dtype, n_rows, n_heads, n_kv_heads, head_dim) -> bool:
+    """True when every row of the step is a single token of its request and the tensor-core decode form takes
+    the shape: then rotate-and-store and attention are one launch."""
+    plan = getattr(step, "attention_plan", None)
+    bs = cache.block_size
+    return (out_dtype == torch.bfloat16 and plan is not None and plan.n_decode == n_rows and plan.n_tiles == 0
+            and n_rows > 0 and bs & (bs - 1) == 0 and head_dim % 16 == 0
+            and attention_mma_supported(n_heads, n_kv_heads, head_dim, 2, n_heads * head_dim))
+
+
 def attention_prefill(q, q_stride, out, kpool, vpool, positions, seq_of_row, tables, tile_row0, tile_nrows, n_tiles,
                       n_heads, n_kv_heads, head_dim, scale, window, err) -> None:
     lib = library.load()

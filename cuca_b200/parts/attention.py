@@ -92,6 +92,17 @@ class PagedAttention(Mixer):
             # few tokens: the projection leaves its K slices unadded; rotate-and-store adds them in 32-bit
             cos, sin, rot = fused
             parts = ops.gemm_partial(h, self.w_qkv, self.rt.err)
+            if ops.attention_decode_fused_supported(step, cache, h.dtype, h.shape[0], nh, self.n_kv_heads, d):
+                # single tokens only: adding the slices, rotation, the page write and attention are one launch
+                attn = self.rt.empty(h.shape[0], nh * d)
+                plan = step.attention_plan
+                chunk, n_splits = plan.chunk(self.n_kv_heads, d)
+                ops.attention_decode_fused(parts, self.b_qkv, cos, sin, rot, nkv > 0, attn, cache.k, cache.v,
+                                           step.positions, step.seq_of_row, cache.tables, plan.decode_rows,
+                                           plan.n_decode, nh, self.n_kv_heads, d, self.scale, self.window, chunk,
+                                           n_splits, self.rt.err)
+                self.rt.linear_into_stream(attn, self.w_o, stream, bias=self.b_o)
+                return
             q = self.rt.empty(h.shape[0], nh * d)
             ops.rope_store_partial(parts, self.b_qkv, q, step.positions, step.seq_of_row, cache.tables, cos, sin, rot,
                                    kpool, vpool, cache.block_size, nh, nkv, d, self.rt.err)

@@ -291,6 +291,66 @@ def test_attention_decode_mma(dev, nh, nkv, d, bs, window, chunk):
 
 
 @pytest.mark.parametrize("nh,nkv,d,bs,window", MMA_SHAPES)
+@pytest.mark.parametrize("chunk,partial_rotary,has_kv", [(64, False, True), (0, True, True), (0, False, False)])
+def test_attention_decode_fused_with_rotation_and_store(dev, nh, nkv, d, bs, window, chunk, partial_rotary, has_kv):
+    """The decode form fed by the projection's K slices: it adds them, rotates q and k, writes k and v to the page
+    and attends, against the same steps done one by one in 32-bit. The page slot of the new position holds a
+    large stale value beforehand, so a read of the page instead of the new key would show."""
+    from cuca_b200.kernels import ops
+    from cuca_b200.parts.rope import rope_tables
+    dtype = torch.bfloat16
+    lens = [1, 2, 16, 17, 64, 65, 129, 300, 513]
+    k, v, kpool, vpool, tables = _paged_setup(dev, dtype, lens, nh, nkv, d, bs,
+                                              n_blocks=sum(-(-l // bs) for l in lens) + 5, seed=5)
+    rot = d // 2 if partial_rotary else d
+    cos, sin = rope_tables(600, rot, 10000.0)
+    cos, sin = cos.to(dev), sin.to(dev)
+    g = torch.Generator(device=dev).manual_seed(4)
+    T = len(lens) + 1  # the last row is padding
+    width = (nh + (2 * nkv if has_kv else 0)) * d
+    slices = torch.randn(3, T, width, device=dev, generator=g) * 0.6
+    bias = (torch.randn(width, device=dev, generator=g) * 0.1).to(dtype)
+    total = slices.sum(0) + bias.float()
+    positions = torch.zeros(T, dtype=torch.int32, device=dev)
+    seq = torch.full((T,), -1, dtype=torch.int32, device=dev)
+
+    def rotate(x, p):
+        c, s_ = cos[p], sin[p]
+        a, b = x[:, :rot // 2], x[:, rot // 2:rot]
+        return torch.cat([a * c - b * s_, a * s_ + b * c, x[:, rot:]], dim=1)
+
+    ref, new_kv = {}, {}
+    for s, l in enumerate(lens):
+        pos = l - 1
+        positions[s], seq[s] = pos, s
+        heads = total[s].view(-1, d)
+        q = rotate(heads[:nh], pos).to(dtype).float()
+        ks, vs = k[s].to(dtype).float().clone(), v[s].to(dtype).float().clone()
+        page, off = int(tables[s, pos // bs]), pos % bs
+        if has_kv:
+            ks[pos] = rotate(heads[nh:nh + nkv], pos).to(dtype).float()
+            vs[pos] = heads[nh + nkv:].to(dtype).float()
+            new_kv[s] = (page, off, ks[pos], vs[pos])
+            kpool[page, :, off] = 100.0  # stale
+            vpool[page, :, off] = 100.0
+        ref[s] = _ref_attention(q, ks, vs, pos, 1.0 / math.sqrt(d), window)
+    out = torch.zeros(T, nh * d, device=dev, dtype=dtype)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    n_splits = -(-max(lens) // chunk) if chunk else 5
+    ops.attention_decode_fused(ops.PartialSums(slices, 3), bias, cos, sin, rot, has_kv, out, kpool, vpool, positions,
+                               seq, tables, None, T, nh, nkv, d, 1.0 / math.sqrt(d), window, chunk, n_splits, err)
+    assert int(err.item()) == 0
+    for s in range(len(lens)):
+        got = out[s].float().view(nh, d)
+        assert torch.allclose(got, ref[s], atol=3e-2, rtol=3e-2), (s, float((got - ref[s]).abs().max()))
+        if has_kv:
+            page, off, kn, vn = new_kv[s]
+            assert torch.allclose(kpool[page, :, off].float(), kn, atol=2e-2, rtol=2e-2)
+            assert torch.allclose(vpool[page, :, off].float(), vn, atol=2e-2, rtol=2e-2)
+    assert float(out[-1].abs().sum()) == 0
+
+
+@pytest.mark.parametrize("nh,nkv,d,bs,window", MMA_SHAPES)
 def test_attention_prefill_mma(dev, nh, nkv, d, bs, window):
     """Prefill attention on tensor cores: portions that start at position 0 and in the middle of a request
     (keys partly from earlier steps), tiles of 64 rows and ragged tails, against 32-bit attention."""
