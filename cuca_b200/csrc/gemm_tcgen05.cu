@@ -1,7 +1,9 @@
 // bfloat16 contraction on the 5th-generation tensor cores: out = epilogue(X[M,K] W[N,K]^T).
 //
-// A persistent, warp-specialised kernel: one warp streams tiles with TMA (128-byte swizzle) into a ring of
-// shared-memory stages, one thread issues tcgen05.mma (kind::f16, 32-bit accumulate) into one of two TMEM
+// A persistent, warp-specialised kernel: two threads (of two warps, taking stages in turn: one thread alone requests
+// about 16 KB per 0.45 us, less than an SM's share of the memory's rate) stream tiles with TMA (128-byte swizzle)
+// into a ring of shared-memory stages; over few tokens the weights carry the L2 hint "evict first", since a decode
+// step reads each weight once and far more of them than L2 holds; one thread issues tcgen05.mma (kind::f16, 32-bit accumulate) into one of two TMEM
 // accumulators, and four warps drain the other accumulator with tcgen05.ld and run the epilogue (store, bias,
 // add into the 32-bit residual stream, or SwiGLU), so the epilogue of one tile overlaps the main loop of the
 // next. tcgen05.commit hands stages back to the producer and accumulators to the epilogue.
@@ -20,8 +22,7 @@
 // The kernel is a programmatic dependent: it requests its first ring of weight tiles before waiting for its
 // predecessor, since weights are never written. Every wait on an mbarrier is bounded; on a timeout the kernel
 // records CUCA_ERR_WAIT_TIMEOUT, every role stops, copies in flight land, TMEM is freed and the kernel returns.
-#include "common.cuh"
-#include <cuda.h>
+#include "tcgen05.cuh"
 #include <mutex>
 #include <unordered_map>
 #include <string.h>
@@ -34,128 +35,8 @@
 
 namespace {
 
-constexpr int TILE_A = 128;  // rows of the MMA's M operand = TMEM lanes
-constexpr int TILE_K = 64;   // bf16 elements per stage row = 128 bytes = one swizzle span
-constexpr int UMMA_K = 16;
-constexpr int NTHREADS = 192;  // warp 0 producer, warp 1 MMA, warps 2..5 epilogue
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
-
-// ------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait: false if the phase did not complete in WAIT_LIMIT_NS (the error word is set) or if another
-// role of this CTA gave up (`abort` is set).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, volatile int* abort) {
-  if (mbar_try_wait(bar, parity)) return true;
-  unsigned long long t0 = global_ns();
-  unsigned spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 63u) == 0) {
-      if (*abort) return false;
-      if (global_ns() - t0 > WAIT_LIMIT_NS) {
-        if (err) atomicExch(err, CUCA_ERR_WAIT_TIMEOUT);
-        *abort = 1;
-        return false;
-      }
-    }
-  }
-  return true;
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
-      : "memory");
-}
-// Bring a tile of the tensor into L2 without a destination in shared memory.
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int c0, int c1) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t* dst, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst)), "r"(ncols)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-      "}\n" ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
-  uint32_t r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// Shared-memory operand descriptor: K-major tile of 128-byte rows, 128-byte swizzle,
-// 8-row groups 1024 bytes apart; the tile base is 1024-byte aligned.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)1 << 16;                  // leading byte offset: unused with a swizzled K-major tile
-  d |= (uint64_t)(1024 >> 4) << 32;        // stride byte offset between 8-row groups
-  d |= (uint64_t)1 << 46;                  // descriptor version of sm_100
-  d |= (uint64_t)2 << 61;                  // 128-byte swizzle
-  return d;
-}
-// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128, N = n.
-__host__ __device__ constexpr uint32_t instr_desc(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_A >> 4) << 24);
-}
-
+constexpr int NTHREADS = 224;  // warps 0 and 6 producers, warp 1 MMA, warps 2..5 epilogue
+constexpr int NPROD = 2;       // one thread requests about 16 KB per 0.45 us: too little for an SM's share of the memory's rate
 
 struct Params {
   void* out;
@@ -349,7 +230,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   // With late_trigger the producer and MMA threads call pdl_trigger() only when their stream is fully requested,
   // so the next kernel's CTAs move in (and request their own weights) while this kernel drains, not while it
   // still streams; everyone else calls it now.
-  if (!p.late_trigger || !((warp == 0 || warp == 1) && lane == 0)) pdl_trigger();
+  if (!p.late_trigger || !((warp == 0 || warp == 1 || warp == 6) && lane == 0)) pdl_trigger();
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(&full[s], 1);
@@ -378,10 +259,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     b0 = (tile / p.tiles_a) * C::OUT_COLS;
   };
   // weights and activations of one stage: which is which depends on the orientation
+  // few tokens: every weight is read once per step, so it should not displace what is read again (activations,
+  // partial sums, keys and values)
+  const uint64_t once = SWAP ? l2_evict_first() : 0;
   auto load_weights = [&](uint8_t* st, uint64_t* bar, int a0, int b0, int kc) {
     if (SWAP) {
-      tma_load_2d(st, &tmA, bar, kc, a0);
-      if (DUAL) tma_load_2d(st + TILE_A * TILE_K * 2, &tmA, bar, kc, p.N + a0);
+      tma_load_2d_hint(st, &tmA, bar, kc, a0, once);
+      if (DUAL) tma_load_2d_hint(st + TILE_A * TILE_K * 2, &tmA, bar, kc, p.N + a0, once);
     } else {
       tma_load_2d(st + C::A_BYTES, &tmB, bar, kc, b0);
       tma_load_2d(st + C::A_BYTES + 128 * TILE_K * 2, &tmB, bar, kc, DUAL ? p.N + b0 : b0 + 128);
@@ -401,8 +285,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     else tma_load_2d(st, &tmA, bar, kc, a0);
   };
 
-  if (warp == 0 && lane == 0) {
-    // ------------------------------------------------ producer
+  if ((warp == 0 || warp == 6) && lane == 0) {
+    // ------------------------------------------------ producers: stages in turn (it mod NPROD)
+    const int mine = warp == 0 ? 0 : 1;
     // the first ring of weight tiles is requested before waiting for the predecessor kernel
     {
       SegmentWalk pre(p);
@@ -413,6 +298,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         int a0, b0;
         tile_origin(s.tile, a0, b0);
         for (int ks = s.ks0; ks < s.ks1 && it < ahead; ++ks, ++it) {
+          if (it % NPROD != mine) continue;
           if (it < C::STAGES) {
             mbar_expect_tx(&full[it], C::STAGE_BYTES);
             load_weights(smem + it * C::STAGE_BYTES, &full[it], a0, b0, ks * TILE_K);
@@ -431,6 +317,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int a0, b0;
       tile_origin(s.tile, a0, b0);
       for (int ks = s.ks0; ks < s.ks1; ++ks, ++it) {
+        if (it % NPROD != mine) continue;
         const int st = it % C::STAGES;
         uint8_t* sp = smem + st * C::STAGE_BYTES;
         if (it >= C::STAGES) {
@@ -476,7 +363,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       ++seg;
     }
     if (p.late_trigger) pdl_trigger();
-  } else if (warp >= 2) {
+  } else if (warp >= 2 && warp <= 5) {
     // ------------------------------------------------ epilogue: four warps, one TMEM lane per thread
     pdl_wait();
     const int quarter = warp & 3;               // the TMEM lanes this warp may read
@@ -591,7 +478,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 }
 
 // ------------------------------------------------------------------ host side
-int device_sms() {
+}  // namespace
+int cuca_device_sms() {
   static int sms = 0;
   if (!sms) {
     int dev = 0;
@@ -602,6 +490,7 @@ int device_sms() {
   return sms;
 }
 
+namespace {
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -638,8 +527,10 @@ struct MapHash {
   }
 };
 
-// Tensor map of a row-major bf16 matrix [rows, cols] with `stride` elements between rows; box = box_rows x 64.
-bool tensor_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_t stride, uint32_t box_rows, CUtensorMap* out) {
+}  // namespace
+
+bool cuca_tensor_map_bf16(const void* ptr, uint64_t rows, uint64_t cols, uint64_t stride, uint32_t box_rows,
+                          CUtensorMap* out) {
   static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
   static std::mutex mu;
   MapKey key{ptr, rows, cols, stride, box_rows};
@@ -663,6 +554,7 @@ bool tensor_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_t stride, 
   return true;
 }
 
+namespace {
 template <int BN, bool DUAL, bool SWAP>
 int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, int grid, cudaStream_t stream) {
   using C = Cfg<BN, DUAL, SWAP>;
@@ -707,11 +599,11 @@ static int gemm_tc_impl(const void* A, const void* W, const void* bias, void* ou
   const uint64_t w_rows = (uint64_t)N * (dual ? 2 : 1);
   CUtensorMap tmA, tmB;
   if (swap) {
-    CUCA_REQUIRE(tensor_map(W, w_rows, K, K, TILE_A, &tmA), "gemm_tc: weight tensor map failed");
-    CUCA_REQUIRE(tensor_map(A, M, K, lda, bn, &tmB), "gemm_tc: activation tensor map failed");
+    CUCA_REQUIRE(cuca_tensor_map_bf16(W, w_rows, K, K, TILE_A, &tmA), "gemm_tc: weight tensor map failed");
+    CUCA_REQUIRE(cuca_tensor_map_bf16(A, M, K, lda, bn, &tmB), "gemm_tc: activation tensor map failed");
   } else {
-    CUCA_REQUIRE(tensor_map(A, M, K, lda, TILE_A, &tmA), "gemm_tc: activation tensor map failed");
-    CUCA_REQUIRE(tensor_map(W, w_rows, K, K, 128, &tmB), "gemm_tc: weight tensor map failed");
+    CUCA_REQUIRE(cuca_tensor_map_bf16(A, M, K, lda, TILE_A, &tmA), "gemm_tc: activation tensor map failed");
+    CUCA_REQUIRE(cuca_tensor_map_bf16(W, w_rows, K, K, 128, &tmB), "gemm_tc: weight tensor map failed");
   }
   Params p;
   p.out = out; p.bias = (const __nv_bfloat16*)bias; p.workspace = (float*)workspace; p.counters = counters;
@@ -731,7 +623,7 @@ static int gemm_tc_impl(const void* A, const void* W, const void* bias, void* ou
   }
   p.l2_ahead = env_l2;
   p.late_trigger = env_late;
-  const int sms = device_sms();
+  const int sms = cuca_device_sms();
   const long long units = (long long)p.tiles * p.ksteps;
   int grid = p.tiles < sms ? p.tiles : sms;
   p.stream_k = 0;
@@ -801,7 +693,7 @@ CUCA_API int cuca_gemm_tc(const void* A, const void* W, const void* bias, void* 
 // How many K slices cuca_gemm_tc_partial will write for this shape (the first dimension of its output).
 CUCA_API int cuca_gemm_tc_partial_slices(int M, int N, int K, int max_slices) {
   if (M > 64 || M <= 0 || N <= 0 || K <= 0) return 0;
-  const int sms = device_sms();
+  const int sms = cuca_device_sms();
   const int tiles = (N + TILE_A - 1) / TILE_A, ksteps = (K + TILE_K - 1) / TILE_K;
   int per_tile = sms / tiles;
   if (per_tile > max_slices) per_tile = max_slices;
