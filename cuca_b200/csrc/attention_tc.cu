@@ -1,34 +1,50 @@
 // Paged causal attention for prompt portions on the 5th-generation tensor cores (bfloat16, head size 128).
 //
 // A CTA takes up to 128 consecutive rows of one request and one query head and walks the request's keys in
-// tiles of 128 positions. Both contractions run as tcgen05.mma with accumulators in tensor memory:
+// tiles of 64 positions. Both contractions run as tcgen05.mma with accumulators in tensor memory:
 //
-//   S[128 rows, 128 keys]  = Q K^T        (Q and K tiles K-major in shared memory, loaded by TMA from the
+//   S[128 rows, 64 keys]   = Q K^T        (Q and K tiles K-major in shared memory, loaded by TMA from the
 //                                          q buffer and straight from the pages through the block table)
 //   O[128 rows, head size] += P V         (P written to shared memory by the softmax threads as the K-major
 //                                          A operand; V tiles as loaded, i.e. the MN-major B operand)
 //
-// Warp 0 issues TMA, one thread of warp 1 issues the MMAs, warps 2..5 own one query row per thread (= one
-// TMEM lane): they read S with tcgen05.ld, scale, mask (causal, window), keep the running maximum and sum in
-// 32-bit, rescale O in tensor memory, and hand P back. Softmax and the tensor pipe alternate per tile.
+// Warp 0 issues TMA, one thread of warp 1 issues the MMAs, four warps per query tile own one query row per
+// thread (= one TMEM lane): they read S with tcgen05.ld, scale, mask (causal, window), keep the running maximum and sum in
+// 32-bit, rescale O in tensor memory, and hand P back.
+//
+// A kernel that allocates tensor memory gets one CTA per SM, so the overlap of softmax and tensor pipe has to
+// happen inside the CTA: it takes the same rows for TWO query heads of one key/value head (when the group size is
+// even; else one), with four softmax warps each. Both tiles read the same K and V tiles; while the softmax threads
+// of one work on its scores, the tensor pipe runs the other's P V and its next scores.
 //
 // Every mbarrier wait is bounded; on a timeout the kernel records CUCA_ERR_WAIT_TIMEOUT, all roles stop, TMEM
 // is freed and the kernel returns.
 #include "common.cuh"
 #include <cuda.h>
 #include <math.h>
+#include <stdlib.h>
 #include <mutex>
 #include <unordered_map>
 
 namespace {
 
 constexpr int D = 128;        // head size
-constexpr int ROWS = 128;     // query rows per CTA = TMEM lanes
-constexpr int KEYS = 128;     // keys per tile
-constexpr int KV_STAGES = 2;
-constexpr int HALF_BYTES = 128 * 128;            // one [128 rows][64 elements] swizzled block: 16 KB
-constexpr int TILE_BYTES = 2 * HALF_BYTES;       // [2 halves of 64 columns][128 rows][128 B]
-constexpr int NTHREADS = 192;
+constexpr int ROWS = 128;     // query rows per tile = TMEM lanes
+constexpr int KEYS = 64;      // keys per tile
+constexpr int NQ = 2;         // query tiles per CTA (two query heads of one key/value group, same rows)
+constexpr int KV_STAGES = 3;
+// Tiles are stored as 64-element halves: [halves][rows][128 B], 128-byte swizzled.
+constexpr int Q_HALF = ROWS * 128;               // 16 KB; a Q tile has D / 64 = 2 of them
+constexpr int Q_BYTES = (D / 64) * Q_HALF;
+constexpr int P_HALF = ROWS * 128;               // a P tile [rows][keys] has KEYS / 64 of them
+constexpr int P_BYTES = (KEYS / 64) * P_HALF;
+constexpr int KV_HALF = KEYS * 128;              // a K or V tile [keys][D] has D / 64 = 2 of them
+constexpr int KV_TILE = (D / 64) * KV_HALF;
+constexpr int TILES_BYTES = NQ * (Q_BYTES + P_BYTES) + KV_STAGES * 2 * KV_TILE;   // 192 KB
+constexpr int BAR_BYTES = 256;                   // mbarriers, the TMEM address, the abort flag: behind the tiles
+constexpr int DYN_SMEM = TILES_BYTES + BAR_BYTES + 1024;  // + what aligning the tiles to 1024 bytes may cost
+constexpr int TMEM_COLS = 512;                   // S of both tiles (2 x 64 columns), O of both (2 x 128)
+constexpr int NTHREADS = 64 + NQ * 128;          // warp 0 TMA, warp 1 MMA, four softmax warps per query tile
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
 struct Params {
@@ -41,6 +57,7 @@ struct Params {
   const int* tile_row0;
   const int* tile_nrows;
   int n_blocks, bs, nh, nkv;
+  int heads_per_cta;     // 2: a CTA takes two query heads of one key/value head (even group size); else 1
   float scale_log2e;
   int window;
   int* err;
@@ -109,7 +126,6 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void softmax_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   uint32_t r[32];
@@ -183,9 +199,9 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t lbo, ui
   d |= (uint64_t)2 << 61;
   return d;
 }
-// bf16 x bf16 -> f32, M = 128, N = 128; b_mn: the B operand is MN-major
-__host__ __device__ constexpr uint32_t instr_desc(bool b_mn) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(128 >> 3) << 17) |
+// bf16 x bf16 -> f32, M = 128, N = n; b_mn: the B operand is MN-major
+__host__ __device__ constexpr uint32_t instr_desc(bool b_mn, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
          ((uint32_t)(128 >> 4) << 24);
 }
 
@@ -194,28 +210,35 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                const __grid_constant__ CUtensorMap tmV, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* q_s = smem;                                  // Q tile, 32 KB
-  uint8_t* p_s = smem + TILE_BYTES;                     // P tile, 32 KB
-  uint8_t* kv_s = smem + 2 * TILE_BYTES;                // KV_STAGES x (K tile + V tile)
-  uint64_t* bars = (uint64_t*)(kv_s + KV_STAGES * 2 * TILE_BYTES);
+  uint8_t* q_s = smem;                                  // NQ Q tiles
+  uint8_t* p_s = q_s + NQ * Q_BYTES;                    // NQ P tiles
+  uint8_t* kv_s = p_s + NQ * P_BYTES;                   // KV_STAGES x (K tile + V tile)
+  uint64_t* bars = (uint64_t*)(kv_s + KV_STAGES * 2 * KV_TILE);
   uint64_t* q_full = bars;
   uint64_t* kv_full = bars + 1;              // [KV_STAGES]
   uint64_t* kv_empty = kv_full + KV_STAGES;  // [KV_STAGES]
-  uint64_t* s_full = kv_empty + KV_STAGES;   // S is in tensor memory
-  uint64_t* p_full = s_full + 1;             // P is in shared memory and O is rescaled (128 arrivals)
-  uint64_t* pv_done = p_full + 1;            // the P V contraction of a tile has finished
-  uint32_t* tmem_slot = (uint32_t*)(pv_done + 1);
+  uint64_t* s_full = kv_empty + KV_STAGES;   // [NQ] the scores of a tile are in tensor memory
+  uint64_t* p_full = s_full + NQ;            // [NQ] P is in shared memory and O is rescaled (128 arrivals)
+  uint64_t* pv_done = p_full + NQ;           // [NQ] the P V contraction of a tile has finished
+  uint32_t* tmem_slot = (uint32_t*)(pv_done + NQ);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   pdl_trigger();
   pdl_wait();
-  const int tile = blockIdx.x, head = blockIdx.y;
+  if (smem + TILES_BYTES + BAR_BYTES > smem_raw + DYN_SMEM) {
+    if (threadIdx.x == 0 && p.err) atomicExch(p.err, CUCA_ERR_SMEM_LAYOUT);
+    return;
+  }
+  // This CTA's query tiles: the same rows for `nq` consecutive query heads, which share their key/value head.
+  const int tile = blockIdx.x;
+  const int nq = p.heads_per_cta;             // 1 or NQ
+  const int head0 = blockIdx.y * nq;
   const int row0 = p.tile_row0[tile], n_rows = p.tile_nrows[tile];
   const int seq = p.seq_of_row[row0];
   if (seq < 0) return;
   const int pos0 = p.positions[row0];
-  const int kvh = head / (p.nh / p.nkv);
+  const int kvh = head0 / (p.nh / p.nkv);
   const int lo_min = (p.window > 0 && pos0 - (p.window - 1) > 0) ? pos0 - (p.window - 1) : 0;
   const int hi = pos0 + n_rows;                       // keys [lo_min, hi) matter
   const int first_tile = lo_min / KEYS;
@@ -225,34 +248,40 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    mbar_init(s_full, 1);
-    mbar_init(p_full, 128);
-    mbar_init(pv_done, 1);
+    for (int x = 0; x < NQ; ++x) {
+      mbar_init(&s_full[x], 1);
+      mbar_init(&p_full[x], 128);
+      mbar_init(&pv_done[x], 1);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 256);
+    tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
+  // tile x: scores in columns [64 x, 64 x + 64), output in [128 + 128 x, 256 + 128 x)
+  auto tmem_s = [&](int x) { return tmem_base + (uint32_t)(x * KEYS); };
+  auto tmem_o = [&](int x) { return tmem_base + (uint32_t)(NQ * KEYS + x * D); };
 
   if (warp == 0 && lane == 0) {
-    // ------------------------------------------------ producer: Q once, then K and V tiles page by page
-    mbar_expect_tx(q_full, TILE_BYTES);
-    tma_load_2d(q_s, &tmQ, q_full, head * D, row0);
-    tma_load_2d(q_s + HALF_BYTES, &tmQ, q_full, head * D + 64, row0);
+    // ------------------------------------------------ producer: the Q tiles once, then K and V tiles page by page
+    mbar_expect_tx(q_full, nq * Q_BYTES);
+    for (int x = 0; x < nq; ++x) {
+      tma_load_2d(q_s + x * Q_BYTES, &tmQ, q_full, (head0 + x) * D, row0);
+      tma_load_2d(q_s + x * Q_BYTES + Q_HALF, &tmQ, q_full, (head0 + x) * D + 64, row0);
+    }
     const int pages = KEYS / p.bs;
     for (int j = 0; j < n_tiles; ++j) {
       const int s = j % KV_STAGES;
       if (j >= KV_STAGES && !mbar_wait(&kv_empty[s], ((j / KV_STAGES) & 1) ^ 1, p.err, abort_flag)) break;
-      uint8_t* ks = kv_s + s * 2 * TILE_BYTES;
-      uint8_t* vs = ks + TILE_BYTES;
-      mbar_expect_tx(&kv_full[s], 2 * TILE_BYTES);
+      uint8_t* ks = kv_s + s * 2 * KV_TILE;
+      uint8_t* vs = ks + KV_TILE;
+      mbar_expect_tx(&kv_full[s], 2 * KV_TILE);
       const int key0 = (first_tile + j) * KEYS;
       for (int pg = 0; pg < pages; ++pg) {
         int kp = key0 + pg * p.bs;
@@ -265,66 +294,83 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const int grow = (blk * p.nkv + kvh) * p.bs;  // row of the page in the pool seen as [rows][D]
         const int off = pg * p.bs * 128;              // bytes: bs rows of 128 B inside a half
         tma_load_2d(ks + off, &tmK, &kv_full[s], 0, grow);
-        tma_load_2d(ks + HALF_BYTES + off, &tmK, &kv_full[s], 64, grow);
+        tma_load_2d(ks + KV_HALF + off, &tmK, &kv_full[s], 64, grow);
         tma_load_2d(vs + off, &tmV, &kv_full[s], 0, grow);
-        tma_load_2d(vs + HALF_BYTES + off, &tmV, &kv_full[s], 64, grow);
+        tma_load_2d(vs + KV_HALF + off, &tmV, &kv_full[s], 64, grow);
       }
     }
   } else if (warp == 1 && lane == 0) {
     // ------------------------------------------------ MMA issuer
-    constexpr uint32_t idesc_qk = instr_desc(false), idesc_pv = instr_desc(true);
+    // The two query tiles take turns: while the softmax threads of one work on its scores, the tensor pipe runs
+    // the other's P V and its next scores. Per key tile j: P V of tile 0, scores j + 1 of tile 0, P V of tile 1,
+    // scores j + 1 of tile 1; the key tile is handed back after the last P V that reads its values.
+    constexpr uint32_t idesc_qk = instr_desc(false, KEYS), idesc_pv = instr_desc(true, D);
     bool ok = mbar_wait(q_full, 0, p.err, abort_flag);
-    for (int j = 0; ok && j < n_tiles; ++j) {
-      const int s = j % KV_STAGES;
-      if (!mbar_wait(&kv_full[s], (j / KV_STAGES) & 1, p.err, abort_flag)) break;
-      tc_fence_after();
-      const uint32_t qa = smem_u32(q_s), ka = smem_u32(kv_s + s * 2 * TILE_BYTES), va = ka + TILE_BYTES;
-      // S = Q K^T: 8 steps of 16 head dimensions; a step moves 32 bytes inside a 64-wide half
+    auto scores = [&](int x, int t) {  // S_x = Q_x K_t^T: 8 steps of 16 head dimensions, 32 bytes inside a 64-wide half
+      const uint32_t qa = smem_u32(q_s + x * Q_BYTES);
+      const uint32_t ka = smem_u32(kv_s + (t % KV_STAGES) * 2 * KV_TILE);
 #pragma unroll
       for (int k = 0; k < D / 16; ++k) {
-        const uint32_t off = (k / 4) * HALF_BYTES + (k % 4) * 32;
-        umma_bf16(tmem_s, desc_kmajor(qa + off), desc_kmajor(ka + off), idesc_qk, k > 0);
+        const uint32_t in_half = (k % 4) * 32;
+        umma_bf16(tmem_s(x), desc_kmajor(qa + (k / 4) * Q_HALF + in_half), desc_kmajor(ka + (k / 4) * KV_HALF + in_half),
+                  idesc_qk, k > 0);
       }
-      umma_commit(s_full);
-      // O += P V once the softmax threads have written P and rescaled O
-      if (!mbar_wait(p_full, j & 1, p.err, abort_flag)) break;
+      umma_commit(&s_full[x]);
+    };
+    if (ok) ok = mbar_wait(&kv_full[0], 0, p.err, abort_flag);
+    if (ok) {
       tc_fence_after();
-      const uint32_t pa = smem_u32(p_s);
+      for (int x = 0; x < nq; ++x) scores(x, 0);
+    }
+    for (int j = 0; ok && j < n_tiles; ++j) {
+      const int s = j % KV_STAGES;
+      const uint32_t va = smem_u32(kv_s + s * 2 * KV_TILE) + KV_TILE;
+      if (j + 1 < n_tiles) ok = mbar_wait(&kv_full[(j + 1) % KV_STAGES], ((j + 1) / KV_STAGES) & 1, p.err, abort_flag);
+      for (int x = 0; ok && x < nq; ++x) {
+        // O_x += P_x V_j once the softmax threads of tile x have written P and rescaled O
+        if (!mbar_wait(&p_full[x], j & 1, p.err, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t pa = smem_u32(p_s + x * P_BYTES);
 #pragma unroll
-      for (int k = 0; k < KEYS / 16; ++k) {
-        // A = P[rows][keys] K-major: 16 keys = 32 bytes inside a 64-key half.
-        // B = V[keys][dims] MN-major: 16 keys = two 8-key groups of 1024 bytes; dims 64..127 in the second half.
-        const uint32_t aoff = (k / 4) * HALF_BYTES + (k % 4) * 32;
-        umma_bf16(tmem_o, desc_kmajor(pa + aoff), desc_mnmajor(va + k * 2048, HALF_BYTES, 1024), idesc_pv,
-                  (j > 0 || k > 0));
+        for (int k = 0; k < KEYS / 16; ++k) {
+          // A = P[rows][keys] K-major: 16 keys = 32 bytes inside a 64-key half.
+          // B = V[keys][dims] MN-major: 16 keys = two 8-key groups of 1024 bytes; dims 64..127 in the second half.
+          const uint32_t aoff = (k / 4) * P_HALF + (k % 4) * 32;
+          umma_bf16(tmem_o(x), desc_kmajor(pa + aoff), desc_mnmajor(va + k * 2048, KV_HALF, 1024), idesc_pv,
+                    (j > 0 || k > 0));
+        }
+        if (x == nq - 1) umma_commit(&kv_empty[s]);
+        umma_commit(&pv_done[x]);
+        if (j + 1 < n_tiles) scores(x, j + 1);  // its scores were read before P was handed over
       }
-      umma_commit(&kv_empty[s]);
-      umma_commit(pv_done);
     }
   } else if (warp >= 2) {
-    // ------------------------------------------------ softmax: one query row per thread
-    const int quarter = warp & 3;
+    // ------------------------------------------------ softmax: one query row per thread, four warps per tile
+    const int x = (warp - 2) >> 2;              // which query tile
+    const int quarter = warp & 3;               // the TMEM lanes this warp may touch
     const int r = quarter * 32 + lane;
     const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
     const bool row_ok = r < n_rows;
     const int row_pos = pos0 + r;
     const int row_lo = (p.window > 0 && row_pos - (p.window - 1) > 0) ? row_pos - (p.window - 1) : 0;
+    uint8_t* p_x = p_s + x * P_BYTES;
     float m = -INFINITY, l = 0.f;
-    bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
+    bool ok = x < nq;
+    for (int j = 0; ok && j < n_tiles; ++j) {
       // the tcgen05.ld/st below are warp-wide: a warp leaves the loop together or not at all
-      if (!__all_sync(0xffffffffu, mbar_wait(s_full, j & 1, p.err, abort_flag))) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[x], j & 1, p.err, abort_flag))) { ok = false; break; }
       tc_fence_after();
       const int key0 = (first_tile + j) * KEYS;
       const bool whole = key0 >= lo_min && key0 + KEYS - 1 <= pos0 && (p.window <= 0 || key0 >= pos0 + ROWS - 1 - (p.window - 1));
       // pass 1: the whole row of scores in one round trip to tensor memory, then scale, mask, maximum
-      uint32_t raw[4][32];
+      constexpr int NC = KEYS / 32;  // groups of 32 scores
+      uint32_t raw[NC][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32_nowait(tmem_s + lane_bits + c * 32, raw[c]);
+      for (int c = 0; c < NC; ++c) tmem_ld32_nowait(tmem_s(x) + lane_bits + c * 32, raw[c]);
       tmem_ld_wait();
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < NC; ++c) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           float v = __uint_as_float(raw[c][i]) * p.scale_log2e;
@@ -343,14 +389,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       if (mx > m + 8.f || m == -INFINITY) m_new = fmaxf(m, mx);
       const float corr = (m_new == -INFINITY || m == m_new) ? 1.f : fast_exp2(m - m_new);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      // the previous P V must have finished before O is rescaled and P is overwritten
-      if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(pv_done, (j - 1) & 1, p.err, abort_flag))) { ok = false; break; }
+      // the previous P V of this tile must have finished before O is rescaled and P is overwritten
+      if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(&pv_done[x], (j - 1) & 1, p.err, abort_flag))) { ok = false; break; }
       tc_fence_after();
       // pass 2: P = exp2(s - m) as bf16 into shared memory (K-major, 128-byte swizzle), row sum
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint8_t* half = p_s + (c / 2) * HALF_BYTES + r * 128;
+      for (int c = 0; c < NC; ++c) {
+        uint8_t* half = p_x + (c / 2) * P_HALF + r * 128;
 #pragma unroll
         for (int q8 = 0; q8 < 4; ++q8) {   // 8 keys = 16 bytes = one swizzle chunk
           uint32_t w[4];
@@ -374,25 +420,25 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           float o[32];
-          tmem_ld32(tmem_o + lane_bits + c * 32, o);
+          tmem_ld32(tmem_o(x) + lane_bits + c * 32, o);
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] *= corr;
-          tmem_st32(tmem_o + lane_bits + c * 32, o);
+          tmem_st32(tmem_o(x) + lane_bits + c * 32, o);
         }
         tmem_st_wait();
       }
       tc_fence_before();
       fence_async_smem();   // P was written through the generic proxy; the tensor core reads it through the async one
-      mbar_arrive(p_full);
+      mbar_arrive(&p_full[x]);
     }
-    if (ok && __all_sync(0xffffffffu, mbar_wait(pv_done, (n_tiles - 1) & 1, p.err, abort_flag))) {
+    if (ok && __all_sync(0xffffffffu, mbar_wait(&pv_done[x], (n_tiles - 1) & 1, p.err, abort_flag))) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = p.out + (size_t)(row0 + r) * p.out_stride + (size_t)head * D;
+      __nv_bfloat16* dst = p.out + (size_t)(row0 + r) * p.out_stride + (size_t)(head0 + x) * D;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         float o[32];
-        tmem_ld32(tmem_o + lane_bits + c * 32, o);  // warp-wide: every lane reads, only rows of the tile store
+        tmem_ld32(tmem_o(x) + lane_bits + c * 32, o);  // warp-wide: every lane reads, only rows of the tile store
         if (row_ok) {
           uint32_t w[16];
 #pragma unroll
@@ -414,7 +460,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, 256);
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
 // ------------------------------------------------------------------ host side
@@ -466,7 +512,7 @@ bool tensor_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_t stride, 
 
 }  // namespace
 
-// 1 if the tcgen05 prefill attention takes this shape: head size 128, pages of 8..128 positions (a power of
+// 1 if the tcgen05 prefill attention takes this shape: head size 128, pages of 8..64 positions (a power of
 // two), rows of the q buffer and the pools 16-byte aligned.
 CUCA_API int cuca_attention_tc_supported(int nh, int nkv, int d, int bs, int q_stride, int out_stride, const void* q,
                                          const void* kpool, const void* vpool) {
@@ -499,7 +545,8 @@ CUCA_API int cuca_attention_prefill_tc(const void* q, int q_stride, int n_rows_t
   p.positions = positions; p.seq_of_row = seq_of_row; p.tile_row0 = tile_row0; p.tile_nrows = tile_nrows;
   p.n_blocks = n_blocks; p.bs = bs; p.nh = nh; p.nkv = nkv; p.scale_log2e = scale * 1.4426950408889634f;
   p.window = window; p.err = err;
-  const int smem = 2 * TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + 1024 + 256;
+  p.heads_per_cta = ((nh / nkv) % NQ == 0) ? NQ : 1;
+  const int smem = DYN_SMEM;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -507,7 +554,7 @@ CUCA_API int cuca_attention_prefill_tc(const void* q, int q_stride, int n_rows_t
                  cudaGetErrorString(e));
     configured = true;
   }
-  cuca_launch(attn_tc_kernel, dim3(n_tiles, nh), dim3(NTHREADS), smem, stream, true, tmQ, tmK, tmV, p);
+  cuca_launch(attn_tc_kernel, dim3(n_tiles, nh / p.heads_per_cta), dim3(NTHREADS), smem, stream, true, tmQ, tmK, tmV, p);
   CUCA_CHECK_LAUNCH("attention_prefill_tc");
   return 0;
 }

@@ -17,6 +17,7 @@
 #define CUCA_ERR_TOKEN_RANGE 1
 #define CUCA_ERR_BLOCK_RANGE 2
 #define CUCA_ERR_WAIT_TIMEOUT 3
+#define CUCA_ERR_SMEM_LAYOUT 4
 
 void cuca_set_error(const char* fmt, ...);
 extern "C" const char* cuca_last_error();

@@ -14,6 +14,7 @@ _ERR_TEXT = {
     1: "a token id or position outside its table reached a kernel",
     2: "a page id outside the pool, or a position without a page, reached a kernel",
     3: "a bounded wait inside a kernel ran out",
+    4: "a kernel found its shared memory laid out otherwise than its budget assumes",
 }
 
 
