@@ -228,8 +228,7 @@ def main() -> int:
         core.rt.check_device_errors()
         g = backend.graphs.get(batch, seqs[0].blocks.length, False)
         for s in list(seqs):
-            sched._release(s)
-            sched._finish(s, "length")
+            sched.cancel(s)
         sched.finished.clear()
         mean_ctx = ctx0 + (steps - 1) / 2.0 + 1
         return ms / steps, mean_ctx, g

@@ -8,11 +8,17 @@ one block table per group (src/provider/local/model/paged.rs:6-16,52-103,
 in a windowed group, as soon as the window has passed them
 (model/paged.rs:736-761). No tensors live here; `cache/device.py` owns the
 memory the page ids index.
+
+The books themselves are kept by the C++ host core (`csrc/host/kv_pools.cpp`);
+the classes here hold a handle and translate its status codes into exceptions.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+import ctypes
+from dataclasses import dataclass
 from typing import Optional
+
+from ..native import host
 
 NO_BLOCK = -1  # a table entry whose page was given back (behind a window)
 
@@ -36,6 +42,13 @@ class GroupLayout:
     n_blocks: int
 
 
+def _raise(code: int) -> None:
+    msg = host.last_error()
+    if code == host.EXHAUSTED:
+        raise PoolExhausted(msg or "the K/V page pool is exhausted")
+    raise CacheBookkeepingError(msg or f"cache bookkeeping error {code}")
+
+
 class BlockPool:
     """Free list of one group's pages; pops from the back, as the reference's does."""
 
@@ -43,46 +56,142 @@ class BlockPool:
         if n_blocks <= 0:
             raise ValueError("a pool needs at least one page")
         self.n_blocks = n_blocks
-        self._free = list(range(n_blocks - 1, -1, -1))
-        self._held = [False] * n_blocks
+        self._lib = host.load()
+        self._h = self._lib.cuca_host_blockpool_new(n_blocks)
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.cuca_host_blockpool_free(self._h)
+            self._h = None
 
     @property
     def free(self) -> int:
-        return len(self._free)
+        return self._lib.cuca_host_blockpool_free_count(self._h)
 
     @property
     def used(self) -> int:
-        return self.n_blocks - len(self._free)
+        return self.n_blocks - self.free
 
     def alloc(self) -> Optional[int]:
-        if not self._free:
-            return None
-        b = self._free.pop()
-        if self._held[b]:
-            raise CacheBookkeepingError(f"page {b} was on the free list while held")
-        self._held[b] = True
-        return b
+        b = self._lib.cuca_host_blockpool_alloc(self._h)
+        if b == -2:
+            raise CacheBookkeepingError("a page was on the free list while held")
+        return None if b < 0 else b
 
     def release(self, b: int) -> None:
-        if not 0 <= b < self.n_blocks or not self._held[b]:
+        if self._lib.cuca_host_blockpool_release(self._h, int(b)) != 0:
             raise CacheBookkeepingError(f"page {b} is freed but not held")
-        self._held[b] = False
-        self._free.append(b)
 
     def reset(self) -> None:
-        self._free = list(range(self.n_blocks - 1, -1, -1))
-        self._held = [False] * self.n_blocks
+        self._lib.cuca_host_blockpool_reset(self._h)
 
 
-@dataclass(eq=False)  # identity: two requests with equal tables are still two requests
+class _GroupPool:
+    """One group's pool inside `KvPools`, for reading its counts."""
+
+    def __init__(self, pools: "KvPools", gi: int):
+        self._pools, self._gi = pools, gi
+
+    @property
+    def n_blocks(self) -> int:
+        return self._pools._lib.cuca_host_pools_total_blocks(self._pools._h, self._gi)
+
+    @property
+    def free(self) -> int:
+        return self._pools._lib.cuca_host_pools_free_blocks(self._pools._h, self._gi)
+
+    @property
+    def used(self) -> int:
+        return self.n_blocks - self.free
+
+
+class _PerGroup:
+    """`first_live` / `dirty_from` of a request: a list-like view of one integer per group."""
+
+    def __init__(self, seq: "SeqBlocks", base: int):
+        self._seq, self._base = seq, base
+
+    def __len__(self):
+        return self._seq._pools.n_groups
+
+    def __getitem__(self, gi: int) -> int:
+        return self._seq._get(self._base + range(len(self))[gi])
+
+    def __setitem__(self, gi: int, value: int) -> None:
+        self._seq._set(self._base + range(len(self))[gi], int(value))
+
+    def __iter__(self):
+        return (self[i] for i in range(len(self)))
+
+    def __eq__(self, other):
+        return list(self) == list(other)
+
+    def __repr__(self):
+        return repr(list(self))
+
+
 class SeqBlocks:
-    """One request's block tables (one per group) and how many positions it has cached."""
+    """One request's block tables (one per group) and how many positions it has cached.
 
-    tables: list
-    length: int = 0
-    released: bool = False
-    first_live: list = field(default_factory=list)  # per group: index of the first table entry still held
-    dirty_from: list = field(default_factory=list)  # per group: table entries from here on are not yet on the device
+    Identity is the handle: two requests with equal tables are still two requests."""
+
+    __slots__ = ("_pools", "handle", "_owns", "__weakref__")
+
+    def __init__(self, pools: "KvPools", handle: int, owns: bool = True):
+        self._pools, self.handle, self._owns = pools, handle, owns
+
+    def __del__(self):
+        # the record goes back to the host core with its last owner (tables the scheduler made are the scheduler's)
+        try:
+            pools = self._pools
+            if self._owns and pools._h:
+                pools._lib.cuca_host_pools_drop_seq(pools._h, self.handle)
+        except Exception:  # interpreter shutdown
+            pass
+
+    def _get(self, field: int) -> int:
+        return self._pools._lib.cuca_host_seq_get(self._pools._h, self.handle, field)
+
+    def _set(self, field: int, value: int) -> None:
+        if self._pools._lib.cuca_host_seq_set(self._pools._h, self.handle, field, value) != 0:
+            raise CacheBookkeepingError(host.last_error())
+
+    @property
+    def length(self) -> int:
+        return self._get(0)
+
+    @length.setter
+    def length(self, value: int) -> None:
+        self._set(0, int(value))
+
+    @property
+    def released(self) -> bool:
+        return self._get(1) != 0
+
+    @property
+    def tables(self) -> list:
+        """A copy of the request's tables: one list of page ids per group."""
+        lib, h = self._pools._lib, self._pools._h
+        out = []
+        for gi in range(self._pools.n_groups):
+            n = lib.cuca_host_seq_table(h, self.handle, gi, None, 0)
+            buf = (ctypes.c_int * max(1, n))()
+            lib.cuca_host_seq_table(h, self.handle, gi, buf, n)
+            out.append(list(buf[:n]))
+        return out
+
+    @property
+    def first_live(self):
+        return _PerGroup(self, 2)
+
+    @property
+    def dirty_from(self):
+        return _PerGroup(self, 2 + self._pools.n_groups)
+
+    @dirty_from.setter
+    def dirty_from(self, values) -> None:
+        for gi, v in enumerate(values):
+            self._set(2 + self._pools.n_groups + gi, int(v))
 
 
 class KvPools:
@@ -93,114 +202,83 @@ class KvPools:
             raise ValueError("block size must be positive")
         self.groups = list(groups)
         self.block_size = block_size
-        self.pools = [BlockPool(g.n_blocks) for g in self.groups]
-        self._live: list = []
+        self.n_groups = len(self.groups)
+        for g in self.groups:
+            if g.n_blocks <= 0:
+                raise ValueError("a pool needs at least one page")
+        self._lib = host.load()
+        self._h = self._lib.cuca_host_pools_new(
+            self.n_groups, host.ints(g.n_blocks for g in self.groups),
+            host.ints(-1 if g.window is None else int(g.window) for g in self.groups), block_size)
+        if not self._h:
+            raise ValueError("the page pools could not be made")
+        self.pools = [_GroupPool(self, gi) for gi in range(self.n_groups)]
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            h, self._h = self._h, None
+            self._lib.cuca_host_pools_free(h)
 
     # ------------------------------------------------------------ requests
     def new_seq(self) -> SeqBlocks:
-        seq = SeqBlocks(tables=[[] for _ in self.groups], first_live=[0 for _ in self.groups],
-                        dirty_from=[0 for _ in self.groups])
-        self._live.append(seq)
-        return seq
+        return SeqBlocks(self, self._lib.cuca_host_pools_new_seq(self._h))
+
+    def adopt(self, handle: int) -> SeqBlocks:
+        """A view of tables that the host core made itself (the scheduler admits requests there)."""
+        return SeqBlocks(self, handle, owns=False)
 
     def blocks_for(self, tokens: int) -> int:
         return -(-tokens // self.block_size)
 
     def owed(self, seq: Optional[SeqBlocks], tokens: int) -> list:
         """Pages each group still has to give before the request can hold `tokens` positions."""
-        need = self.blocks_for(tokens)
-        if seq is None:
-            return [need for _ in self.groups]
-        return [max(0, need - len(t)) for t in seq.tables]
+        out = (ctypes.c_int * max(1, self.n_groups))()
+        self._lib.cuca_host_pools_owed(self._h, -1 if seq is None else seq.handle, int(tokens), out)
+        return list(out[:self.n_groups])
 
     def can_give(self, owed: list) -> bool:
-        return all(p.free >= o for p, o in zip(self.pools, owed))
+        return bool(self._lib.cuca_host_pools_can_give(self._h, host.ints(owed)))
 
     def reserve(self, seq: SeqBlocks, upto: int) -> None:
         """Give the request pages for positions < upto in every group; all or nothing."""
-        if seq.released:
-            raise CacheBookkeepingError("reserve on a released request")
-        owed = self.owed(seq, upto)
-        if not self.can_give(owed):
-            raise PoolExhausted("the K/V page pool is exhausted")
-        for table, pool, n in zip(seq.tables, self.pools, owed):
-            for _ in range(n):
-                table.append(pool.alloc())
+        code = self._lib.cuca_host_pools_reserve(self._h, seq.handle, int(upto))
+        if code:
+            _raise(code)
 
     def release_window(self, seq: SeqBlocks) -> int:
         """Give back pages that every later query of a windowed group has passed; returns how many."""
-        n = 0
-        for gi, (g, table, pool) in enumerate(zip(self.groups, seq.tables, self.pools)):
-            if g.window is None:
-                continue
-            # the next query sits at position seq.length and sees keys >= length - (window - 1)
-            first_needed = max(0, seq.length - (g.window - 1))
-            upto = min(first_needed // self.block_size, len(table))
-            for i in range(seq.first_live[gi], upto):
-                if table[i] != NO_BLOCK:
-                    pool.release(table[i])
-                    table[i] = NO_BLOCK
-                    n += 1
-            seq.first_live[gi] = max(seq.first_live[gi], upto)
+        n = self._lib.cuca_host_pools_release_window(self._h, seq.handle)
+        if n < 0:
+            _raise(host.BOOKKEEPING)
         return n
 
     def truncate(self, seq: SeqBlocks, length: int) -> None:
         """Roll the request back to `length` positions, giving back the pages beyond."""
-        keep = self.blocks_for(length)
-        for gi, (table, pool) in enumerate(zip(seq.tables, self.pools)):
-            while len(table) > keep:
-                b = table.pop()
-                if b != NO_BLOCK:
-                    pool.release(b)
-            seq.dirty_from[gi] = min(seq.dirty_from[gi], len(table))
-        seq.length = min(seq.length, length)
+        code = self._lib.cuca_host_pools_truncate(self._h, seq.handle, int(length))
+        if code:
+            _raise(code)
 
     def release(self, seq: SeqBlocks) -> None:
         """The request ended: every page it holds goes back."""
-        if seq.released:
-            raise CacheBookkeepingError("a request's pages are released twice")
-        for table, pool in zip(seq.tables, self.pools):
-            for b in table:
-                if b != NO_BLOCK:
-                    pool.release(b)
-            table.clear()
-        seq.released = True
-        self._live.remove(seq)
+        code = self._lib.cuca_host_pools_release(self._h, seq.handle)
+        if code:
+            _raise(code)
 
     def reset(self) -> None:
         """After a failed step: forget every request, every page is free again."""
-        for p in self.pools:
-            p.reset()
-        for s in self._live:
-            s.released = True
-            for t in s.tables:
-                t.clear()
-        self._live.clear()
+        self._lib.cuca_host_pools_reset(self._h)
 
     # ------------------------------------------------------------ accounting
     def check(self) -> None:
         """Every page is either free or held by exactly one live request."""
-        for gi, pool in enumerate(self.pools):
-            held = {}
-            for s in self._live:
-                for b in s.tables[gi]:
-                    if b == NO_BLOCK:
-                        continue
-                    if b in held:
-                        raise CacheBookkeepingError(f"group {gi}: page {b} is held twice")
-                    held[b] = s
-            free = set(pool._free)
-            if len(free) != len(pool._free):
-                raise CacheBookkeepingError(f"group {gi}: a page is on the free list twice")
-            if free & set(held):
-                raise CacheBookkeepingError(f"group {gi}: pages {sorted(free & set(held))} are free and held")
-            if len(free) + len(held) != pool.n_blocks:
-                lost = set(range(pool.n_blocks)) - free - set(held)
-                raise CacheBookkeepingError(f"group {gi}: pages {sorted(lost)} are lost")
+        code = self._lib.cuca_host_pools_check(self._h)
+        if code:
+            _raise(code)
 
     def stats(self) -> dict:
         return {"free_blocks": [p.free for p in self.pools], "used_blocks": [p.used for p in self.pools],
-                "total_blocks": [p.n_blocks for p in self.pools], "live_requests": len(self._live)}
+                "total_blocks": [p.n_blocks for p in self.pools],
+                "live_requests": self._lib.cuca_host_pools_live(self._h)}
 
 
 class StateSlots:
@@ -209,26 +287,25 @@ class StateSlots:
 
     def __init__(self, max_sequences: int):
         self.max_sequences = max_sequences
-        self._free = list(range(max_sequences))
-        self._held = [False] * max_sequences
+        self._lib = host.load()
+        self._h = self._lib.cuca_host_slots_new(max_sequences)
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            h, self._h = self._h, None
+            self._lib.cuca_host_slots_free(h)
 
     @property
     def free(self) -> int:
-        return len(self._free)
+        return self._lib.cuca_host_slots_free_count(self._h)
 
     def alloc(self) -> Optional[int]:
-        if not self._free:
-            return None
-        s = self._free.pop()
-        self._held[s] = True
-        return s
+        s = self._lib.cuca_host_slots_alloc(self._h)
+        return None if s < 0 else s
 
     def release(self, slot: int) -> None:
-        if not 0 <= slot < self.max_sequences or not self._held[slot]:
+        if self._lib.cuca_host_slots_release(self._h, int(slot)) != 0:
             raise CacheBookkeepingError(f"state slot {slot} is freed but not held")
-        self._held[slot] = False
-        self._free.append(slot)
 
     def reset(self) -> None:
-        self._free = list(range(self.max_sequences))
-        self._held = [False] * self.max_sequences
+        self._lib.cuca_host_slots_reset(self._h)

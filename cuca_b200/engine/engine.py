@@ -16,6 +16,7 @@ from ..config.engine_config import LocalModelConfig, SamplingConfig
 from ..config.model_config import read_config_json
 from ..config.registry import build_spec
 from ..kernels import ops
+from ..native import host
 from ..weights.loader import FolderSource
 from .core import EngineCore
 from .graphs import MAX_HISTORY, DecodeGraphs
@@ -81,18 +82,20 @@ class GpuBackend:
     def _table_updates(self, seqs) -> None:
         """Upload page-table entries that changed (new pages) for these requests."""
         core = self.core
-        W = core.cache.table_width
-        for gi in range(len(core.pools.groups)):
-            idx, val = [], []
-            for s in seqs:
-                table, lo = s.blocks.tables[gi], s.blocks.dirty_from[gi]
-                if lo < len(table):
-                    idx.extend(range(s.slot * W + lo, s.slot * W + len(table)))
-                    val.extend(table[lo:])
-                    s.blocks.dirty_from[gi] = len(table)
-            if idx:
-                dev = core.stepper._staging.upload(np.asarray(idx + val, dtype=np.int32))
-                ops.scatter_int(core.cache.tables[gi], dev[:len(idx)], dev[len(idx):])
+        lib, staging = host.load(), core.stepper._staging
+        n = len(seqs)
+        handles, slots = host.ints(s.blocks.handle for s in seqs), host.ints(s.slot for s in seqs)
+        for gi in range(core.pools.n_groups):
+            buf = staging.take()
+            count = lib.cuca_host_table_updates(core.pools._h, handles, slots, n, core.cache.table_width, gi,
+                                                buf.data_ptr(), buf.shape[0])
+            if count < 0:  # more new pages than the buffer holds: the widest case is every entry of every table
+                buf = staging.take(2 * n * core.cache.table_width)
+                count = lib.cuca_host_table_updates(core.pools._h, handles, slots, n, core.cache.table_width, gi,
+                                                    buf.data_ptr(), buf.shape[0])
+            if count > 0:
+                dev = staging.send(2 * count)
+                ops.scatter_int(core.cache.tables[gi], dev[:count], dev[count:])
 
     def _run_decode_graph(self, plans: Sequence[Plan]) -> list:
         seqs = [p.seq for p in plans]
@@ -103,12 +106,16 @@ class GpuBackend:
         g.load_rows([p.tokens[0] for p in plans], [s.blocks.length for s in seqs], [s.slot for s in seqs])
         g.replay()
         tokens = g.sampled[:n].tolist()  # the one synchronisation of a step
-        for s in seqs:
-            s.blocks.length += 1
-            self.core.pools.release_window(s.blocks)
+        self._advance(seqs, 1)
         self.core.stepper.steps += 1
         self.graph_steps += 1
         return tokens
+
+    def _advance(self, seqs, n_steps: int) -> None:
+        """Every request has `n_steps` more positions cached; pages behind windows go back."""
+        if host.load().cuca_host_step_advance(self.core.pools._h, host.ints(s.blocks.handle for s in seqs),
+                                              host.ints([n_steps] * len(seqs)), len(seqs)):
+            raise RuntimeError(host.last_error())
 
     def burst(self, seqs, tokens, n_steps: int):
         """`n_steps` decode steps back to back on the device, each feeding its sampled tokens to the next; the
@@ -126,8 +133,7 @@ class GpuBackend:
         g.counter.zero_()
         for _ in range(n_steps):
             g.replay()
-        for s in seqs:
-            s.blocks.length += n_steps
+        self._advance(seqs, n_steps)
         self.graph_steps += n_steps
         return g.history[:n_steps, :n]
 

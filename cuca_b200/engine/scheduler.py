@@ -24,13 +24,14 @@ This file decides; it touches no device. The `backend` runs a step and samples.
 """
 from __future__ import annotations
 
+import ctypes
 import time
 from collections import deque
 from dataclasses import dataclass, field
 from typing import Callable, Optional, Sequence
 
-from ..cache.pages import KvPools, PoolExhausted, StateSlots
-from .step import StepEntry
+from ..cache.pages import KvPools, StateSlots
+from ..native import host
 
 PREFILL, DECODE, ENDED = "prefill", "decode", "ended"
 _GOLDEN = 0x9E3779B97F4A7C15
@@ -77,6 +78,8 @@ class Sequence_:
     first_token_at: float = 0.0
     finished_at: float = 0.0
     preemptions: int = 0
+    core_id: int = -1  # the request's record in the host core (reused after the request is forgotten)
+    _forget: object = None  # set when the request has ended (see `_Forget`)
 
     def rng_state(self) -> int:
         return (self.seed + self.draws * _GOLDEN) & _M64
@@ -129,7 +132,16 @@ def prefill_chunk_for(context_length: int) -> int:
     return max(16, min(256, (1 << 21) // max(1, context_length)))
 
 
+_PHASES = (PREFILL, DECODE, ENDED)
+_REASONS = {1: "stop", 2: "length", 3: "error", 4: "cancelled"}
+_EV_ADMITTED, _EV_TOKEN, _EV_FINISHED, _EV_PREEMPTED, _EV_PREFILLED, _EV_DECODING = 1, 2, 3, 4, 5, 6
+
+
 class Scheduler:
+    """The decisions are taken by the C++ host core (`csrc/host/scheduler.cpp`); this class hands requests over,
+    runs the planned step through the `backend`, hands the sampled tokens back and keeps `Sequence_` objects in
+    step with the events the core reports."""
+
     def __init__(self, pools: KvPools, slots: StateSlots, backend, config: SchedulerConfig,
                  seed_source: Optional[Callable[[], int]] = None):
         self.pools = pools
@@ -142,29 +154,44 @@ class Scheduler:
         self.stats = ServingStats(max_sequences=config.max_sequences)
         self._next_id = 0
         self._seed_source = seed_source or _default_seed_source()
+        self._lib = host.load()
+        eos = [int(t) for t in config.eos_token_ids]
+        self._h = self._lib.cuca_host_sched_new(pools._h, slots._h, config.max_sequences, config.max_step_tokens,
+                                                config.prefill_chunk, config.context_length, host.ints(eos), len(eos))
+        self._seqs: dict = {}  # id in the core -> Sequence_, while the core still knows the request
+        self._plan_buf = (ctypes.c_int * (8 * max(1, config.max_step_tokens)))()
+        self._event_buf = (ctypes.c_int * 4096)()
+        self._on_token = None
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            h, self._h = self._h, None
+            self._lib.cuca_host_sched_free(h)
 
     # ------------------------------------------------------------ submit
     def submit(self, request: Request) -> Sequence_:
         n = len(request.prompt)
         if n == 0:
             raise RequestError("the prompt is empty")
-        if n >= self.cfg.context_length:
-            # src/provider/local/mod.rs:3252, engine/scheduler.rs:471-482
-            raise RequestError(f"the prompt has {n} tokens; the context holds {self.cfg.context_length}")
         if request.temperature < 0 or request.temperature != request.temperature:
             raise RequestError("temperature must be a finite number >= 0")
         if not 0.0 < request.top_p <= 1.0:
             raise RequestError("top_p must lie in (0, 1]")
-        room = self.cfg.context_length - n
-        budget = room if request.max_tokens is None else min(int(request.max_tokens), room)
+        prompt = [int(t) for t in request.prompt]
+        stops = [int(t) for t in request.stop_token_ids]
+        sid = self._lib.cuca_host_sched_submit(self._h, host.ints(prompt), n,
+                                               -1 if request.max_tokens is None else int(request.max_tokens),
+                                               int(request.temperature > 0), host.ints(stops), len(stops))
+        if sid < 0:
+            # src/provider/local/mod.rs:3252, engine/scheduler.rs:471-482
+            raise RequestError(host.last_error())
         seed = request.seed if request.seed is not None else self._seed_source()
-        seq = Sequence_(request, self._next_id, list(request.prompt), n, budget, seed & _M64,
-                        queued_at=time.perf_counter())
+        seq = Sequence_(request, self._next_id, prompt, n, int(self._lib.cuca_host_sched_seq_get(self._h, sid, 7)),
+                        seed & _M64, queued_at=time.perf_counter(), core_id=sid)
         self._next_id += 1
-        if budget <= 0:
-            self._finish(seq, "length")
-            return seq
+        self._seqs[sid] = seq
         self.waiting.append(seq)
+        self._events()  # a request without room for a single token has ended already
         return seq
 
     # ------------------------------------------------------------ one turn
@@ -173,21 +200,35 @@ class Scheduler:
 
     def turn(self) -> int:
         """Admit, plan, run one step, apply its results. Returns the rows of the step (0: nothing to do)."""
-        self._admit()
-        plans = self._plan()
-        if not plans:
+        lib = self._lib
+        lib.cuca_host_sched_admit(self._h)
+        self._events()
+        n = lib.cuca_host_sched_plan(self._h, self._plan_buf, len(self._plan_buf) // 8)
+        if n < 0:
+            raise RuntimeError("the plan of a step has more requests than rows: the host core is confused")
+        self._events()  # preemptions and failures found while planning
+        if n == 0:
             self._publish()
             return 0
+        buf, plans = self._plan_buf, []
+        for i in range(n):
+            sid, offset, cnt, want_last, _slot, _blocks, _start, token = buf[8 * i:8 * i + 8]
+            seq = self._seqs[sid]
+            plans.append(Plan(seq, [token] if token >= 0 else seq.prompt[offset:offset + cnt], bool(want_last)))
         t0 = time.perf_counter()
         try:
             tokens = self.backend.run(plans)
         except Exception as e:  # a failed step fails every running request and resets the cache
-            self._fail_running(f"step failed: {e}")
+            lib.cuca_host_sched_fail_running(self._h, f"step failed: {e}".encode())
+            self._events()
             raise
         rows = sum(len(p.tokens) for p in plans)
         st = self.stats
         st.prefill_rows += sum(len(p.tokens) for p in plans if p.seq.phase == PREFILL)
-        self._apply(plans, tokens)
+        toks = [int(t) for t in tokens]
+        if lib.cuca_host_sched_apply(self._h, host.ints(toks), len(toks)):
+            raise RuntimeError(host.last_error())
+        self._events()
         st.steps += 1
         st.batched_rows += rows
         st.step_seconds += time.perf_counter() - t0
@@ -195,167 +236,80 @@ class Scheduler:
         self._publish()
         return rows
 
+    def cancel(self, seq: Sequence_) -> None:
+        """The caller has no use for the request any more: its pages and slot go back, it ends as "cancelled"
+        (src/provider/local/engine/scheduler.rs:663-678)."""
+        if seq.phase != ENDED and self._seqs.get(seq.core_id) is seq:
+            self._lib.cuca_host_sched_cancel(self._h, seq.core_id)
+            self._events()
+
     def run_until_done(self, on_token: Optional[Callable] = None) -> None:
         self._on_token = on_token
         while self.has_work():
             if self.turn() == 0 and self.has_work():
                 raise RuntimeError("the scheduler made no progress: the page pool is too small for the queue's head")
 
-    # ------------------------------------------------------------ admission
-    def _committed(self) -> list:
-        """Pages the prompts being prefilled still need (per group)."""
-        total = [0] * len(self.pools.groups)
-        for s in self.running:
-            if s.phase == PREFILL:
-                for i, o in enumerate(self.pools.owed(s.blocks, len(s.prompt) + 1)):
-                    total[i] += o
-        return total
-
-    def _admit(self) -> None:
-        while self.waiting and len(self.running) < self.cfg.max_sequences and self.slots.free > 0:
-            seq = self.waiting[0]
-            owed = [c + o for c, o in zip(self._committed(), self.pools.owed(None, len(seq.prompt) + 1))]
-            if not self.pools.can_give(owed):
-                if not self.running and not self.pools.can_give(self.pools.owed(None, len(seq.prompt) + 1)):
-                    # nothing runs and it still does not fit: it never will
-                    self.waiting.popleft()
-                    self._finish(seq, "error", f"the prompt needs more pages than the pool has")
-                    continue
-                break  # head-of-line blocking
-            self.waiting.popleft()
-            seq.slot = self.slots.alloc()
-            seq.blocks = self.pools.new_seq()
-            seq.phase, seq.pos, seq.pending = PREFILL, 0, None
-            seq.started_at = seq.started_at or time.perf_counter()
-            self.backend.start(seq)
-            self.running.append(seq)
-            self.stats.admissions += 1
-
-    # ------------------------------------------------------------ planning
-    def _plan(self) -> list:
-        budget = self.cfg.max_step_tokens
-        plans, used = [], 0
-        # decoding requests, oldest first
-        for seq in list(self.running):
-            if seq.phase != DECODE or seq not in self.running:
-                continue
-            if used >= budget:
-                break
-            if not self._ensure_block(seq):
-                continue
-            plans.append(Plan(seq, [seq.pending], True))
-            used += 1
-        # the preemptions above may have removed planned requests
-        plans = [p for p in plans if p.seq in self.running]
-        used = len(plans)
-        # prompts, in admission order
-        for seq in list(self.running):
-            if seq.phase != PREFILL:
-                continue
-            room = budget - used
-            if room <= 0:
-                break
-            n = min(len(seq.prompt) - seq.pos, self.cfg.prefill_chunk, room)
-            try:
-                self.pools.reserve(seq.blocks, seq.pos + n)
-            except PoolExhausted:
-                # a prompt portion that cannot get its pages fails that request
-                # (src/provider/local/engine/scheduler.rs:1260-1263)
-                self._release(seq)
-                self._finish(seq, "error", "the K/V page pool is exhausted")
-                continue
-            last = seq.pos + n == len(seq.prompt)
-            plans.append(Plan(seq, seq.prompt[seq.pos:seq.pos + n], last))
-            used += n
-        return plans
-
-    def _ensure_block(self, seq: Sequence_) -> bool:
-        """Pages for the pending token's position; preempts the youngest on exhaustion."""
+    # ------------------------------------------------------------ what the core reports
+    def _events(self) -> None:
+        lib, buf = self._lib, self._event_buf
         while True:
-            try:
-                self.pools.reserve(seq.blocks, seq.blocks.length + 1)
-                return True
-            except PoolExhausted:
-                if len(self.running) == 1:
-                    self._release(seq)
-                    self._finish(seq, "error", "the K/V page pool is exhausted by one request")
-                    return False
-                victim = self.running[-1]  # youngest
-                if victim is self.running[0]:
-                    victim = seq
-                self._preempt(victim)
-                if victim is seq:
-                    return False
-
-    def _preempt(self, seq: Sequence_) -> None:
-        """Free the request's pages; it goes back to the front of the queue with all it had as its prompt."""
-        self._release(seq)
-        seq.prompt = list(seq.request.prompt) + list(seq.completion)
-        # the pending token is the last of `completion`; it is part of the new prompt and its logits
-        # will be asked for again at the end of the re-prefill
-        seq.phase, seq.pos, seq.pending = PREFILL, 0, None
-        seq.preemptions += 1
-        self.stats.preemptions += 1
-        self.waiting.appendleft(seq)
-
-    # ------------------------------------------------------------ results
-    def _apply(self, plans: list, tokens: list) -> None:
-        it = iter(tokens)
-        for p in plans:
-            seq = p.seq
-            if seq.phase == PREFILL:
-                seq.pos += len(p.tokens)
-                if not p.want_last:
-                    continue
-                # (a preempted request re-prefilled its own completion too: the logits just computed are those
-                # that follow its last emitted token, so decoding simply goes on)
+            n = lib.cuca_host_sched_events(self._h, buf, len(buf) // 4)
+            if n < 0:
+                self._event_buf = buf = (ctypes.c_int * (4 * -n))()
+                continue
+            break
+        now = None
+        for i in range(n):
+            kind, sid, value, extra = buf[4 * i:4 * i + 4]
+            seq = self._seqs[sid]
+            if kind == _EV_TOKEN:
+                if not seq.completion:
+                    seq.first_token_at = time.perf_counter()
+                seq.completion.append(value)
+                seq.pending = value
+                if seq.request.temperature > 0:
+                    seq.draws += 1
+                self.stats.generated_tokens += 1
+                if self._on_token:
+                    self._on_token(seq, value)
+            elif kind == _EV_PREFILLED:
+                seq.pos = value
+            elif kind == _EV_DECODING:
                 seq.phase = DECODE
-            self._take_token(seq, int(next(it)))
+            elif kind == _EV_ADMITTED:
+                self.waiting.remove(seq)
+                seq.slot, seq.blocks = value, self.pools.adopt(extra)
+                seq.phase, seq.pos, seq.pending = PREFILL, 0, None
+                seq.started_at = seq.started_at or time.perf_counter()
+                self.backend.start(seq)
+                self.running.append(seq)
+                self.stats.admissions += 1
+            elif kind == _EV_PREEMPTED:
+                self.running.remove(seq)
+                seq.prompt = list(seq.request.prompt) + list(seq.completion)
+                seq.phase, seq.pos, seq.pending, seq.slot = PREFILL, 0, None, -1
+                seq.preemptions += 1
+                self.stats.preemptions += 1
+                self.waiting.appendleft(seq)
+            elif kind == _EV_FINISHED:
+                if seq in self.running:
+                    self.running.remove(seq)
+                elif seq in self.waiting:
+                    self.waiting.remove(seq)
+                if value == 1 and seq.request.temperature > 0:
+                    seq.draws += 1  # the end token was drawn too
+                seq.phase, seq.slot, seq.pending = ENDED, -1, None
+                seq.finish_reason = _REASONS[value]
+                err = lib.cuca_host_sched_seq_error(self._h, sid)
+                seq.error = err.decode(errors="replace") if err else None
+                seq.finished_at = time.perf_counter()
+                self.finished.append(seq)
+                seq._forget = _Forget(self, sid)
 
-    def _take_token(self, seq: Sequence_, tok: int) -> None:
-        """Rules of src/provider/local/engine/scheduler.rs:1287-1316."""
-        seq.draws += 1 if seq.request.temperature > 0 else 0
-        if tok in self.cfg.eos_token_ids or tok in seq.request.stop_token_ids:
-            self._release(seq)
-            self._finish(seq, "stop")
-            return
-        if not seq.completion:
-            seq.first_token_at = time.perf_counter()
-        seq.completion.append(tok)
-        self.stats.generated_tokens += 1
-        if getattr(self, "_on_token", None):
-            self._on_token(seq, tok)
-        total = seq.prompt_tokens + len(seq.completion)
-        if len(seq.completion) >= seq.budget or total >= self.cfg.context_length:
-            self._release(seq)
-            self._finish(seq, "length")
-            return
-        seq.pending = tok
-
-    def _release(self, seq: Sequence_) -> None:
-        if seq in self.running:
-            self.running.remove(seq)
-        if seq.blocks is not None and not seq.blocks.released:
-            self.pools.release(seq.blocks)
-        if seq.slot >= 0:
-            self.slots.release(seq.slot)
-            seq.slot = -1
-
-    def _finish(self, seq: Sequence_, reason: str, error: Optional[str] = None) -> None:
-        seq.phase = ENDED
-        seq.finish_reason = reason
-        seq.error = error
-        seq.finished_at = time.perf_counter()
-        self.finished.append(seq)
-
-    def _fail_running(self, why: str) -> None:
-        """src/provider/local/engine/scheduler.rs:950-966: every running request fails, the pools start over."""
-        for seq in list(self.running):
-            self.running.remove(seq)
-            seq.slot = -1
-            self._finish(seq, "error", why)
-        self.pools.reset()
-        self.slots.reset()
+    def _release_record(self, sid: int) -> None:
+        """The last reference to an ended request is gone: the core may reuse its record."""
+        if getattr(self, "_h", None) and self._seqs.get(sid) is None:
+            self._lib.cuca_host_sched_forget(self._h, sid)
 
     def _publish(self) -> None:
         st, ps = self.stats, self.pools.stats()
@@ -363,6 +317,23 @@ class Scheduler:
         st.free_blocks, st.used_blocks, st.total_blocks = (min(ps["free_blocks"], default=0),
                                                            max(ps["used_blocks"], default=0),
                                                            min(ps["total_blocks"], default=0))
+
+
+class _Forget:
+    """Lives as long as an ended `Sequence_` does; when it goes, the host core may reuse the request's record."""
+
+    def __init__(self, scheduler: Scheduler, sid: int):
+        import weakref
+        self._scheduler, self._sid = weakref.ref(scheduler), sid
+        scheduler._seqs.pop(sid, None)
+
+    def __del__(self):
+        try:
+            sch = self._scheduler()
+            if sch is not None:
+                sch._release_record(self._sid)
+        except Exception:  # interpreter shutdown
+            pass
 
 
 def _default_seed_source():

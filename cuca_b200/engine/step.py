@@ -16,6 +16,7 @@ in one copy from pinned memory.
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass, field
 from typing import Optional, Sequence
 
@@ -23,8 +24,9 @@ import numpy as np
 import torch
 
 from ..cache.device import DeviceCache
-from ..cache.pages import NO_BLOCK, KvPools, SeqBlocks
+from ..cache.pages import KvPools, SeqBlocks
 from ..kernels import ops
+from ..native import host
 
 
 class StepError(ValueError):
@@ -89,21 +91,31 @@ class _Staging:
         self.events = [None] * n
         self.i = 0
 
-    def upload(self, arr: np.ndarray) -> torch.Tensor:
-        n = arr.shape[0]
+    def take(self, ints: int = 0) -> torch.Tensor:
+        """The next pinned buffer (at least `ints` long), free to be written."""
         i = self.i
-        self.i = (self.i + 1) % len(self.bufs)
         if self.events[i] is not None:
             self.events[i].synchronize()
-        if self.bufs[i].shape[0] < n:
-            self.bufs[i] = torch.empty(max(n, 2 * self.bufs[i].shape[0]), dtype=torch.int32).pin_memory()
-        self.bufs[i][:n].numpy()[:] = arr
+            self.events[i] = None
+        if self.bufs[i].shape[0] < ints:
+            self.bufs[i] = torch.empty(max(ints, 2 * self.bufs[i].shape[0]), dtype=torch.int32).pin_memory()
+        return self.bufs[i]
+
+    def send(self, n: int) -> torch.Tensor:
+        """Copy the first `n` integers of the buffer `take` returned to the device."""
+        i = self.i
+        self.i = (self.i + 1) % len(self.bufs)
         dev = torch.empty(n, dtype=torch.int32, device=self.device)
         dev.copy_(self.bufs[i][:n], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
         self.events[i] = ev
         return dev
+
+    def upload(self, arr: np.ndarray) -> torch.Tensor:
+        n = arr.shape[0]
+        self.take(n)[:n].numpy()[:] = arr
+        return self.send(n)
 
 
 class Stepper:
@@ -119,124 +131,60 @@ class Stepper:
         self._staging = _Staging(self.rt.device)
         self.steps = 0
 
-    # ------------------------------------------------------------ validation
-    def _validate(self, entries: Sequence[StepEntry]) -> None:
-        if not entries:
-            raise StepError("a step needs at least one request")
-        bs = self.pools.block_size
-        seen = set()
-        for e in entries:
-            t = len(e.tokens)
-            if t == 0:
-                raise StepError("a request in a step brings no tokens")
-            if e.blocks.released:
-                raise StepError("a request in a step has given its pages back already")
-            if not 0 <= e.slot < self.cache.max_sequences:
-                raise StepError(f"state slot {e.slot} is outside 0..{self.cache.max_sequences - 1}")
-            if e.slot in seen:
-                raise StepError(f"state slot {e.slot} appears twice in one step")
-            seen.add(e.slot)
-            start = e.blocks.length
-            if start + t > self.context_length:
-                raise StepError(f"positions {start}..{start + t - 1} exceed the context length {self.context_length}")
-            lo, hi = min(e.tokens), max(e.tokens)
-            if lo < 0 or hi >= self.vocab:
-                raise StepError(f"token id {hi if hi >= self.vocab else lo} is outside the vocabulary of {self.vocab}")
-            for table in e.blocks.tables:
-                if len(table) * bs < start + t:
-                    raise StepError(f"the request holds pages for {len(table) * bs} positions but the step "
-                                    f"writes up to position {start + t - 1}")
-                first, last = start // bs, (start + t - 1) // bs
-                if any(table[i] == NO_BLOCK for i in range(first, last + 1)):
-                    raise StepError("a page the step writes was given back already")
-            for w in e.want:
-                if not 0 <= w < t:
-                    raise StepError(f"wanted place {w} is outside the request's {t} tokens")
-
     # ------------------------------------------------------------ the step
     def build(self, entries: Sequence[StepEntry]) -> StepBatch:
-        tokens, positions, slot_of_row, slots, logit_rows = [], [], [], [], []
-        starts, counts = [], []
-        row = 0
-        for e in entries:
-            t = len(e.tokens)
-            start = e.blocks.length
-            tokens.extend(int(x) for x in e.tokens)
-            positions.extend(range(start, start + t))
-            slot_of_row.extend([e.slot] * t)
-            slots.append(e.slot)
-            logit_rows.extend(row + int(w) for w in e.want)
-            starts.append(start)
-            counts.append(t)
-            row += t
-        T, S, R = row, len(entries), len(logit_rows)
-        # attention plan: single-token requests are decode rows, longer portions are cut into tiles of 64 rows
-        decode_rows, tile_row0, tile_nrows, big_row0, big_nrows, max_len = [], [], [], [], [], 1
-        r0 = 0
-        for start, t in zip(starts, counts):
-            if t == 1:
-                decode_rows.append(r0)
-                max_len = max(max_len, start + 1)
-            else:
-                for off in range(0, t, 64):
-                    tile_row0.append(r0 + off)
-                    tile_nrows.append(min(64, t - off))
-                for off in range(0, t, 128):
-                    big_row0.append(r0 + off)
-                    big_nrows.append(min(128, t - off))
-            r0 += t
-        # heavy tiles (late positions see most keys) first
-        order = sorted(range(len(tile_row0)), key=lambda i: -positions[tile_row0[i]])
-        tile_row0 = [tile_row0[i] for i in order]
-        tile_nrows = [tile_nrows[i] for i in order]
-        order = sorted(range(len(big_row0)), key=lambda i: -positions[big_row0[i]])
-        big_row0 = [big_row0[i] for i in order]
-        big_nrows = [big_nrows[i] for i in order]
-        identity = len(decode_rows) == T
-        # page-table entries that changed since they were last uploaded
-        upd_idx, upd_val = [[] for _ in self.pools.groups], [[] for _ in self.pools.groups]
-        W = self.cache.table_width
-        for e in entries:
-            for gi, table in enumerate(e.blocks.tables):
-                lo = e.blocks.dirty_from[gi]
-                if lo < len(table):
-                    upd_idx[gi].extend(range(e.slot * W + lo, e.slot * W + len(table)))
-                    upd_val[gi].extend(table[lo:])
-                    e.blocks.dirty_from[gi] = len(table)
-        parts = [tokens, positions, slot_of_row, slots, logit_rows, [] if identity else decode_rows, tile_row0,
-                 tile_nrows, big_row0, big_nrows]
-        n_fixed = len(parts)
-        for gi in range(len(self.pools.groups)):
-            parts += [upd_idx[gi], upd_val[gi]]
-        sizes = [len(p) for p in parts]
-        flat = np.fromiter((x for p in parts for x in p), dtype=np.int32, count=sum(sizes))
-        dev = self._staging.upload(flat)
+        """Validate the batch and pack it (the host core does both, `csrc/host/step_pack.cpp`): empty batch, empty
+        token list, context overflow, token id out of range, missing or returned pages, wanted places and duplicate
+        slots are refused before anything changes. Then one copy from pinned memory brings tokens, positions,
+        slots, wanted rows, the attention plan and the page-table entries that changed."""
+        lib, pools = host.load(), self.pools
+        n = len(entries)
+        counts = [len(e.tokens) for e in entries]
+        flat_tokens = [int(t) for e in entries for t in e.tokens]
+        n_want = [len(e.want) for e in entries]
+        flat_want = [int(w) for e in entries for w in e.want]
+        seqs = host.ints(e.blocks.handle for e in entries)
+        slots_c = host.ints(e.slot for e in entries)
+        sizes = (ctypes.c_int * (10 + 2 * pools.n_groups))()
+        meta = (ctypes.c_int * 9)()
+        args = (pools._h, n, seqs, slots_c, host.ints(counts), host.ints(flat_tokens), host.ints(n_want),
+                host.ints(flat_want), self.context_length, self.vocab, self.cache.max_sequences, self.cache.table_width)
+        buf = self._staging.take()
+        code = lib.cuca_host_step_pack(*args, buf.data_ptr(), buf.shape[0], sizes, meta)
+        if code == host.TOO_SMALL:
+            buf = self._staging.take(meta[8])
+            code = lib.cuca_host_step_pack(*args, buf.data_ptr(), buf.shape[0], sizes, meta)
+        if code:
+            raise StepError(host.last_error())
+        T, S, R, n_decode, max_len, identity, n_tiles, n_tiles128, total = list(meta)
+        dev = self._staging.send(total)
         views, off = [], 0
-        for n in sizes:
-            views.append(dev[off:off + n])
-            off += n
-        for gi in range(len(self.pools.groups)):
-            idx, val = views[n_fixed + 2 * gi], views[n_fixed + 1 + 2 * gi]
+        for k in sizes:
+            views.append(dev[off:off + k])
+            off += k
+        for gi in range(pools.n_groups):
+            idx, val = views[10 + 2 * gi], views[11 + 2 * gi]
             if idx.shape[0]:
                 ops.scatter_int(self.cache.tables[gi], idx, val)
+        starts, row = [], 0
         return StepBatch(n_rows=T, n_seqs=S, tokens=views[0], positions=views[1], seq_of_row=views[2],
                          slots=views[3], logit_rows=views[4] if R else None, n_logit_rows=R,
-                         host={"starts": starts, "counts": counts, "slots": slots, "tokens": tokens,
-                               "positions": positions},
-                         attention_plan=AttentionPlan(None if identity else views[5], len(decode_rows), max_len,
-                                                      views[6] if tile_row0 else None,
-                                                      views[7] if tile_row0 else None, len(tile_row0),
-                                                      tile128_row0=views[8] if big_row0 else None,
-                                                      tile128_nrows=views[9] if big_row0 else None,
-                                                      n_tiles128=len(big_row0)))
+                         host={"counts": counts, "slots": [e.slot for e in entries], "tokens": flat_tokens},
+                         attention_plan=AttentionPlan(None if identity else views[5], n_decode, max_len,
+                                                      views[6] if n_tiles else None, views[7] if n_tiles else None,
+                                                      n_tiles, tile128_row0=views[8] if n_tiles128 else None,
+                                                      tile128_nrows=views[9] if n_tiles128 else None,
+                                                      n_tiles128=n_tiles128))
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run one step; returns logits [wanted, vocab] (32-bit, on the device) or None if nothing is wanted."""
-        self._validate(entries)
+        if not entries:
+            raise StepError("a step needs at least one request")
         batch = self.build(entries)
         logits = self.model.forward(batch, self.cache)
-        for e in entries:
-            e.blocks.length += len(e.tokens)
-            self.pools.release_window(e.blocks)
+        # every request has its tokens cached now; pages behind windows go back
+        if host.load().cuca_host_step_advance(self.pools._h, host.ints(e.blocks.handle for e in entries),
+                                              host.ints(len(e.tokens) for e in entries), len(entries)):
+            raise StepError(host.last_error())
         self.steps += 1
         return logits
