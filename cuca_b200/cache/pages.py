@@ -104,6 +104,11 @@ class _GroupPool:
     def used(self) -> int:
         return self.n_blocks - self.free
 
+    @property
+    def cached(self) -> int:
+        """Unreferenced pages kept for their name (counted in `free`: an allocation may take them)."""
+        return self._pools._lib.cuca_host_pools_cached_blocks(self._pools._h, self._gi)
+
 
 class _PerGroup:
     """`first_live` / `dirty_from` of a request: a list-like view of one integer per group."""
@@ -223,6 +228,26 @@ class KvPools:
     def new_seq(self) -> SeqBlocks:
         return SeqBlocks(self, self._lib.cuca_host_pools_new_seq(self._h))
 
+    def new_seq_with_prefix(self, prompt) -> SeqBlocks:
+        """A new request that starts with the longest cached prefix of `prompt` (whole pages, at most
+        len(prompt) - 1 positions): its tables share those pages and `length` says how many positions they hold."""
+        prompt = [int(t) for t in prompt]
+        return SeqBlocks(self, self._lib.cuca_host_pools_new_seq_with_prefix(self._h, host.ints(prompt), len(prompt)))
+
+    def publish(self, seq: SeqBlocks, ids) -> None:
+        """Name every full page of the request (`ids`: the tokens at its cached positions) for later prompts."""
+        ids = [int(t) for t in ids]
+        code = self._lib.cuca_host_pools_publish(self._h, seq.handle, host.ints(ids), len(ids))
+        if code:
+            _raise(code)
+
+    def finish(self, seq: SeqBlocks, ids) -> None:
+        """`publish`, then `release`: the request's full pages stay in the pool as cached."""
+        ids = [int(t) for t in ids]
+        code = self._lib.cuca_host_pools_finish(self._h, seq.handle, host.ints(ids), len(ids))
+        if code:
+            _raise(code)
+
     def adopt(self, handle: int) -> SeqBlocks:
         """A view of tables that the host core made itself (the scheduler admits requests there)."""
         return SeqBlocks(self, handle, owns=False)
@@ -277,7 +302,7 @@ class KvPools:
 
     def stats(self) -> dict:
         return {"free_blocks": [p.free for p in self.pools], "used_blocks": [p.used for p in self.pools],
-                "total_blocks": [p.n_blocks for p in self.pools],
+                "total_blocks": [p.n_blocks for p in self.pools], "cached_blocks": [p.cached for p in self.pools],
                 "live_requests": self._lib.cuca_host_pools_live(self._h)}
 
 

@@ -37,7 +37,7 @@ class BatchingConfig:
     max_sequences: int = 4  # 1..=64
     kv_tokens: Optional[int] = None  # positions in the shared page pool; default context + min(context, 4096)
     max_step_tokens: Optional[int] = None  # rows of one step; default the prefill chunk of the context
-    prefix_cache: bool = False  # the prefix store of the reference is not part of this engine
+    prefix_cache: bool = False  # requests reuse the cached pages of a prompt prefix they share with earlier ones
     prefill_chunk: Optional[int] = None  # ours: most tokens of one prompt per step; default: the reference's
     # clamp(2^21 / context, 16, 256), or max_step_tokens when that is given (a B200 takes a 2048-token portion whole)
 

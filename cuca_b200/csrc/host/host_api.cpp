@@ -49,6 +49,10 @@ HOST_API int cuca_host_pools_release_window(void* h, int seq) {
 }
 HOST_API int cuca_host_pools_truncate(void* h, int seq, int length) { return pool_status((KvPools*)h, ((KvPools*)h)->truncate(seq, length)); }
 HOST_API int cuca_host_pools_release(void* h, int seq) { return pool_status((KvPools*)h, ((KvPools*)h)->release(seq)); }
+HOST_API int cuca_host_pools_publish(void* h, int seq, const int* ids, int n) { return pool_status((KvPools*)h, ((KvPools*)h)->publish(seq, ids, n)); }
+HOST_API int cuca_host_pools_finish(void* h, int seq, const int* ids, int n) { return pool_status((KvPools*)h, ((KvPools*)h)->finish(seq, ids, n)); }
+HOST_API int cuca_host_pools_new_seq_with_prefix(void* h, const int* prompt, int n) { return ((KvPools*)h)->new_seq_with_prefix(prompt, n); }
+HOST_API int cuca_host_pools_cached_blocks(void* h, int g) { return ((KvPools*)h)->pool(g).cached_count(); }
 HOST_API void cuca_host_pools_reset(void* h) { ((KvPools*)h)->reset(); }
 HOST_API int cuca_host_pools_check(void* h) { return pool_status((KvPools*)h, ((KvPools*)h)->check()); }
 HOST_API int cuca_host_pools_live(void* h) { return ((KvPools*)h)->live(); }
@@ -139,8 +143,9 @@ struct SchedulerBox {
 };
 
 HOST_API void* cuca_host_sched_new(void* pools, void* slots, int max_sequences, int max_step_tokens, int prefill_chunk,
-                                   int context_length, const int* eos, int n_eos) {
+                                   int context_length, const int* eos, int n_eos, int prefix_cache) {
   SchedulerConfig c;
+  c.prefix_cache = prefix_cache != 0;
   c.max_sequences = max_sequences; c.max_step_tokens = max_step_tokens; c.prefill_chunk = prefill_chunk;
   c.context_length = context_length;
   c.eos_token_ids.assign(eos, eos + n_eos);
@@ -186,7 +191,7 @@ HOST_API int cuca_host_sched_events(void* h, int* out, int cap_events) {
   ev.clear();
   return n;
 }
-// counters: 0 running, 1 waiting, 2 preemptions, 3 admissions, 4 generated tokens
+// counters: 0 running, 1 waiting, 2 preemptions, 3 admissions, 4 generated tokens, 5 prompt tokens found cached
 HOST_API long long cuca_host_sched_counter(void* h, int which) {
   Scheduler& s = ((SchedulerBox*)h)->sched;
   switch (which) {
@@ -195,6 +200,7 @@ HOST_API long long cuca_host_sched_counter(void* h, int which) {
     case 2: return s.preemptions;
     case 3: return s.admissions;
     case 4: return s.generated_tokens;
+    case 5: return s.prefix_hit_tokens;
   }
   return -1;
 }

@@ -64,10 +64,15 @@ void Scheduler::admit() {
     const int id = waiting_.front();
     Sequence& s = seqs_[id];
     committed(com);
-    pools_.owed(-1, (int)s.prompt.size() + 1, owed.data());
+    // with the prefix cache the request starts from the pages that already hold the head of its prompt
+    // (src/provider/local/engine/scheduler.rs:805-813)
+    const int blocks = cfg_.prefix_cache ? pools_.new_seq_with_prefix(s.prompt.data(), (int)s.prompt.size()) : pools_.new_seq();
+    pools_.owed(blocks, (int)s.prompt.size() + 1, owed.data());
     for (int g = 0; g < G; ++g) need[g] = com[g] + owed[g];
     if (!pools_.can_give(need.data())) {
-      if (running_.empty() && !pools_.can_give(owed.data())) {
+      const bool never = running_.empty() && !pools_.can_give(owed.data());
+      pools_.drop_seq(blocks);
+      if (never) {
         // nothing runs and it still does not fit: it never will
         waiting_.pop_front();
         finish(id, FIN_ERROR, "the prompt needs more pages than the pool has");
@@ -77,13 +82,15 @@ void Scheduler::admit() {
     }
     waiting_.pop_front();
     s.slot = slots_.alloc();
-    s.blocks = pools_.new_seq();
+    s.blocks = blocks;
     s.phase = PH_PREFILL;
-    s.pos = 0;
+    s.pos = pools_.seq(blocks)->length;
     s.pending = -1;
     running_.push_back(id);
     ++admissions;
+    prefix_hit_tokens += s.pos;
     emit(EV_ADMITTED, id, s.slot, s.blocks);
+    if (s.pos > 0) emit(EV_PREFILLED, id, s.pos);
   }
 }
 
@@ -114,7 +121,7 @@ void Scheduler::plan(std::vector<PlanItem>& out) {
     if (pools_.reserve(s.blocks, s.pos + n) != OK) {
       // a prompt portion that cannot get its pages fails that request
       // (src/provider/local/engine/scheduler.rs:1260-1263)
-      release(id);
+      release(id, false);
       finish(id, FIN_ERROR, "the K/V page pool is exhausted");
       continue;
     }
@@ -136,7 +143,7 @@ bool Scheduler::ensure_block(int id) {
     const Status st = pools_.reserve(s.blocks, (b ? b->length : 0) + 1);
     if (st == OK) return true;
     if (running_.size() == 1) {
-      release(id);
+      release(id, false);
       finish(id, FIN_ERROR, "the K/V page pool is exhausted by one request");
       return false;
     }
@@ -149,7 +156,7 @@ bool Scheduler::ensure_block(int id) {
 
 // Free the request's pages; it goes back to the front of the queue with all it had as its prompt.
 void Scheduler::preempt(int id) {
-  release(id);
+  release(id, true);  // what it computed stays findable: its re-prefill starts from there if the pages survive
   Sequence& s = seqs_[id];
   s.prompt = s.request_prompt;
   s.prompt.insert(s.prompt.end(), s.completion.begin(), s.completion.end());
@@ -176,6 +183,12 @@ bool Scheduler::apply(const std::vector<PlanItem>& plans, const int* tokens, int
       // emitted token, so decoding simply goes on)
       s.phase = PH_DECODE;
       emit(EV_DECODING, p.seq);
+      if (cfg_.prefix_cache) {
+        // a full page is never written again: requests that arrive while this one decodes may share its prompt
+        std::vector<int> ids;
+        tokens_cached(s, ids);
+        pools_.publish(s.blocks, ids.data(), (int)ids.size());
+      }
     }
     if (it >= n_tokens) { error_ = "the step returned fewer tokens than requests that asked for one"; return false; }
     take_token(p.seq, tokens[it++]);
@@ -190,7 +203,7 @@ void Scheduler::take_token(int id, int tok) {
   const bool stop = std::find(cfg_.eos_token_ids.begin(), cfg_.eos_token_ids.end(), tok) != cfg_.eos_token_ids.end() ||
                     std::find(s.stop_ids.begin(), s.stop_ids.end(), tok) != s.stop_ids.end();
   if (stop) {
-    release(id);
+    release(id, true);
     finish(id, FIN_STOP);
     return;
   }
@@ -199,19 +212,34 @@ void Scheduler::take_token(int id, int tok) {
   emit(EV_TOKEN, id, tok);
   const int total = (int)s.request_prompt.size() + (int)s.completion.size();
   if ((int)s.completion.size() >= s.budget || total >= cfg_.context_length) {
-    release(id);
+    release(id, true);
     finish(id, FIN_LENGTH);
     return;
   }
   s.pending = tok;
 }
 
-void Scheduler::release(int id) {
+// The tokens at the positions the request has cached: its prompt, then what it generated and forwarded.
+void Scheduler::tokens_cached(const Sequence& s, std::vector<int>& ids) const {
+  ids = s.request_prompt;
+  ids.insert(ids.end(), s.completion.begin(), s.completion.end());
+}
+
+void Scheduler::release(int id, bool share) {
   Sequence& s = seqs_[id];
   running_.erase(std::remove(running_.begin(), running_.end(), id), running_.end());
   if (s.blocks >= 0) {
     SeqBlocks* b = pools_.seq(s.blocks);
-    if (b && !b->released) pools_.release(s.blocks);
+    if (b && !b->released) {
+      if (share && cfg_.prefix_cache) {
+        // src/provider/local/engine/scheduler.rs:884-896: the full pages are filed in the prefix store
+        std::vector<int> ids;
+        tokens_cached(s, ids);
+        pools_.finish(s.blocks, ids.data(), (int)ids.size());
+      } else {
+        pools_.release(s.blocks);
+      }
+    }
   }
   if (s.slot >= 0) {
     slots_.release(s.slot);
@@ -232,7 +260,7 @@ void Scheduler::cancel(int id) {
   Sequence* s = seq(id);
   if (!s || s->phase == PH_ENDED) return;
   waiting_.erase(std::remove(waiting_.begin(), waiting_.end(), id), waiting_.end());
-  release(id);
+  release(id, true);
   finish(id, FIN_CANCELLED);
 }
 

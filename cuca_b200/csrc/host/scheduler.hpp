@@ -32,6 +32,7 @@ struct Event { int kind, seq, value, extra; };
 struct SchedulerConfig {
   int max_sequences = 4, max_step_tokens = 256, prefill_chunk = 256, context_length = 8192;
   std::vector<int> eos_token_ids;
+  bool prefix_cache = false;  // requests start from the longest cached prefix of their prompt and leave their pages named
 };
 
 // A request's share of the coming step: prompt[offset, offset + n) while prefilling, else its one pending `token`.
@@ -67,14 +68,15 @@ class Scheduler {
   const std::string& error() const { return error_; }
   const std::vector<int>& running() const { return running_; }
   const std::deque<int>& waiting() const { return waiting_; }
-  long long preemptions = 0, admissions = 0, generated_tokens = 0;
+  long long preemptions = 0, admissions = 0, generated_tokens = 0, prefix_hit_tokens = 0;
 
  private:
   void committed(std::vector<int>& total);
   bool ensure_block(int id);
   void preempt(int id);
   void take_token(int id, int tok);
-  void release(int id);
+  void release(int id, bool share);  // share: with the prefix cache on, its full pages stay findable
+  void tokens_cached(const Sequence& s, std::vector<int>& ids) const;
   void finish(int id, int reason, const std::string& error = std::string());
   bool is_running(int id) const;
   void emit(int kind, int seq, int value = 0, int extra = 0) { events_.push_back(Event{kind, seq, value, extra}); }

@@ -186,7 +186,7 @@ class LocalModel:
         self.scheduler = Scheduler(core.pools, core.slots, self.backend, SchedulerConfig(
             max_sequences=config.batching.max_sequences, max_step_tokens=sizes["max_step_tokens"],
             prefill_chunk=sizes["prefill_chunk"], context_length=sizes["context_length"],
-            eos_token_ids=tuple(core.spec.eos_token_ids)))
+            eos_token_ids=tuple(core.spec.eos_token_ids), prefix_cache=bool(config.batching.prefix_cache)))
         self._file_sampling = _file_sampling(model_dir)
         self.load_seconds = 0.0
 

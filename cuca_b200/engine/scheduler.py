@@ -105,6 +105,7 @@ class SchedulerConfig:
     prefill_chunk: int = 256
     context_length: int = 8192
     eos_token_ids: tuple = ()
+    prefix_cache: bool = False  # requests start from the longest cached prefix of their prompt
 
 
 @dataclass
@@ -123,6 +124,7 @@ class ServingStats:
     prefill_rows: int = 0
     generated_tokens: int = 0
     admissions: int = 0
+    prefix_hit_tokens: int = 0  # prompt tokens whose keys and values were found cached
     step_seconds: float = 0.0
     last_step_rows: int = 0
 
@@ -157,7 +159,8 @@ class Scheduler:
         self._lib = host.load()
         eos = [int(t) for t in config.eos_token_ids]
         self._h = self._lib.cuca_host_sched_new(pools._h, slots._h, config.max_sequences, config.max_step_tokens,
-                                                config.prefill_chunk, config.context_length, host.ints(eos), len(eos))
+                                                config.prefill_chunk, config.context_length, host.ints(eos), len(eos),
+                                                int(config.prefix_cache))
         self._seqs: dict = {}  # id in the core -> Sequence_, while the core still knows the request
         self._plan_buf = (ctypes.c_int * (8 * max(1, config.max_step_tokens)))()
         self._event_buf = (ctypes.c_int * 4096)()
@@ -314,6 +317,7 @@ class Scheduler:
     def _publish(self) -> None:
         st, ps = self.stats, self.pools.stats()
         st.running, st.waiting = len(self.running), len(self.waiting)
+        st.prefix_hit_tokens = int(self._lib.cuca_host_sched_counter(self._h, 5))
         st.free_blocks, st.used_blocks, st.total_blocks = (min(ps["free_blocks"], default=0),
                                                            max(ps["used_blocks"], default=0),
                                                            min(ps["total_blocks"], default=0))

@@ -78,6 +78,8 @@ _SIGNATURES = {
     "cuca_host_pools_owed": (None, [_P, _I, _I, _IP]), "cuca_host_pools_can_give": (_I, [_P, _IP]),
     "cuca_host_pools_reserve": (_I, [_P, _I, _I]), "cuca_host_pools_release_window": (_I, [_P, _I]),
     "cuca_host_pools_truncate": (_I, [_P, _I, _I]), "cuca_host_pools_release": (_I, [_P, _I]),
+    "cuca_host_pools_publish": (_I, [_P, _I, _IP, _I]), "cuca_host_pools_finish": (_I, [_P, _I, _IP, _I]),
+    "cuca_host_pools_new_seq_with_prefix": (_I, [_P, _IP, _I]), "cuca_host_pools_cached_blocks": (_I, [_P, _I]),
     "cuca_host_pools_reset": (None, [_P]), "cuca_host_pools_check": (_I, [_P]), "cuca_host_pools_live": (_I, [_P]),
     "cuca_host_pools_free_blocks": (_I, [_P, _I]), "cuca_host_pools_total_blocks": (_I, [_P, _I]),
     "cuca_host_seq_get": (_I, [_P, _I, _I]), "cuca_host_seq_set": (_I, [_P, _I, _I, _I]),
@@ -88,7 +90,7 @@ _SIGNATURES = {
     "cuca_host_step_pack": (_I, [_P, _I, _IP, _IP, _IP, _IP, _IP, _IP, _I, _I, _I, _I, _P, _I, _IP, _IP]),
     "cuca_host_table_updates": (_I, [_P, _IP, _IP, _I, _I, _I, _P, _I]),
     "cuca_host_step_advance": (_I, [_P, _IP, _IP, _I]),
-    "cuca_host_sched_new": (_P, [_P, _P, _I, _I, _I, _I, _IP, _I]), "cuca_host_sched_free": (None, [_P]),
+    "cuca_host_sched_new": (_P, [_P, _P, _I, _I, _I, _I, _IP, _I, _I]), "cuca_host_sched_free": (None, [_P]),
     "cuca_host_sched_submit": (_I, [_P, _IP, _I, _L, _I, _IP, _I]), "cuca_host_sched_admit": (None, [_P]),
     "cuca_host_sched_plan": (_I, [_P, _IP, _I]), "cuca_host_sched_apply": (_I, [_P, _IP, _I]),
     "cuca_host_sched_fail_running": (None, [_P, c_char_p]), "cuca_host_sched_forget": (None, [_P, _I]), "cuca_host_sched_cancel": (None, [_P, _I]),

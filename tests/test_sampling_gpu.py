@@ -200,3 +200,39 @@ def test_command_line(folders):
     assert r.returncode == 0, r.stderr[-2000:]
     assert len(r.stdout.split()) == 6
     assert "load:" in r.stderr and "loaded on" in r.stderr and "timing: 4 prompt tokens" in r.stderr
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_generation_from_cached_prefixes_equals_generation_from_scratch(folders, dtype):
+    """With `prefix_cache` a request starts from the pages an earlier request left for the head of its prompt.
+    Tokens must be those of an engine without it: in 32-bit exactly (the shared keys and values are the same
+    bits), and the prompt rows that were found are not computed again."""
+    from cuca_b200 import LocalModel, LocalModelConfig, BatchingConfig
+    cfg, _ = plain_llama.load_model_dir(folders["A"])
+    rs = np.random.default_rng(11)
+    head = rs.integers(0, cfg["vocab_size"], size=50).tolist()
+    prompts = [head + rs.integers(0, cfg["vocab_size"], size=n).tolist() for n in (5, 1, 23)] + [head[:37]]
+    plain = LocalModel.load(LocalModelConfig(source=str(folders["A"]), dtype=dtype,
+                                             batching=BatchingConfig(max_sequences=4)))
+    want = [plain.generate(p, max_tokens=12, temperature=0.0).tokens for p in prompts]
+    cached = LocalModel.load(LocalModelConfig(source=str(folders["A"]), dtype=dtype,
+                                              batching=BatchingConfig(max_sequences=4, prefix_cache=True)))
+    got, hits = [], []
+    for p in prompts:                      # one after the other: each finds what the ones before left
+        before = cached.serving_stats().prefix_hit_tokens
+        got.append(cached.generate(p, max_tokens=12, temperature=0.0).tokens)
+        hits.append(cached.serving_stats().prefix_hit_tokens - before)
+    assert hits == [0, 48, 48, 32]         # whole pages of 16 below the last prompt token
+    if dtype == "float32":
+        assert got == want
+    else:
+        assert [g[:4] for g in got] == [w[:4] for w in want]
+    # together: the first is admitted with nothing cached for `other`, later ones share pages with running requests
+    other = rs.integers(0, cfg["vocab_size"], size=40).tolist()
+    batch = [other + [1, 2], other + [3], other[:35]]
+    outs = cached.generate(batch, max_tokens=8, temperature=0.0)
+    if dtype == "float32":
+        assert [o.tokens for o in outs] == [plain.generate(p, max_tokens=8, temperature=0.0).tokens for p in batch]
+    st = cached.serving_stats()
+    assert st.running == 0 and st.used_blocks == 0
+    cached.core.pools.check()
