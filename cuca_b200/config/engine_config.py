@@ -26,6 +26,8 @@ class SamplingConfig:
     top_k: Optional[int] = None
     top_p: Optional[float] = None
     seed: Optional[int] = None
+    suppress_tokens: Optional[list] = None  # token ids that are never sampled (the reference takes them from the
+    # tokenizer's metadata; here: this list, else generation_config.json's `suppress_tokens`)
 
     DEFAULT_TEMPERATURE = 1.0
     DEFAULT_TOP_K = 64

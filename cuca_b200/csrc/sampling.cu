@@ -442,6 +442,28 @@ CUCA_API int cuca_argmax(const float* logits, size_t row_stride, int n_rows, int
   return 0;
 }
 
+namespace {
+__global__ void suppress_kernel(float* __restrict__ logits, size_t row_stride, int V, const int* __restrict__ ids, int n) {
+  pdl_trigger();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int id = ids[i];
+  if (id >= 0 && id < V) logits[(size_t)blockIdx.y * row_stride + id] = -INFINITY;
+}
+}  // namespace
+
+// logits[r, ids[i]] = -inf for every row: tokens that must never be sampled
+// (src/provider/local/tokenizer/mod.rs:131-151, engine/scheduler.rs:1554). Ids outside the vocabulary are skipped.
+CUCA_API int cuca_suppress_tokens(float* logits, size_t row_stride, int n_rows, int V, const int* ids, int n,
+                                  cudaStream_t stream) {
+  if (n_rows == 0 || n == 0) return 0;
+  CUCA_REQUIRE(n_rows <= 65535, "suppress_tokens: too many rows");
+  cuca_launch(suppress_kernel, dim3((n + 127) / 128, n_rows), dim3(128), 0, stream, true, logits, row_stride, V, ids, n);
+  CUCA_CHECK_LAUNCH("suppress_tokens");
+  return 0;
+}
+
 // Smallest scratch row (in 64-bit words) that lets cuca_sample sort a whole vocabulary of V ids.
 CUCA_API int cuca_sample_scratch_stride(int V) {
   int n = 1;

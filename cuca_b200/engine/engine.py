@@ -59,6 +59,7 @@ class GpuBackend:
         self.top_k = torch.zeros(n, dtype=torch.int32, device=dev)
         self.top_p = torch.ones(n, dtype=torch.float32, device=dev)
         self._scratch = None
+        self.suppress = None  # int32 ids whose logits are set to -inf before sampling
         self._needs_scratch = [False] * n
         self.vocab = core.spec.vocab_size
         self.use_graphs = core.model.graph_safe()
@@ -155,6 +156,8 @@ class GpuBackend:
             if self._scratch is None or self._scratch.shape[0] < len(rows):
                 self._scratch = torch.empty(max(len(rows), 4), words, dtype=torch.int64, device=self.core.rt.device)
             scratch = self._scratch
+        if self.suppress is not None:
+            ops.suppress_tokens(logits, self.suppress)
         ops.sample(logits, self.temperature, self.top_k, self.top_p, self.rng, slot_of_row, out, scratch)
         tokens = out.tolist()  # the one synchronisation of a step
         self.core.rt.check_device_errors()
@@ -172,7 +175,7 @@ def _file_sampling(model_dir: Optional[Path]) -> dict:
         g = json.loads(f.read_text())
     except ValueError:
         return {}
-    return {k: g[k] for k in ("temperature", "top_k", "top_p") if g.get(k) is not None}
+    return {k: g[k] for k in ("temperature", "top_k", "top_p", "suppress_tokens") if g.get(k) is not None}
 
 
 class LocalModel:
@@ -188,6 +191,12 @@ class LocalModel:
             prefill_chunk=sizes["prefill_chunk"], context_length=sizes["context_length"],
             eos_token_ids=tuple(core.spec.eos_token_ids), prefix_cache=bool(config.batching.prefix_cache)))
         self._file_sampling = _file_sampling(model_dir)
+        suppressed = config.sampling.suppress_tokens
+        if suppressed is None:
+            suppressed = self._file_sampling.get("suppress_tokens")
+        if suppressed:
+            self.backend.suppress = torch.tensor([int(t) for t in suppressed], dtype=torch.int32,
+                                                 device=core.rt.device)
         self.load_seconds = 0.0
 
     # ------------------------------------------------------------ loading

@@ -58,6 +58,8 @@ class DecodeGraph:
     def _body(self):
         logits = self.core.model.forward(self.batch, self.core.cache)
         be = self.backend
+        if be.suppress is not None:
+            ops.suppress_tokens(logits, be.suppress)
         ops.sample(logits, be.temperature, be.top_k, be.top_p, be.rng, self.slot_of_row, self.sampled, self.scratch)
         ops.decode_advance(self.tokens, self.positions, self.slot_of_row, self.sampled, self.history, self.counter,
                            MAX_HISTORY)

@@ -285,6 +285,14 @@ def scatter_int(dst, idx, val) -> None:
     library.check(lib.cuca_scatter_int(_p(dst), _p(idx), _p(val), idx.shape[0], dst.numel(), _stream()), "scatter_int")
 
 
+def suppress_tokens(logits, ids) -> None:
+    """logits[:, ids] = -inf on the device (`ids`: int32 tensor): tokens that must never be sampled."""
+    _cuda(logits, ids)
+    lib = library.load()
+    library.check(lib.cuca_suppress_tokens(_p(logits), logits.stride(0), logits.shape[0], logits.shape[1], _p(ids),
+                                           ids.shape[0], _stream()), "suppress_tokens")
+
+
 def sample_scratch_words(vocab: int) -> int:
     n = 1
     while n < vocab:

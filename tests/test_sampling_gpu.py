@@ -236,3 +236,33 @@ def test_generation_from_cached_prefixes_equals_generation_from_scratch(folders,
     st = cached.serving_stats()
     assert st.running == 0 and st.used_blocks == 0
     cached.core.pools.check()
+
+
+def test_suppressed_tokens_are_never_sampled(folders):
+    """`sampling.suppress_tokens`: their logits are -inf before sampling, in eager steps and in captured decode
+    graphs alike; the tokens equal plain greedy decoding over the masked logits."""
+    from cuca_b200 import LocalModel, LocalModelConfig, SamplingConfig
+    from cuca_b200.kernels import ops
+    dev = torch.device("cuda:0")
+    lg = torch.randn(3, 50, device=dev)
+    top = lg.argmax(-1)
+    ops.suppress_tokens(lg, torch.tensor([int(top[0]), int(top[2]), 70, -3], dtype=torch.int32, device=dev))
+    assert torch.isinf(lg[:, int(top[0])]).all() and torch.isinf(lg[:, int(top[2])]).all()
+    assert int(torch.isinf(lg).sum()) == 3 * len({int(top[0]), int(top[2])})
+
+    cfg, weights = plain_llama.load_model_dir(folders["A"])
+    prompt = np.random.default_rng(21).integers(0, cfg["vocab_size"], size=9).tolist()
+    free = plain_llama.generate_greedy(cfg, weights, prompt, 10)
+    banned = sorted(set(free[:4]))
+    want, ids = [], list(prompt)
+    for _ in range(10):
+        row = plain_llama.forward(cfg, weights, ids)[-1].clone()
+        row[banned] = -float("inf")
+        want.append(int(row.argmax()))
+        ids.append(want[-1])
+    model = LocalModel.load(LocalModelConfig(source=str(folders["A"]), dtype="float32",
+                                             sampling=SamplingConfig(suppress_tokens=banned)))
+    got = model.generate(prompt, max_tokens=10, temperature=0.0).tokens
+    assert got == want and not set(got) & set(banned)
+    sampled = model.generate(prompt, max_tokens=40, temperature=1.5, top_k=0, top_p=1.0, seed=3).tokens
+    assert not set(sampled) & set(banned)
