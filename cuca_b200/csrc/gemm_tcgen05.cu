@@ -54,8 +54,6 @@ struct Params {
   int stream_k;  // 0: whole tiles in turn; 1: units dealt out evenly; 2: per_tile even K slices of every tile
   int per_tile;  // mode 2: CTAs per tile
   int max_parts; // workspace slots per tile
-  int l2_ahead;  // weight tiles requested into L2 beyond the ring before the predecessor has finished
-  int late_trigger;  // 1: dependents may move in once this CTA's stream is fully requested; 0: at once
 };
 
 // SWAP: weight rows on the 128 lanes, BN tokens as columns. Otherwise tokens on the lanes, 256 weight rows
@@ -77,9 +75,6 @@ struct Cfg {
   static constexpr int NCOLS = SWAP ? BN * (DUAL ? 2 : 1) : 256;   // accumulator columns of one tile
   static constexpr int TMEM_COLS = 2 * NCOLS < 32 ? 32 : 2 * NCOLS;  // two accumulators
   static constexpr int OUT_COLS = SWAP ? BN : (DUAL ? 128 : 256);  // output columns of one tile
-  // weight tiles requested into L2 beyond the shared-memory ring before the predecessor has finished (decode
-  // only): about what the memory system delivers while the predecessor drains and reduces its partial tiles
-  static constexpr int L2_AHEAD = SWAP ? (1024 * 1024) / A_BYTES : 0;  // upper bound of Params::l2_ahead
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 512 /*barriers*/;
 };
 
@@ -227,10 +222,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   volatile int* seg_ok = (volatile int*)(tmem_slot + 3);  // [2]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // With late_trigger the producer and MMA threads call pdl_trigger() only when their stream is fully requested,
-  // so the next kernel's CTAs move in (and request their own weights) while this kernel drains, not while it
-  // still streams; everyone else calls it now.
-  if (!p.late_trigger || !((warp == 0 || warp == 1 || warp == 6) && lane == 0)) pdl_trigger();
+  pdl_trigger();
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(&full[s], 1);
@@ -271,15 +263,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tma_load_2d(st + C::A_BYTES + 128 * TILE_K * 2, &tmB, bar, kc, DUAL ? p.N + b0 : b0 + 128);
     }
   };
-  auto prefetch_weights = [&](int a0, int b0, int kc) {
-    if (SWAP) {
-      tma_prefetch_2d(&tmA, kc, a0);
-      if (DUAL) tma_prefetch_2d(&tmA, kc, p.N + a0);
-    } else {
-      tma_prefetch_2d(&tmB, kc, b0);
-      tma_prefetch_2d(&tmB, kc, DUAL ? p.N + b0 : b0 + 128);
-    }
-  };
   auto load_activations = [&](uint8_t* st, uint64_t* bar, int a0, int b0, int kc) {
     if (SWAP) tma_load_2d(st + C::A_BYTES, &tmB, bar, kc, b0);
     else tma_load_2d(st, &tmA, bar, kc, a0);
@@ -293,18 +276,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       SegmentWalk pre(p);
       Segment s;
       int it = 0;
-      const int ahead = C::STAGES + (p.l2_ahead < C::L2_AHEAD ? p.l2_ahead : C::L2_AHEAD);
+      const int ahead = C::STAGES;
       while (it < ahead && pre.next(s)) {
         int a0, b0;
         tile_origin(s.tile, a0, b0);
         for (int ks = s.ks0; ks < s.ks1 && it < ahead; ++ks, ++it) {
           if (it % NPROD != mine) continue;
-          if (it < C::STAGES) {
-            mbar_expect_tx(&full[it], C::STAGE_BYTES);
-            load_weights(smem + it * C::STAGE_BYTES, &full[it], a0, b0, ks * TILE_K);
-          } else {
-            prefetch_weights(a0, b0, ks * TILE_K);  // beyond the ring: into L2
-          }
+          mbar_expect_tx(&full[it], C::STAGE_BYTES);
+          load_weights(smem + it * C::STAGE_BYTES, &full[it], a0, b0, ks * TILE_K);
         }
       }
     }
@@ -328,7 +307,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         load_activations(sp, &full[st], a0, b0, ks * TILE_K);
       }
     }
-    if (p.late_trigger) pdl_trigger();
   } else if (warp == 1 && lane == 0) {
     // ------------------------------------------------ MMA issuer
     pdl_wait();
@@ -362,7 +340,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (ok) umma_commit(&tmem_full[buf]);
       ++seg;
     }
-    if (p.late_trigger) pdl_trigger();
   } else if (warp >= 2 && warp <= 5) {
     // ------------------------------------------------ epilogue: four warps, one TMEM lane per thread
     pdl_wait();
@@ -614,15 +591,6 @@ static int gemm_tc_impl(const void* A, const void* W, const void* bias, void* ou
   const int tiles_b = swap ? (M + bn - 1) / bn : (N + out_cols - 1) / out_cols;
   p.tiles = p.tiles_a * tiles_b;
   p.ksteps = (K + TILE_K - 1) / TILE_K;
-  static int env_l2 = -1, env_late = -1;
-  if (env_l2 < 0) {
-    const char* e = getenv("CUCA_GEMM_L2_AHEAD");
-    env_l2 = e ? atoi(e) : 0;
-    e = getenv("CUCA_GEMM_LATE_TRIGGER");
-    env_late = e ? atoi(e) : 0;
-  }
-  p.l2_ahead = env_l2;
-  p.late_trigger = env_late;
   const int sms = cuca_device_sms();
   const long long units = (long long)p.tiles * p.ksteps;
   int grid = p.tiles < sms ? p.tiles : sms;

@@ -101,10 +101,11 @@ class GpuBackend:
     def _run_decode_graph(self, plans: Sequence[Plan]) -> list:
         seqs = [p.seq for p in plans]
         n = len(seqs)
-        max_len = max(s.blocks.length for s in seqs) + 1
+        starts = [p.start if p.start >= 0 else p.seq.blocks.length for p in plans]
+        max_len = max(starts) + 1
         g = self.graphs.get(n, max_len, any(self._needs_scratch[s.slot] for s in seqs))
         self._table_updates(seqs)
-        g.load_rows([p.tokens[0] for p in plans], [s.blocks.length for s in seqs], [s.slot for s in seqs])
+        g.load_rows([p.tokens[0] for p in plans], starts, [s.slot for s in seqs])
         g.replay()
         tokens = g.sampled[:n].tolist()  # the one synchronisation of a step
         self._advance(seqs, 1)
@@ -125,12 +126,13 @@ class GpuBackend:
         n = len(seqs)
         if n_steps > MAX_HISTORY:
             raise ValueError(f"a burst holds at most {MAX_HISTORY} steps")
-        for s in seqs:
-            core.pools.reserve(s.blocks, s.blocks.length + n_steps)
-        max_len = max(s.blocks.length for s in seqs) + n_steps
+        starts = [s.blocks.length for s in seqs]
+        for s, start in zip(seqs, starts):
+            core.pools.reserve(s.blocks, start + n_steps)
+        max_len = max(starts) + n_steps
         g = self.graphs.get(n, max_len, any(self._needs_scratch[s.slot] for s in seqs))
         self._table_updates(seqs)
-        g.load_rows(tokens, [s.blocks.length for s in seqs], [s.slot for s in seqs])
+        g.load_rows(tokens, starts, [s.slot for s in seqs])
         g.counter.zero_()
         for _ in range(n_steps):
             g.replay()

@@ -96,6 +96,7 @@ class Plan:
     seq: Sequence_
     tokens: list
     want_last: bool
+    start: int = -1  # positions the request has cached before the step (-1: ask its block tables)
 
 
 @dataclass
@@ -215,9 +216,9 @@ class Scheduler:
             return 0
         buf, plans = self._plan_buf, []
         for i in range(n):
-            sid, offset, cnt, want_last, _slot, _blocks, _start, token = buf[8 * i:8 * i + 8]
+            sid, offset, cnt, want_last, _slot, _blocks, start, token = buf[8 * i:8 * i + 8]
             seq = self._seqs[sid]
-            plans.append(Plan(seq, [token] if token >= 0 else seq.prompt[offset:offset + cnt], bool(want_last)))
+            plans.append(Plan(seq, [token] if token >= 0 else seq.prompt[offset:offset + cnt], bool(want_last), start))
         t0 = time.perf_counter()
         try:
             tokens = self.backend.run(plans)
