@@ -32,7 +32,7 @@ constexpr int D = 128;        // head size
 constexpr int ROWS = 128;     // query rows per tile = TMEM lanes
 constexpr int KEYS = 64;      // keys per tile
 constexpr int NQ = 2;         // query tiles per CTA (two query heads of one key/value group, same rows)
-constexpr int KV_STAGES = 3;
+constexpr int KV_STAGES = 4;
 // Tiles are stored as 64-element halves: [halves][rows][128 B], 128-byte swizzled.
 constexpr int Q_HALF = ROWS * 128;               // 16 KB; a Q tile has D / 64 = 2 of them
 constexpr int Q_BYTES = (D / 64) * Q_HALF;
@@ -40,10 +40,10 @@ constexpr int P_HALF = ROWS * 128;               // a P tile [rows][keys] has KE
 constexpr int P_BYTES = (KEYS / 64) * P_HALF;
 constexpr int KV_HALF = KEYS * 128;              // a K or V tile [keys][D] has D / 64 = 2 of them
 constexpr int KV_TILE = (D / 64) * KV_HALF;
-constexpr int TILES_BYTES = NQ * (Q_BYTES + P_BYTES) + KV_STAGES * 2 * KV_TILE;   // 192 KB
+constexpr int TILES_BYTES = NQ * (Q_BYTES + P_BYTES) + KV_STAGES * 2 * KV_TILE;   // 224 KB
 constexpr int BAR_BYTES = 256;                   // mbarriers, the TMEM address, the abort flag: behind the tiles
 constexpr int DYN_SMEM = TILES_BYTES + BAR_BYTES + 1024;  // + what aligning the tiles to 1024 bytes may cost
-constexpr int TMEM_COLS = 512;                   // S of both tiles (2 x 64 columns), O of both (2 x 128)
+constexpr int TMEM_COLS = 512;                   // two S buffers per query tile (4 x 64 columns), O of both (2 x 128)
 constexpr int NTHREADS = 64 + NQ * 128;          // warp 0 TMA, warp 1 MMA, four softmax warps per query tile
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
@@ -77,6 +77,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// test_wait never suspends the thread (try_wait may, for a time the hardware chooses): for loops that watch
+// several barriers at once
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
@@ -217,8 +226,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   uint64_t* q_full = bars;
   uint64_t* kv_full = bars + 1;              // [KV_STAGES]
   uint64_t* kv_empty = kv_full + KV_STAGES;  // [KV_STAGES]
-  uint64_t* s_full = kv_empty + KV_STAGES;   // [NQ] the scores of a tile are in tensor memory
-  uint64_t* p_full = s_full + NQ;            // [NQ] P is in shared memory and O is rescaled (128 arrivals)
+  uint64_t* s_full = kv_empty + KV_STAGES;   // [NQ][2] the scores of an even / odd key tile are in tensor memory
+  uint64_t* p_full = s_full + 2 * NQ;        // [NQ] P is in shared memory and O is rescaled (128 arrivals)
   uint64_t* pv_done = p_full + NQ;           // [NQ] the P V contraction of a tile has finished
   uint32_t* tmem_slot = (uint32_t*)(pv_done + NQ);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
@@ -249,7 +258,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     mbar_init(q_full, 1);
     for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
     for (int x = 0; x < NQ; ++x) {
-      mbar_init(&s_full[x], 1);
+      mbar_init(&s_full[2 * x], 1);
+      mbar_init(&s_full[2 * x + 1], 1);
       mbar_init(&p_full[x], 128);
       mbar_init(&pv_done[x], 1);
     }
@@ -264,84 +274,122 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // tile x: scores in columns [64 x, 64 x + 64), output in [128 + 128 x, 256 + 128 x)
-  auto tmem_s = [&](int x) { return tmem_base + (uint32_t)(x * KEYS); };
-  auto tmem_o = [&](int x) { return tmem_base + (uint32_t)(NQ * KEYS + x * D); };
+  // query tile x: scores of key tile t in columns [64 (2 x + t % 2), + 64), output in [256 + 128 x, + 128)
+  auto tmem_s = [&](int x, int t) { return tmem_base + (uint32_t)((2 * x + (t & 1)) * KEYS); };
+  auto tmem_o = [&](int x) { return tmem_base + (uint32_t)(2 * NQ * KEYS + x * D); };
 
-  if (warp == 0 && lane == 0) {
-    // ------------------------------------------------ producer: the Q tiles once, then K and V tiles page by page
-    mbar_expect_tx(q_full, nq * Q_BYTES);
-    for (int x = 0; x < nq; ++x) {
-      tma_load_2d(q_s + x * Q_BYTES, &tmQ, q_full, (head0 + x) * D, row0);
-      tma_load_2d(q_s + x * Q_BYTES + Q_HALF, &tmQ, q_full, (head0 + x) * D + 64, row0);
+  if (warp == 0) {
+    // ------------------------------------------------ producer: the Q tiles once, then K and V tiles page by page.
+    // Lane 0 issues the copies; the warp reads the block table 32 entries at a time (one coalesced load for
+    // several tiles ahead), so no copy waits for a table lookup of its own.
+    if (lane == 0) {
+      mbar_expect_tx(q_full, nq * Q_BYTES);
+      for (int x = 0; x < nq; ++x) {
+        tma_load_2d(q_s + x * Q_BYTES, &tmQ, q_full, (head0 + x) * D, row0);
+        tma_load_2d(q_s + x * Q_BYTES + Q_HALF, &tmQ, q_full, (head0 + x) * D + 64, row0);
+      }
     }
-    const int pages = KEYS / p.bs;
+    const int pages = KEYS / p.bs;          // pages per key tile: 1..8
+    const int per_batch = 32 / pages;       // key tiles whose table entries one load brings
+    int entry = 0;
     for (int j = 0; j < n_tiles; ++j) {
+      const int in_batch = j % per_batch;
+      if (in_batch == 0) {
+        const int tj = j + lane / pages;
+        const int kp = (first_tile + tj) * KEYS + (lane % pages) * p.bs;
+        entry = (lane < per_batch * pages && tj < n_tiles && kp < hi) ? table[kp / p.bs] : 0;
+      }
       const int s = j % KV_STAGES;
-      if (j >= KV_STAGES && !mbar_wait(&kv_empty[s], ((j / KV_STAGES) & 1) ^ 1, p.err, abort_flag)) break;
+      int ok = 1;
+      if (lane == 0 && j >= KV_STAGES) ok = mbar_wait(&kv_empty[s], ((j / KV_STAGES) & 1) ^ 1, p.err, abort_flag) ? 1 : 0;
+      if (!__shfl_sync(0xffffffffu, ok, 0)) break;
       uint8_t* ks = kv_s + s * 2 * KV_TILE;
       uint8_t* vs = ks + KV_TILE;
-      mbar_expect_tx(&kv_full[s], 2 * KV_TILE);
-      const int key0 = (first_tile + j) * KEYS;
-      for (int pg = 0; pg < pages; ++pg) {
-        int kp = key0 + pg * p.bs;
-        int blk = kp < hi ? table[kp / p.bs] : 0;
+      if (lane == 0) mbar_expect_tx(&kv_full[s], 2 * KV_TILE);
+      __syncwarp();
+      // one copy per lane: a page needs four (keys and values, two 64-wide halves each), a tile has up to 8 pages;
+      // a single thread would need about as long to issue them as the tensor pipe needs for the tile
+      const int pg = lane >> 2, which = lane & 3;
+      int blk = __shfl_sync(0xffffffffu, entry, in_batch * pages + (pg < pages ? pg : 0));
+      if (pg < pages) {
+        const int kp = (first_tile + j) * KEYS + pg * p.bs;
         if (blk < 0 || blk >= p.n_blocks) {
           // keys before the window may have given their page back; they are masked. Anything else is an error.
           if (kp + p.bs > lo_min && kp < hi && p.err) atomicExch(p.err, CUCA_ERR_BLOCK_RANGE);
           blk = 0;
         }
         const int grow = (blk * p.nkv + kvh) * p.bs;  // row of the page in the pool seen as [rows][D]
-        const int off = pg * p.bs * 128;              // bytes: bs rows of 128 B inside a half
-        tma_load_2d(ks + off, &tmK, &kv_full[s], 0, grow);
-        tma_load_2d(ks + KV_HALF + off, &tmK, &kv_full[s], 64, grow);
-        tma_load_2d(vs + off, &tmV, &kv_full[s], 0, grow);
-        tma_load_2d(vs + KV_HALF + off, &tmV, &kv_full[s], 64, grow);
+        uint8_t* dst = ((which & 2) ? vs : ks) + ((which & 1) ? KV_HALF : 0) + pg * p.bs * 128;  // bs rows of 128 B
+        tma_load_2d(dst, (which & 2) ? &tmV : &tmK, &kv_full[s], (which & 1) ? 64 : 0, grow);
       }
     }
   } else if (warp == 1 && lane == 0) {
     // ------------------------------------------------ MMA issuer
-    // The two query tiles take turns: while the softmax threads of one work on its scores, the tensor pipe runs
-    // the other's P V and its next scores. Per key tile j: P V of tile 0, scores j + 1 of tile 0, P V of tile 1,
-    // scores j + 1 of tile 1; the key tile is handed back after the last P V that reads its values.
+    // Scores run one key tile ahead of the softmax: each query tile has two S buffers, so when its softmax threads
+    // hand over P of key tile j, the scores of j + 1 are already there and those of j + 2 are requested behind the
+    // P V of j. The two query tiles share the tensor pipe: whatever is ready is issued (keys landed and an S buffer
+    // free -> scores; P handed over -> P V), neither waits for the other. A key/value stage goes back to the
+    // producer after the last P V that reads it.
     constexpr uint32_t idesc_qk = instr_desc(false, KEYS), idesc_pv = instr_desc(true, D);
     bool ok = mbar_wait(q_full, 0, p.err, abort_flag);
-    auto scores = [&](int x, int t) {  // S_x = Q_x K_t^T: 8 steps of 16 head dimensions, 32 bytes inside a 64-wide half
+    auto scores = [&](int x, int t) {  // S_x[t % 2] = Q_x K_t^T: 8 steps of 16 head dimensions, 32 bytes inside a 64-wide half
+      tc_fence_after();
       const uint32_t qa = smem_u32(q_s + x * Q_BYTES);
       const uint32_t ka = smem_u32(kv_s + (t % KV_STAGES) * 2 * KV_TILE);
 #pragma unroll
       for (int k = 0; k < D / 16; ++k) {
         const uint32_t in_half = (k % 4) * 32;
-        umma_bf16(tmem_s(x), desc_kmajor(qa + (k / 4) * Q_HALF + in_half), desc_kmajor(ka + (k / 4) * KV_HALF + in_half),
+        umma_bf16(tmem_s(x, t), desc_kmajor(qa + (k / 4) * Q_HALF + in_half), desc_kmajor(ka + (k / 4) * KV_HALF + in_half),
                   idesc_qk, k > 0);
       }
-      umma_commit(&s_full[x]);
+      umma_commit(&s_full[2 * x + (t & 1)]);
     };
-    if (ok) ok = mbar_wait(&kv_full[0], 0, p.err, abort_flag);
-    if (ok) {
-      tc_fence_after();
-      for (int x = 0; x < nq; ++x) scores(x, 0);
-    }
-    for (int j = 0; ok && j < n_tiles; ++j) {
-      const int s = j % KV_STAGES;
-      const uint32_t va = smem_u32(kv_s + s * 2 * KV_TILE) + KV_TILE;
-      if (j + 1 < n_tiles) ok = mbar_wait(&kv_full[(j + 1) % KV_STAGES], ((j + 1) / KV_STAGES) & 1, p.err, abort_flag);
-      for (int x = 0; ok && x < nq; ++x) {
-        // O_x += P_x V_j once the softmax threads of tile x have written P and rescaled O
-        if (!mbar_wait(&p_full[x], j & 1, p.err, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t pa = smem_u32(p_s + x * P_BYTES);
+    int next_sc[NQ] = {0, 0}, next_pv[NQ] = {0, 0};
+    if (nq < NQ) next_sc[1] = next_pv[1] = n_tiles;  // no second query tile
+    unsigned long long idle_since = 0;
+    unsigned spins = 0;
+    while (ok && (next_pv[0] < n_tiles || next_pv[1] < n_tiles)) {
+      bool progressed = false;
 #pragma unroll
-        for (int k = 0; k < KEYS / 16; ++k) {
-          // A = P[rows][keys] K-major: 16 keys = 32 bytes inside a 64-key half.
-          // B = V[keys][dims] MN-major: 16 keys = two 8-key groups of 1024 bytes; dims 64..127 in the second half.
-          const uint32_t aoff = (k / 4) * P_HALF + (k % 4) * 32;
-          umma_bf16(tmem_o(x), desc_kmajor(pa + aoff), desc_mnmajor(va + k * 2048, KV_HALF, 1024), idesc_pv,
-                    (j > 0 || k > 0));
+      for (int x = 0; x < NQ; ++x) {
+        // scores of key tile t need its keys and the S buffer that the softmax of t - 2 has let go
+        const int t = next_sc[x];
+        if (t < n_tiles && t <= next_pv[x] + 1 && mbar_test_wait(&kv_full[t % KV_STAGES], (t / KV_STAGES) & 1)) {
+          scores(x, t);
+          ++next_sc[x];
+          progressed = true;
         }
-        if (x == nq - 1) umma_commit(&kv_empty[s]);
-        umma_commit(&pv_done[x]);
-        if (j + 1 < n_tiles) scores(x, j + 1);  // its scores were read before P was handed over
+        const int j = next_pv[x];
+        if (j < n_tiles && j < next_sc[x] && mbar_test_wait(&p_full[x], j & 1)) {
+          // O_x += P_x V_j: the softmax threads of tile x have written P and rescaled O
+          tc_fence_after();
+          const int s = j % KV_STAGES;
+          const uint32_t pa = smem_u32(p_s + x * P_BYTES), va = smem_u32(kv_s + s * 2 * KV_TILE) + KV_TILE;
+#pragma unroll
+          for (int k = 0; k < KEYS / 16; ++k) {
+            // A = P[rows][keys] K-major: 16 keys = 32 bytes inside a 64-key half.
+            // B = V[keys][dims] MN-major: 16 keys = two 8-key groups of 1024 bytes; dims 64..127 in the second half.
+            const uint32_t aoff = (k / 4) * P_HALF + (k % 4) * 32;
+            umma_bf16(tmem_o(x), desc_kmajor(pa + aoff), desc_mnmajor(va + k * 2048, KV_HALF, 1024), idesc_pv,
+                      (j > 0 || k > 0));
+          }
+          ++next_pv[x];
+          if (next_pv[x ^ 1] > j) umma_commit(&kv_empty[s]);  // the other query tile is past this key tile too
+          umma_commit(&pv_done[x]);
+          progressed = true;
+        }
+      }
+      if (progressed) {
+        idle_since = 0;
+      } else if ((++spins & 63u) == 0) {
+        if (*abort_flag) break;
+        const unsigned long long now = global_ns();
+        if (idle_since == 0) idle_since = now;
+        else if (now - idle_since > WAIT_LIMIT_NS) {
+          if (p.err) atomicExch(p.err, CUCA_ERR_WAIT_TIMEOUT);
+          *abort_flag = 1;
+          break;
+        }
       }
     }
   } else if (warp >= 2) {
@@ -358,7 +406,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     bool ok = x < nq;
     for (int j = 0; ok && j < n_tiles; ++j) {
       // the tcgen05.ld/st below are warp-wide: a warp leaves the loop together or not at all
-      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[x], j & 1, p.err, abort_flag))) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[2 * x + (j & 1)], (j >> 1) & 1, p.err, abort_flag))) { ok = false; break; }
       tc_fence_after();
       const int key0 = (first_tile + j) * KEYS;
       const bool whole = key0 >= lo_min && key0 + KEYS - 1 <= pos0 && (p.window <= 0 || key0 >= pos0 + ROWS - 1 - (p.window - 1));
@@ -366,23 +414,29 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       constexpr int NC = KEYS / 32;  // groups of 32 scores
       uint32_t raw[NC][32];
 #pragma unroll
-      for (int c = 0; c < NC; ++c) tmem_ld32_nowait(tmem_s(x) + lane_bits + c * 32, raw[c]);
+      for (int c = 0; c < NC; ++c) tmem_ld32_nowait(tmem_s(x, j) + lane_bits + c * 32, raw[c]);
       tmem_ld_wait();
+      // the scale is positive, so the maximum is taken over the raw scores and scaled once; the scaling of every
+      // score happens inside the exponent's multiply-add
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (whole) {
+        // every row of the tile sees every key of the tile: no tests in the loop (most tiles of a long prompt)
 #pragma unroll
-      for (int c = 0; c < NC; ++c) {
+        for (int c = 0; c < NC; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(raw[c][i]) * p.scale_log2e;
-          if (!whole) {
-            int kp = key0 + c * 32 + i;
-            if (!(row_ok && kp <= row_pos && kp >= row_lo)) v = -INFINITY;
+          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(raw[c][i]));
+      } else {
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int kp = key0 + c * 32 + i;
+            if (!(row_ok && kp <= row_pos && kp >= row_lo)) raw[c][i] = 0xff800000u;  // -inf
+            mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(raw[c][i]));
           }
-          raw[c][i] = __float_as_uint(v);
-          mx4[i & 3] = fmaxf(mx4[i & 3], v);
         }
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2e;
       // The running maximum only moves when the new one exceeds it by more than 8 (in log2 units): values up to
       // 2^8 above the reference are exact enough in 32-bit sums, and O is rescaled far less often.
       float m_new = m;
@@ -402,8 +456,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           uint32_t w[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            float pa_ = fast_exp2(__uint_as_float(raw[c][q8 * 8 + 2 * e]) - m_use);
-            float pb_ = fast_exp2(__uint_as_float(raw[c][q8 * 8 + 2 * e + 1]) - m_use);
+            float pa_ = fast_exp2(fmaf(__uint_as_float(raw[c][q8 * 8 + 2 * e]), p.scale_log2e, -m_use));
+            float pb_ = fast_exp2(fmaf(__uint_as_float(raw[c][q8 * 8 + 2 * e + 1]), p.scale_log2e, -m_use));
             sum4[e] += pa_ + pb_;
             __nv_bfloat162 t2 = __floats2bfloat162_rn(pa_, pb_);
             w[e] = *reinterpret_cast<uint32_t*>(&t2);
