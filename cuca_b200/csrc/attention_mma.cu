@@ -261,20 +261,21 @@ attn_mma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tmK, con
   uint8_t* ring = ring_base + (size_t)warp * S::WSTAGES * S::WSTAGE_BYTES;
   auto group_kp0 = [&](int j) { return (first_tile + ti_lo + j) * TILE + warp * 16; };
   auto page_of = [&](int j) { return table[group_kp0(j) >> bs_shift]; };
-  auto issue_group = [&](int j, int page) {  // lane 0 only
+  auto issue_group = [&](int j, int page) {  // the whole warp: one copy per lane (keys and values, 64-wide halves)
     const int kp0 = group_kp0(j);
     if (page < 0 || page >= p.n_blocks) {
-      if (p.err) atomicExch(p.err, CUCA_ERR_BLOCK_RANGE);
+      if (lane == 0 && p.err) atomicExch(p.err, CUCA_ERR_BLOCK_RANGE);
       page = 0;  // any readable page: these keys are masked or the step is lost anyway
     }
     const int row = ((page * p.nkv + kvh) << bs_shift) + (kp0 & bs_mask);
     const int st = j % S::WSTAGES;
     uint8_t* dst = ring + (size_t)st * S::WSTAGE_BYTES;
-    mbar_expect_tx(&w_full[warp][st], S::WSTAGE_BYTES);
-#pragma unroll
-    for (int h = 0; h < S::HALVES; ++h) {
-      tma_load_2d(dst + h * S::SUB_BYTES, &tmK, &w_full[warp][st], 64 * h, row);
-      tma_load_2d(dst + (S::HALVES + h) * S::SUB_BYTES, &tmV, &w_full[warp][st], 64 * h, row);
+    if (lane == 0) mbar_expect_tx(&w_full[warp][st], S::WSTAGE_BYTES);
+    __syncwarp();
+    if (lane < 2 * S::HALVES) {
+      const int h = lane % S::HALVES;
+      const bool values = lane >= S::HALVES;
+      tma_load_2d(dst + lane * S::SUB_BYTES, values ? &tmV : &tmK, &w_full[warp][st], 64 * h, row);
     }
   };
   if (TMA) {
@@ -293,10 +294,13 @@ attn_mma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tmK, con
     ti_lo = lo;
     n_mine = hi > lo ? hi - lo : 0;
     __syncthreads();  // barriers and the abort flag are set up
-    if (lane == 0) {
+    {
       int pg[S::WSTAGES];
 #pragma unroll
-      for (int j = 0; j < S::WSTAGES; ++j) pg[j] = j < n_mine ? page_of(j) : -1;
+      for (int j = 0; j < S::WSTAGES; ++j) {
+        pg[j] = (lane == 0 && j < n_mine) ? page_of(j) : -1;
+        pg[j] = __shfl_sync(0xffffffffu, pg[j], 0);
+      }
 #pragma unroll
       for (int j = 0; j < S::WSTAGES - 1; ++j)
         if (j < n_mine) issue_group(j, pg[j]);
@@ -484,11 +488,12 @@ attn_mma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tmK, con
     // every warp walks its own groups through its own ring: no block-wide barrier in the loop
     bool ok = true;
     for (int i = 0; i < n_mine && ok; ++i) {
-      if (lane == 0) {
+      {
         // group i + WSTAGES - 1 goes into the stage that group i - 1 left; the page of the one after is looked up now
+        // (by lane 0, which hands it to the warp one round later)
         const int j = i + S::WSTAGES - 1;
-        const int page_j = next_page;
-        if (j + 1 < n_mine) next_page = page_of(j + 1);
+        const int page_j = __shfl_sync(0xffffffffu, next_page, 0);
+        if (lane == 0 && j + 1 < n_mine) next_page = page_of(j + 1);
         if (j < n_mine) issue_group(j, page_j);
       }
       const int st_i = i % S::WSTAGES;
