@@ -5,11 +5,10 @@ from __future__ import annotations
 
 import json
 import time
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from pathlib import Path
 from typing import Iterable, Optional, Sequence
 
-import numpy as np
 import torch
 
 from ..config.engine_config import LocalModelConfig, SamplingConfig

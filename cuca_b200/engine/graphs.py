@@ -9,9 +9,8 @@ back to back without the host (`burst`), which is how the device-only decode rat
 """
 from __future__ import annotations
 
-from typing import Optional, Sequence
+from typing import Sequence
 
-import numpy as np
 import torch
 
 from ..kernels import ops

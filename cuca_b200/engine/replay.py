@@ -20,7 +20,6 @@ import json
 import sys
 from pathlib import Path
 
-import numpy as np
 
 from .core import EngineCore
 from .step import StepEntry

@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import threading
-from ctypes import c_float, c_int, c_size_t, c_uint64, c_void_p
+from ctypes import c_float, c_int, c_size_t, c_void_p
 
 from . import build as _build
 

@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from ..parts import attention, block, embedding, mlp, norm, rope  # noqa: F401  (register the built-in parts)
-from ..parts.base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, CacheNeeds, TensorNeed
+from ..parts.base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, TensorNeed
 from ..parts.embedding import OutputHead, TokenEmbedding
 from ..weights import loader
 from .spec import ModelSpec

@@ -9,7 +9,6 @@ import tempfile
 from pathlib import Path
 
 import numpy as np
-import torch
 
 import plain_llama
 

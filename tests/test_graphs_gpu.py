@@ -1,7 +1,6 @@
 """Decode through captured CUDA graphs: same tokens as the eager step, page tables kept in step, bursts."""
 import numpy as np
 import pytest
-import torch
 
 import plain_llama
 import tiny

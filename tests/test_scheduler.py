@@ -2,7 +2,7 @@
 import pytest
 
 from cuca_b200.cache.pages import GroupLayout, KvPools, StateSlots
-from cuca_b200.engine.scheduler import (DECODE, PREFILL, Request, RequestError, Scheduler, SchedulerConfig,
+from cuca_b200.engine.scheduler import (DECODE, Request, RequestError, Scheduler, SchedulerConfig,
                                         prefill_chunk_for)
 
 

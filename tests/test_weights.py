@@ -1,7 +1,6 @@
 """Weights: safetensors reading and writing, binding by name, the one error, random-weights folders."""
 import json
 
-import numpy as np
 import pytest
 import torch
 
