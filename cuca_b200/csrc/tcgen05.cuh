@@ -74,6 +74,25 @@ __device__ __forceinline__ void tma_load_2d_hint(void* dst, const CUtensorMap* m
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "l"(policy)
       : "memory");
 }
+// Shared memory -> global memory through a tensor map (the box is clipped at the tensor's bounds), as one bulk
+// group member of the issuing thread: plain store, or 32-bit add into what is there.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Until at most N of this thread's bulk groups have not yet read their shared memory.
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Makes this thread's shared-memory writes visible to the copy engine.
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 // Policy for data that is read once (a decode step's weights are far larger than L2): first to be evicted.
 __device__ __forceinline__ uint64_t l2_evict_first() {
   uint64_t policy;
@@ -142,4 +161,7 @@ __host__ __device__ constexpr uint32_t instr_desc(int n) {
 // elements, 128-byte swizzle. Maps are cached by their arguments. False if the driver refuses the map.
 bool cuca_tensor_map_bf16(const void* ptr, uint64_t rows, uint64_t cols, uint64_t stride, uint32_t box_rows,
                           CUtensorMap* out);
+// The same for elements of 2 (bf16) or 4 (32-bit float) bytes: the box is box_rows x 128 bytes.
+bool cuca_tensor_map_2d(const void* ptr, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t stride,
+                        uint32_t box_rows, CUtensorMap* out);
 int cuca_device_sms();

@@ -29,7 +29,8 @@ def _ref_gemm(a, w, epilogue, bias, prior):
 
 GEMM_SHAPES = [(1, 64, 64), (3, 96, 96), (8, 176, 64), (16, 128, 200), (17, 331, 120), (33, 1000, 320),
                (64, 512, 1024), (100, 264, 4096), (130, 640, 256), (300, 384, 136), (8, 4096, 4096),
-               (65, 176, 96), (256, 1000, 320), (640, 128, 64), (40, 2304, 512)]
+               (65, 176, 96), (256, 1000, 320), (640, 128, 64), (40, 2304, 512),
+               (2048, 4096, 512), (1300, 5000, 1160)]  # more tiles than SMs: the last round's K steps are dealt out
 
 
 @pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
