@@ -53,7 +53,9 @@ struct Params {
   int tiles;     // all tiles
   int ksteps;    // K steps per tile
   int stream_k;  // 0: whole tiles in turn; 1: units dealt out evenly; 2: per_tile even K slices of every tile
-  int full_tiles;  // mode 1: the first full_tiles tiles are still taken whole, in turn; the units of the rest are dealt out
+  // more than 64 tokens but fewer tiles than SMs (mode 0): instead of whole tiles, `pieces` column pieces of
+  // `piece_w` output columns over all of K, one per CTA
+  int pieces, piece_w;
   int per_tile;  // mode 2: CTAs per tile
   int max_parts; // workspace slots per tile
   int tma_out;   // many tokens: whole tiles leave through shared memory and the copy engine (tensor map of `out`)
@@ -88,28 +90,50 @@ struct Cfg {
 // One CTA's run of work: segments (tile, K steps [ks0, ks1)) in the order every role walks them.
 struct Segment {
   int tile, ks0, ks1, part, nparts;
+  int a0, b0;  // first row of the 128-row operand, first output column (of the column operand)
+  int w;       // output columns
 };
 struct SegmentWalk {
   const Params& p;
   long long u, u_end;   // stream-K: unit cursor
   int tile_cursor;      // whole tiles: next tile
-  __device__ SegmentWalk(const Params& prm) : p(prm) {
-    const long long U = (long long)(p.tiles - p.full_tiles) * p.ksteps, G = gridDim.x;
+  int out_cols;         // output columns of a whole tile
+  bool piece_done;
+  __device__ SegmentWalk(const Params& prm, int cols) : p(prm), out_cols(cols), piece_done(false) {
+    const long long U = (long long)p.tiles * p.ksteps, G = gridDim.x;
     u = (long long)blockIdx.x * U / G;
     u_end = ((long long)blockIdx.x + 1) * U / G;
     tile_cursor = blockIdx.x;
   }
+  __device__ void origin(Segment& s) const {
+    s.a0 = (s.tile % p.tiles_a) * TILE_A;
+    s.b0 = (s.tile / p.tiles_a) * out_cols;
+    s.w = out_cols;
+  }
   __device__ bool next(Segment& s) {
     if (!p.stream_k) {
-      if (tile_cursor >= p.tiles) return false;
-      s.tile = tile_cursor; s.ks0 = 0; s.ks1 = p.ksteps; s.part = 0; s.nparts = 1;
-      tile_cursor += gridDim.x;
+      s.ks0 = 0; s.ks1 = p.ksteps; s.part = 0; s.nparts = 1;
+      if (!p.pieces) {
+        if (tile_cursor >= p.tiles) return false;
+        s.tile = tile_cursor;
+        origin(s);
+        tile_cursor += gridDim.x;
+        return true;
+      }
+      // column piece number blockIdx.x: neighbouring CTAs take the same columns of different row blocks
+      if (piece_done) return false;
+      piece_done = true;
+      s.tile = p.tiles;  // no whole tile
+      s.a0 = ((int)blockIdx.x % p.tiles_a) * TILE_A;
+      s.b0 = ((int)blockIdx.x / p.tiles_a) * p.piece_w;
+      s.w = p.piece_w;
       return true;
     }
     if (p.stream_k == 2) {
       // one K slice of one tile per CTA
       if (tile_cursor < 0) return false;
       s.tile = (int)blockIdx.x / p.per_tile;
+      origin(s);
       s.part = (int)blockIdx.x % p.per_tile;
       s.nparts = p.per_tile;
       s.ks0 = (int)((long long)s.part * p.ksteps / p.per_tile);
@@ -117,21 +141,16 @@ struct SegmentWalk {
       tile_cursor = -1;
       return true;
     }
-    if (tile_cursor < p.full_tiles) {
-      s.tile = tile_cursor; s.ks0 = 0; s.ks1 = p.ksteps; s.part = 0; s.nparts = 1;
-      tile_cursor += gridDim.x;
-      return true;
-    }
     if (u >= u_end) return false;
-    const long long K = p.ksteps, U = (long long)(p.tiles - p.full_tiles) * K, G = gridDim.x;
-    const int rest_tile = (int)(u / K);  // among the tiles whose units are dealt out
-    s.tile = p.full_tiles + rest_tile;
+    const long long K = p.ksteps, U = (long long)p.tiles * K, G = gridDim.x;
+    s.tile = (int)(u / K);
+    origin(s);
     s.ks0 = (int)(u % K);
     long long left = u_end - u;
     s.ks1 = (int)((K - s.ks0 < left) ? K : s.ks0 + left);
     u += s.ks1 - s.ks0;
     // CTAs whose share touches this tile: first .. last
-    long long t0 = (long long)rest_tile * K, t1 = t0 + K;
+    long long t0 = (long long)s.tile * K, t1 = t0 + K;
     int first = (int)(((t0 + 1) * G + U - 1) / U) - 1;
     int last = (int)((t1 * G + U - 1) / U) - 1;
     s.part = (int)blockIdx.x - first;
@@ -226,14 +245,13 @@ __device__ __forceinline__ void store16(const Params& p, int a0, int b0, int lan
 // per lane and instruction: measured, 13 us per tile of the output projection against 26 us of main loop.
 template <bool DUAL>
 __device__ __forceinline__ void tma_epilogue(const Params& p, const CUtensorMap* tmO, uint32_t acc, int a0, int b0,
-                                             int quarter, int lane, uint8_t* staging, int& chunk_no) {
+                                             int width, int quarter, int lane, uint8_t* staging, int& chunk_no) {
   const int y0 = a0 + quarter * 32;
-  const int ch = p.out_f32 ? 32 : 64;
-  constexpr int OUT_COLS = DUAL ? 128 : 256;
+  const int ch = p.out_f32 ? 32 : 64;  // the host cuts column pieces in whole runs
   uint8_t* const my_row = staging + lane * 128;
   const int sw = lane & 7;
 #pragma unroll 1
-  for (int c = 0; c < OUT_COLS; c += ch) {
+  for (int c = 0; c < width; c += ch) {
     uint8_t* row = my_row + (chunk_no & 1) * STAGING_BUF;
     if (lane == 0) bulk_wait_read<1>();  // the copy that last used this buffer has read it
     __syncwarp();
@@ -324,27 +342,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // rows of the two operands in global memory for a tile: the 128-row operand (A) and the column operand (B)
-  auto tile_origin = [&](int tile, int& a0, int& b0) {
-    a0 = (tile % p.tiles_a) * TILE_A;
-    b0 = (tile / p.tiles_a) * C::OUT_COLS;
-  };
   // weights and activations of one stage: which is which depends on the orientation
   // few tokens: every weight is read once per step, so it should not displace what is read again (activations,
   // partial sums, keys and values)
   const uint64_t once = SWAP ? l2_evict_first() : 0;
-  auto load_weights = [&](uint8_t* st, uint64_t* bar, int a0, int b0, int kc) {
+  // bytes a stage of this segment receives: a column piece of up to 128 weight rows needs one box of them only
+  auto stage_tx = [&](const Segment& s) -> uint32_t {
+    return C::STAGE_BYTES - ((!SWAP && !DUAL && s.w <= 128) ? 128 * TILE_K * 2 : 0);
+  };
+  auto load_weights = [&](uint8_t* st, uint64_t* bar, const Segment& s, int kc) {
     if (SWAP) {
-      tma_load_2d_hint(st, &tmA, bar, kc, a0, once);
-      if (DUAL) tma_load_2d_hint(st + TILE_A * TILE_K * 2, &tmA, bar, kc, p.N + a0, once);
+      tma_load_2d_hint(st, &tmA, bar, kc, s.a0, once);
+      if (DUAL) tma_load_2d_hint(st + TILE_A * TILE_K * 2, &tmA, bar, kc, p.N + s.a0, once);
     } else {
-      tma_load_2d(st + C::A_BYTES, &tmB, bar, kc, b0);
-      tma_load_2d(st + C::A_BYTES + 128 * TILE_K * 2, &tmB, bar, kc, DUAL ? p.N + b0 : b0 + 128);
+      tma_load_2d(st + C::A_BYTES, &tmB, bar, kc, s.b0);
+      if (DUAL || s.w > 128) tma_load_2d(st + C::A_BYTES + 128 * TILE_K * 2, &tmB, bar, kc, DUAL ? p.N + s.b0 : s.b0 + 128);
     }
   };
-  auto load_activations = [&](uint8_t* st, uint64_t* bar, int a0, int b0, int kc) {
-    if (SWAP) tma_load_2d(st + C::A_BYTES, &tmB, bar, kc, b0);
-    else tma_load_2d(st, &tmA, bar, kc, a0);
+  auto load_activations = [&](uint8_t* st, uint64_t* bar, const Segment& s, int kc) {
+    if (SWAP) tma_load_2d(st + C::A_BYTES, &tmB, bar, kc, s.b0);
+    else tma_load_2d(st, &tmA, bar, kc, s.a0);
   };
 
   if ((warp == 0 || warp == 6) && lane == 0) {
@@ -352,50 +369,47 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int mine = warp == 0 ? 0 : 1;
     // the first ring of weight tiles is requested before waiting for the predecessor kernel
     {
-      SegmentWalk pre(p);
+      SegmentWalk pre(p, C::OUT_COLS);
       Segment s;
       int it = 0;
       const int ahead = C::STAGES;
       while (it < ahead && pre.next(s)) {
-        int a0, b0;
-        tile_origin(s.tile, a0, b0);
         for (int ks = s.ks0; ks < s.ks1 && it < ahead; ++ks, ++it) {
           if (it % NPROD != mine) continue;
-          mbar_expect_tx(&full[it], C::STAGE_BYTES);
-          load_weights(smem + it * C::STAGE_BYTES, &full[it], a0, b0, ks * TILE_K);
+          mbar_expect_tx(&full[it], stage_tx(s));
+          load_weights(smem + it * C::STAGE_BYTES, &full[it], s, ks * TILE_K);
         }
       }
     }
     pdl_wait();
-    SegmentWalk walk(p);
+    SegmentWalk walk(p, C::OUT_COLS);
     Segment s;
     int it = 0;
     bool ok = true;
     while (ok && walk.next(s)) {
-      int a0, b0;
-      tile_origin(s.tile, a0, b0);
       for (int ks = s.ks0; ks < s.ks1; ++ks, ++it) {
         if (it % NPROD != mine) continue;
         const int st = it % C::STAGES;
         uint8_t* sp = smem + st * C::STAGE_BYTES;
         if (it >= C::STAGES) {
           if (!mbar_wait(&empty[st], ((it / C::STAGES) & 1) ^ 1, p.err, abort_flag)) { ok = false; break; }
-          mbar_expect_tx(&full[st], C::STAGE_BYTES);
-          load_weights(sp, &full[st], a0, b0, ks * TILE_K);
+          mbar_expect_tx(&full[st], stage_tx(s));
+          load_weights(sp, &full[st], s, ks * TILE_K);
         }
-        load_activations(sp, &full[st], a0, b0, ks * TILE_K);
+        load_activations(sp, &full[st], s, ks * TILE_K);
       }
     }
   } else if (warp == 1 && lane == 0) {
     // ------------------------------------------------ MMA issuer
     pdl_wait();
-    constexpr uint32_t idesc = instr_desc(C::MMA_N);
-    SegmentWalk walk(p);
+    SegmentWalk walk(p, C::OUT_COLS);
     Segment s;
     int it = 0, seg = 0;
     bool ok = true;
     while (ok && walk.next(s)) {
       const int buf = seg & 1;
+      // a column piece is narrower than a tile (never with SwiGLU, whose tile is 128 gate and 128 up columns)
+      const uint32_t idesc = instr_desc((SWAP || DUAL) ? C::MMA_N : s.w);
       if (!mbar_wait(&tmem_empty[buf], ((seg >> 1) & 1) ^ 1, p.err, abort_flag)) break;
       tc_fence_after();
       const uint32_t acc = tmem_base + buf * C::NCOLS;
@@ -425,7 +439,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int quarter = warp & 3;               // the TMEM lanes this warp may read
     const int lane_row = quarter * 32 + lane;   // row of the 128-row operand
     const int eidx = (warp - 2) * 32 + lane;    // 0..127 among the epilogue threads
-    SegmentWalk walk(p);
+    SegmentWalk walk(p, C::OUT_COLS);
     Segment s;
     int seg = 0, chunk_no = 0;
     while (walk.next(s)) {
@@ -435,8 +449,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       epilogue_sync();
       if (!seg_ok[buf]) break;
       tc_fence_after();
-      int a0, b0;
-      tile_origin(s.tile, a0, b0);
+      const int a0 = s.a0, b0 = s.b0;
       const uint32_t acc = tmem_base + buf * C::NCOLS + ((uint32_t)(quarter * 32) << 16);
       if (SWAP && !DUAL && p.epilogue == EPI_PARTIAL) {
         // this K slice's partial sums go out as they are, [slice][token][feature]; whoever reads them adds them up
@@ -456,13 +469,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         __syncwarp();
         if (lane == 0) mbar_arrive(&tmem_empty[buf]);
       } else if (!SWAP && s.nparts == 1 && p.tma_out) {
-        tma_epilogue<DUAL>(p, &tmO, acc, a0, b0, quarter, lane, staging + (warp - 2) * (2 * STAGING_BUF), chunk_no);
+        tma_epilogue<DUAL>(p, &tmO, acc, a0, b0, s.w, quarter, lane, staging + (warp - 2) * (2 * STAGING_BUF), chunk_no);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tmem_empty[buf]);
       } else if (s.nparts == 1) {
 #pragma unroll 1
-        for (int c = 0; c < C::OUT_COLS; c += 16) {
+        for (int c = 0; c < (SWAP ? C::OUT_COLS : s.w); c += 16) {
           float v[16], u[16];
           tmem_ld16(acc + c, v);
           if (DUAL) tmem_ld16(acc + (SWAP ? BN : 128) + c, u);
@@ -473,8 +486,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (lane == 0) mbar_arrive(&tmem_empty[buf]);
       } else {
         // a part of a tile: park it in the workspace, [tile][part][column][lane]
-        const int split_tile = s.tile - p.full_tiles;  // workspace and counters are numbered from the first split tile
-        float* ws = p.workspace + ((size_t)split_tile * p.max_parts + s.part) * C::NCOLS * TILE_A;
+        float* ws = p.workspace + ((size_t)s.tile * p.max_parts + s.part) * C::NCOLS * TILE_A;
 #pragma unroll 1
         for (int c = 0; c < C::NCOLS; c += 16) {
           float v[16];
@@ -487,13 +499,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (lane == 0) mbar_arrive(&tmem_empty[buf]);  // the accumulator is free while the parts are added
         __threadfence();
         epilogue_sync();
-        if (eidx == 0) *last_flag = (atomicAdd(&p.counters[split_tile], 1) == s.nparts - 1) ? 1 : 0;
+        if (eidx == 0) *last_flag = (atomicAdd(&p.counters[s.tile], 1) == s.nparts - 1) ? 1 : 0;
         epilogue_sync();
         const bool last = *last_flag != 0;
         epilogue_sync();  // everyone has read the flag before a later segment rewrites it
         if (last) {
           __threadfence();
-          const float* base = p.workspace + (size_t)split_tile * p.max_parts * C::NCOLS * TILE_A + lane_row;
+          const float* base = p.workspace + (size_t)s.tile * p.max_parts * C::NCOLS * TILE_A + lane_row;
 #pragma unroll 1
           for (int c = 0; c < C::OUT_COLS; c += 16) {
             float v[16], u[16];
@@ -522,7 +534,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             store16<BN, DUAL, SWAP>(p, a0, b0, lane_row, c, v, u);
           }
-          if (eidx == 0) p.counters[split_tile] = 0;  // ready for the next launch
+          if (eidx == 0) p.counters[s.tile] = 0;  // ready for the next launch
         }
       }
       ++seg;
@@ -698,10 +710,29 @@ static int gemm_tc_impl(const void* A, const void* W, const void* bias, void* ou
   int grid = p.tiles < sms ? p.tiles : sms;
   p.tma_out = tma_out;
   p.stream_k = 0;
-  p.full_tiles = 0;
+  p.pieces = p.piece_w = 0;
   p.per_tile = 1;
   p.max_parts = 1;
-  if (epilogue == EPI_PARTIAL) {
+  // More than 64 tokens, fewer tiles than SMs, K not long: column pieces as narrow as it takes for about one per SM,
+  // each over all of K, so nothing is added up afterwards. (Measured at 256 tokens, K = 4096: 31 us against 57 us
+  // with K slices; with K = 14336 no gain. A piece's main loop runs at the pace of its loads, 4 stages deep, not
+  // of its MMAs, so a piece takes as long as a whole tile: cutting the last round of many tiles this way gains
+  // nothing and is not done.)
+  bool pieced = false;
+  if (!swap && !dual && p.tiles < sms && p.ksteps <= 128) {
+    const int unit = out_dtype == CUCA_F32 ? 32 : 64;  // whole 128-byte runs of the epilogue
+    for (int w = unit; w < out_cols && !pieced; w += unit) {
+      const int pieces = p.tiles_a * ((N + w - 1) / w);
+      if (pieces > sms) continue;
+      if (pieces * 2 < sms || pieces <= p.tiles) break;  // too few even at the narrowest: K is shared out below instead
+      pieced = true;
+      p.pieces = pieces;
+      p.piece_w = w;
+      grid = pieces;
+    }
+  }
+  if (pieced) {
+  } else if (epilogue == EPI_PARTIAL) {
     CUCA_REQUIRE(swap && out_dtype == CUCA_F32 && bias == nullptr && n_slices_out != nullptr,
                  "gemm_tc: partial sums are for up to 64 tokens, 32-bit, without bias");
     int per_tile = sms / p.tiles;

@@ -76,6 +76,28 @@ def test_gemm_tcgen05(dev, M, N, K, epilogue, max_splits):
     assert int(ops.gemm_scratch(dev)[1].abs().sum().item()) == 0
 
 
+@pytest.mark.parametrize("M,N,K,out_dtype,epilogue", [
+    (256, 4096, 512, torch.float32, 1), (200, 3072, 192, torch.bfloat16, 0), (130, 4000, 1024, torch.float32, 0),
+    (300, 2001, 320, torch.bfloat16, 0), (65, 6144, 256, torch.bfloat16, 0)])
+def test_gemm_tcgen05_column_pieces(dev, M, N, K, out_dtype, epilogue):
+    """More than 64 tokens but fewer whole tiles than SMs: the contraction cuts narrower column pieces, one per
+    CTA. Ragged M and N, rows that are and are not 16-byte multiples (copy-engine and plain stores), a bias."""
+    from cuca_b200.kernels import ops
+    g = torch.Generator(device=dev).manual_seed(M + N + K)
+    a = torch.randn(M, K, device=dev, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=dev, generator=g) / math.sqrt(K)).bfloat16()
+    bias = torch.randn(N, device=dev, generator=g).bfloat16() if M % 2 else None
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = torch.randn(M, N, device=dev, generator=g).to(out_dtype)
+    prior = out.clone()
+    ops.gemm_tc(a, w, out, epilogue, bias, err)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    ref = _ref_gemm(a, w, epilogue, bias, prior.float())
+    tol = 2e-2 if out_dtype == torch.bfloat16 else 2e-3
+    assert torch.allclose(out.float(), ref, atol=tol, rtol=tol), float((out.float() - ref).abs().max())
+
+
 def test_gemm_tcgen05_refuses_unaligned(dev):
     from cuca_b200.kernels import ops
     a = torch.zeros(4, 100, device=dev, dtype=torch.bfloat16)  # K = 100 is no multiple of 8
