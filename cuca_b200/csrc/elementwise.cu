@@ -277,6 +277,78 @@ rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
   }
 }
 
+// The same for bf16 rows whose heads are rotated whole (rot = d) with d a multiple of 16: a thread takes eight
+// pairs (16 bytes of each half of a head, eight cosines and sines) or 16 bytes of v at a time. Same arithmetic,
+// element by element, as the kernel above.
+__global__ void __launch_bounds__(256)
+rope_store_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
+                      const int* __restrict__ seq_of_row, const int* __restrict__ tables, int table_stride,
+                      const float* __restrict__ cos_t, const float* __restrict__ sin_t, int table_rows,
+                      __nv_bfloat16* __restrict__ kpool, __nv_bfloat16* __restrict__ vpool, int n_blocks, int bs,
+                      int nh, int nkv, int d, int* err) {
+  pdl_trigger();
+  pdl_wait();
+  const int row = blockIdx.x;
+  const int seq = seq_of_row[row];
+  if (seq < 0) return;
+  const int pos = positions[row];
+  const int half = d / 2;
+  __nv_bfloat16* base = qkv + (size_t)row * (nh + 2 * nkv) * d;
+  long long page_off = -1;
+  if (nkv > 0) {
+    int blk = pos >= 0 ? tables[(size_t)seq * table_stride + pos / bs] : -1;
+    if (blk < 0 || blk >= n_blocks) {
+      if (threadIdx.x == 0 && err) atomicExch(err, CUCA_ERR_BLOCK_RANGE);
+    } else {
+      page_off = ((long long)blk * nkv * bs + (pos % bs)) * d;
+    }
+  }
+  const bool in_table = pos >= 0 && pos < table_rows;
+  if (!in_table && threadIdx.x == 0 && err) atomicExch(err, CUCA_ERR_TOKEN_RANGE);
+  const float* cr = cos_t + (size_t)(in_table ? pos : 0) * half;
+  const float* sr = sin_t + (size_t)(in_table ? pos : 0) * half;
+  const int per_head = half / 8;  // items of eight pairs
+  const int qk_items = (nh + nkv) * per_head;
+  const int v_items = (nkv > 0 && page_off >= 0) ? nkv * d / 8 : 0;
+  for (int idx = threadIdx.x; idx < qk_items + v_items; idx += blockDim.x) {
+    if (idx >= qk_items) {
+      const int e = (idx - qk_items) * 8, kvh = e / d;
+      const uint4 v = *reinterpret_cast<const uint4*>(base + (size_t)(nh + nkv) * d + e);
+      *reinterpret_cast<uint4*>(vpool + page_off + (size_t)kvh * bs * d + (e - kvh * d)) = v;
+      continue;
+    }
+    const int head = idx / per_head, i = (idx - head * per_head) * 8;
+    __nv_bfloat16* src = base + (size_t)head * d;
+    const bool is_k = head >= nh;
+    if (is_k && page_off < 0) continue;
+    __nv_bfloat16* dst = is_k ? kpool + page_off + (size_t)(head - nh) * bs * d : src;
+    uint4 ua = *reinterpret_cast<const uint4*>(src + i), ub = *reinterpret_cast<const uint4*>(src + i + half);
+    float c[8], sn[8];
+    if (in_table) {
+      *reinterpret_cast<float4*>(c) = *reinterpret_cast<const float4*>(cr + i);
+      *reinterpret_cast<float4*>(c + 4) = *reinterpret_cast<const float4*>(cr + i + 4);
+      *reinterpret_cast<float4*>(sn) = *reinterpret_cast<const float4*>(sr + i);
+      *reinterpret_cast<float4*>(sn + 4) = *reinterpret_cast<const float4*>(sr + i + 4);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { c[j] = 1.f; sn[j] = 0.f; }
+    }
+    const __nv_bfloat16* pa = reinterpret_cast<const __nv_bfloat16*>(&ua);
+    const __nv_bfloat16* pb = reinterpret_cast<const __nv_bfloat16*>(&ub);
+    uint4 oa, ob;
+    __nv_bfloat16* qa = reinterpret_cast<__nv_bfloat16*>(&oa);
+    __nv_bfloat16* qb = reinterpret_cast<__nv_bfloat16*>(&ob);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float a = __bfloat162float(pa[j]), b = __bfloat162float(pb[j]);
+      qa[j] = __float2bfloat16_rn(a * c[j] - b * sn[j]);
+      qb[j] = __float2bfloat16_rn(a * sn[j] + b * c[j]);
+    }
+    *reinterpret_cast<uint4*>(dst + i) = oa;
+    *reinterpret_cast<uint4*>(dst + i + half) = ob;
+  }
+}
+
 CUCA_API int cuca_rope_store(void* qkv, int dtype, const int* positions, const int* seq_of_row,
                              const int* tables, int table_stride, const float* cos_t, const float* sin_t,
                              int table_rows, int rot, void* kpool, void* vpool, int n_blocks, int bs,
@@ -286,7 +358,12 @@ CUCA_API int cuca_rope_store(void* qkv, int dtype, const int* positions, const i
   CUCA_REQUIRE(bs > 0 && nh > 0 && nkv >= 0 && d > 0, "rope_store: bad sizes");
   dim3 grid(n_rows);
   int threads = 256;
-  if (dtype == CUCA_F32)
+  const bool aligned = (((uintptr_t)qkv | (uintptr_t)kpool | (uintptr_t)vpool | (uintptr_t)cos_t | (uintptr_t)sin_t) & 15) == 0;
+  if (dtype == CUCA_BF16 && rot == d && d % 16 == 0 && aligned)
+    cuca_launch(rope_store_vec_kernel, grid, dim3(threads), 0, stream, true, (__nv_bfloat16*)qkv, positions, seq_of_row,
+                tables, table_stride, cos_t, sin_t, table_rows, (__nv_bfloat16*)kpool, (__nv_bfloat16*)vpool, n_blocks,
+                bs, nh, nkv, d, err);
+  else if (dtype == CUCA_F32)
     cuca_launch(rope_store_kernel<float>, grid, dim3(threads), 0, stream, true, (float*)qkv, positions, seq_of_row,
                 tables, table_stride, cos_t, sin_t, table_rows, rot, (float*)kpool, (float*)vpool, n_blocks, bs, nh,
                 nkv, d, err);

@@ -232,11 +232,13 @@ def test_attention_generic_paged(dev, dtype, nh, nkv, d, bs, window):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_rope_store(dev, dtype):
-    """Rotation of q and k (half-split pairs, partial rotary size) and the write of k, v to their pages."""
+@pytest.mark.parametrize("nh,nkv,d,rot", [(6, 2, 48, 32), (6, 2, 48, 48), (5, 5, 128, 128), (4, 1, 80, 80)])
+def test_rope_store(dev, dtype, nh, nkv, d, rot):
+    """Rotation of q and k (half-split pairs, partial and whole rotary size; whole heads of 16-multiples take the
+    vector kernel in bf16) and the write of k, v to their pages."""
     from cuca_b200.kernels import ops
     from cuca_b200.parts.rope import rope_tables
-    nh, nkv, d, rot, bs = 6, 2, 48, 32, 8
+    bs = 8
     T, n_blocks = 11, 9
     cos, sin = rope_tables(64, rot, 10000.0)
     cos, sin = cos.to(dev), sin.to(dev)
