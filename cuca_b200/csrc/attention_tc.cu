@@ -44,7 +44,8 @@ constexpr int TILES_BYTES = NQ * (Q_BYTES + P_BYTES) + KV_STAGES * 2 * KV_TILE; 
 constexpr int BAR_BYTES = 256;                   // mbarriers, the TMEM address, the abort flag: behind the tiles
 constexpr int DYN_SMEM = TILES_BYTES + BAR_BYTES + 1024;  // + what aligning the tiles to 1024 bytes may cost
 constexpr int TMEM_COLS = 512;                   // two S buffers per query tile (4 x 64 columns), O of both (2 x 128)
-constexpr int NTHREADS = 64 + NQ * 128;          // warp 0 TMA, warp 1 MMA, four softmax warps per query tile
+constexpr int NTHREADS = 64 + NQ * 128 + 32;     // warp 0 TMA, warp 1 MMA of query tile 0, four softmax warps per query
+                                                 // tile, last warp MMA of query tile 1
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
 struct Params {
@@ -256,7 +257,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], nq); }  // one commit per query tile
     for (int x = 0; x < NQ; ++x) {
       mbar_init(&s_full[2 * x], 1);
       mbar_init(&s_full[2 * x + 1], 1);
@@ -323,61 +324,71 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tma_load_2d(dst, (which & 2) ? &tmV : &tmK, &kv_full[s], (which & 1) ? 64 : 0, grow);
       }
     }
-  } else if (warp == 1 && lane == 0) {
-    // ------------------------------------------------ MMA issuer
+  } else if ((warp == 1 || warp == 2 + 4 * NQ) && lane == 0) {
+    // ------------------------------------------------ MMA issuers: one thread per query tile
     // Scores run one key tile ahead of the softmax: each query tile has two S buffers, so when its softmax threads
     // hand over P of key tile j, the scores of j + 1 are already there and those of j + 2 are requested behind the
-    // P V of j. The two query tiles share the tensor pipe: whatever is ready is issued (keys landed and an S buffer
-    // free -> scores; P handed over -> P V), neither waits for the other. A key/value stage goes back to the
-    // producer after the last P V that reads it.
+    // P V of j. The two query tiles share the tensor pipe; each has a thread of its own that issues whatever of its
+    // tile is ready (keys landed and an S buffer free -> scores; P handed over -> P V). One thread for both spent
+    // 3,100 cycles per key tile issuing (24 MMAs, their descriptors, 6 commits, the polls) while the tensor pipe
+    // needed 1,400 and the softmax threads waited 1,600 of their 3,000 for scores. A key/value stage goes back to
+    // the producer after both tiles' P V of it (an arrival count of two).
+    const int x = warp == 1 ? 0 : 1;
     constexpr uint32_t idesc_qk = instr_desc(false, KEYS), idesc_pv = instr_desc(true, D);
-    bool ok = mbar_wait(q_full, 0, p.err, abort_flag);
-    auto scores = [&](int x, int t) {  // S_x[t % 2] = Q_x K_t^T: 8 steps of 16 head dimensions, 32 bytes inside a 64-wide half
-      tc_fence_after();
-      const uint32_t qa = smem_u32(q_s + x * Q_BYTES);
-      const uint32_t ka = smem_u32(kv_s + (t % KV_STAGES) * 2 * KV_TILE);
+    bool ok = x < nq && mbar_wait(q_full, 0, p.err, abort_flag);
+    // descriptors once: a tile's further K steps are constant offsets of its first (the address field counts 16 bytes)
+    const uint64_t q_desc = desc_kmajor(smem_u32(q_s + x * Q_BYTES));
+    const uint64_t p_desc = desc_kmajor(smem_u32(p_s + x * P_BYTES));
+    uint64_t k_desc[KV_STAGES], v_desc[KV_STAGES];
 #pragma unroll
-      for (int k = 0; k < D / 16; ++k) {
-        const uint32_t in_half = (k % 4) * 32;
-        umma_bf16(tmem_s(x, t), desc_kmajor(qa + (k / 4) * Q_HALF + in_half), desc_kmajor(ka + (k / 4) * KV_HALF + in_half),
-                  idesc_qk, k > 0);
-      }
-      umma_commit(&s_full[2 * x + (t & 1)]);
+    for (int st = 0; st < KV_STAGES; ++st) {
+      k_desc[st] = desc_kmajor(smem_u32(kv_s + st * 2 * KV_TILE));
+      v_desc[st] = desc_mnmajor(smem_u32(kv_s + st * 2 * KV_TILE + KV_TILE), KV_HALF, 1024);
+    }
+    auto stage_desc = [&](const uint64_t (&d)[KV_STAGES], int st) {  // registers, not local memory
+      uint64_t r = d[0];
+#pragma unroll
+      for (int i = 1; i < KV_STAGES; ++i) r = st == i ? d[i] : r;
+      return r;
     };
-    int next_sc[NQ] = {0, 0}, next_pv[NQ] = {0, 0};
-    if (nq < NQ) next_sc[1] = next_pv[1] = n_tiles;  // no second query tile
+    int next_sc = 0, next_pv = 0;
     unsigned long long idle_since = 0;
     unsigned spins = 0;
-    while (ok && (next_pv[0] < n_tiles || next_pv[1] < n_tiles)) {
+    while (ok && next_pv < n_tiles) {
       bool progressed = false;
+      // scores of key tile t need its keys and the S buffer that the softmax of t - 2 has let go
+      if (next_sc < n_tiles && next_sc <= next_pv + 1 &&
+          mbar_test_wait(&kv_full[next_sc % KV_STAGES], (next_sc / KV_STAGES) & 1)) {
+        const int t = next_sc;
+        tc_fence_after();
+        const uint64_t kd = stage_desc(k_desc, t % KV_STAGES);
+        const uint32_t acc = tmem_s(x, t);
+        // S_x[t % 2] = Q_x K_t^T: 8 steps of 16 head dimensions, 32 bytes inside a 64-wide half
 #pragma unroll
-      for (int x = 0; x < NQ; ++x) {
-        // scores of key tile t need its keys and the S buffer that the softmax of t - 2 has let go
-        const int t = next_sc[x];
-        if (t < n_tiles && t <= next_pv[x] + 1 && mbar_test_wait(&kv_full[t % KV_STAGES], (t / KV_STAGES) & 1)) {
-          scores(x, t);
-          ++next_sc[x];
-          progressed = true;
-        }
-        const int j = next_pv[x];
-        if (j < n_tiles && j < next_sc[x] && mbar_test_wait(&p_full[x], j & 1)) {
-          // O_x += P_x V_j: the softmax threads of tile x have written P and rescaled O
-          tc_fence_after();
-          const int s = j % KV_STAGES;
-          const uint32_t pa = smem_u32(p_s + x * P_BYTES), va = smem_u32(kv_s + s * 2 * KV_TILE) + KV_TILE;
+        for (int k = 0; k < D / 16; ++k)
+          umma_bf16(acc, q_desc + (uint64_t)(((k / 4) * Q_HALF + (k % 4) * 32) >> 4),
+                    kd + (uint64_t)(((k / 4) * KV_HALF + (k % 4) * 32) >> 4), idesc_qk, k > 0);
+        umma_commit(&s_full[2 * x + (t & 1)]);
+        ++next_sc;
+        progressed = true;
+      }
+      if (next_pv < next_sc && mbar_test_wait(&p_full[x], next_pv & 1)) {
+        // O_x += P_x V_j: the softmax threads of tile x have written P and rescaled O
+        const int j = next_pv, st = j % KV_STAGES;
+        tc_fence_after();
+        const uint64_t vd = stage_desc(v_desc, st);
+        const uint32_t acc = tmem_o(x);
 #pragma unroll
-          for (int k = 0; k < KEYS / 16; ++k) {
-            // A = P[rows][keys] K-major: 16 keys = 32 bytes inside a 64-key half.
-            // B = V[keys][dims] MN-major: 16 keys = two 8-key groups of 1024 bytes; dims 64..127 in the second half.
-            const uint32_t aoff = (k / 4) * P_HALF + (k % 4) * 32;
-            umma_bf16(tmem_o(x), desc_kmajor(pa + aoff), desc_mnmajor(va + k * 2048, KV_HALF, 1024), idesc_pv,
-                      (j > 0 || k > 0));
-          }
-          ++next_pv[x];
-          if (next_pv[x ^ 1] > j) umma_commit(&kv_empty[s]);  // the other query tile is past this key tile too
-          umma_commit(&pv_done[x]);
-          progressed = true;
+        for (int k = 0; k < KEYS / 16; ++k) {
+          // A = P[rows][keys] K-major: 16 keys = 32 bytes inside a 64-key half.
+          // B = V[keys][dims] MN-major: 16 keys = two 8-key groups of 1024 bytes; dims 64..127 in the second half.
+          umma_bf16(acc, p_desc + (uint64_t)(((k / 4) * P_HALF + (k % 4) * 32) >> 4), vd + (uint64_t)((k * 2048) >> 4),
+                    idesc_pv, (j > 0 || k > 0));
         }
+        umma_commit(&kv_empty[st]);
+        umma_commit(&pv_done[x]);
+        ++next_pv;
+        progressed = true;
       }
       if (progressed) {
         idle_since = 0;
@@ -392,7 +403,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
     }
-  } else if (warp >= 2) {
+  } else if (warp >= 2 && warp < 2 + 4 * NQ) {
     // ------------------------------------------------ softmax: one query row per thread, four warps per tile
     const int x = (warp - 2) >> 2;              // which query tile
     const int quarter = warp & 3;               // the TMEM lanes this warp may touch
