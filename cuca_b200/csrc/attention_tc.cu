@@ -5,10 +5,11 @@
 //
 //   S[128 rows, 64 keys]   = Q K^T        (Q and K tiles K-major in shared memory, loaded by TMA from the
 //                                          q buffer and straight from the pages through the block table)
-//   O[128 rows, head size] += P V         (P written to shared memory by the softmax threads as the K-major
-//                                          A operand; V tiles as loaded, i.e. the MN-major B operand)
+//   O[128 rows, head size] += P V         (P written by the softmax threads as bf16 into the tensor memory that
+//                                          held S: the A operand comes from there; V tiles as loaded, i.e.
+//                                          the MN-major B operand)
 //
-// Warp 0 issues TMA, one thread of warp 1 issues the MMAs, four warps per query tile own one query row per
+// Warp 0 issues TMA, one thread per query tile issues its MMAs, four warps per query tile own one query row per
 // thread (= one TMEM lane): they read S with tcgen05.ld, scale, mask (causal, window), keep the running maximum and sum in
 // 32-bit, rescale O in tensor memory, and hand P back.
 //
@@ -32,15 +33,13 @@ constexpr int D = 128;        // head size
 constexpr int ROWS = 128;     // query rows per tile = TMEM lanes
 constexpr int KEYS = 64;      // keys per tile
 constexpr int NQ = 2;         // query tiles per CTA (two query heads of one key/value group, same rows)
-constexpr int KV_STAGES = 4;
+constexpr int KV_STAGES = 5;
 // Tiles are stored as 64-element halves: [halves][rows][128 B], 128-byte swizzled.
 constexpr int Q_HALF = ROWS * 128;               // 16 KB; a Q tile has D / 64 = 2 of them
 constexpr int Q_BYTES = (D / 64) * Q_HALF;
-constexpr int P_HALF = ROWS * 128;               // a P tile [rows][keys] has KEYS / 64 of them
-constexpr int P_BYTES = (KEYS / 64) * P_HALF;
 constexpr int KV_HALF = KEYS * 128;              // a K or V tile [keys][D] has D / 64 = 2 of them
 constexpr int KV_TILE = (D / 64) * KV_HALF;
-constexpr int TILES_BYTES = NQ * (Q_BYTES + P_BYTES) + KV_STAGES * 2 * KV_TILE;   // 224 KB
+constexpr int TILES_BYTES = NQ * Q_BYTES + KV_STAGES * 2 * KV_TILE;   // 224 KB
 constexpr int BAR_BYTES = 256;                   // mbarriers, the TMEM address, the abort flag: behind the tiles
 constexpr int DYN_SMEM = TILES_BYTES + BAR_BYTES + 1024;  // + what aligning the tiles to 1024 bytes may cost
 constexpr int TMEM_COLS = 512;                   // two S buffers per query tile (4 x 64 columns), O of both (2 x 128)
@@ -130,12 +129,17 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
       "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// the same with the A operand in tensor memory: row i in lane i, two bf16 per 32-bit column (K = 16 is 8 columns)
+__device__ __forceinline__ void umma_bf16_tmem_a(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   uint32_t r[32];
@@ -166,6 +170,17 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
         "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
         "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
         "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32_raw(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+        "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+        "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
       : "memory");
 }
 __device__ __forceinline__ float fast_exp2(float x) {  // ex2.approx: exp2(-inf) = 0
@@ -221,14 +236,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* q_s = smem;                                  // NQ Q tiles
-  uint8_t* p_s = q_s + NQ * Q_BYTES;                    // NQ P tiles
-  uint8_t* kv_s = p_s + NQ * P_BYTES;                   // KV_STAGES x (K tile + V tile)
+  uint8_t* kv_s = q_s + NQ * Q_BYTES;                   // KV_STAGES x (K tile + V tile)
   uint64_t* bars = (uint64_t*)(kv_s + KV_STAGES * 2 * KV_TILE);
   uint64_t* q_full = bars;
   uint64_t* kv_full = bars + 1;              // [KV_STAGES]
   uint64_t* kv_empty = kv_full + KV_STAGES;  // [KV_STAGES]
   uint64_t* s_full = kv_empty + KV_STAGES;   // [NQ][2] the scores of an even / odd key tile are in tensor memory
-  uint64_t* p_full = s_full + 2 * NQ;        // [NQ] P is in shared memory and O is rescaled (128 arrivals)
+  uint64_t* p_full = s_full + 2 * NQ;        // [NQ] P is in tensor memory and O is rescaled (128 arrivals)
   uint64_t* pv_done = p_full + NQ;           // [NQ] the P V contraction of a tile has finished
   uint32_t* tmem_slot = (uint32_t*)(pv_done + NQ);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
@@ -338,7 +352,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     bool ok = x < nq && mbar_wait(q_full, 0, p.err, abort_flag);
     // descriptors once: a tile's further K steps are constant offsets of its first (the address field counts 16 bytes)
     const uint64_t q_desc = desc_kmajor(smem_u32(q_s + x * Q_BYTES));
-    const uint64_t p_desc = desc_kmajor(smem_u32(p_s + x * P_BYTES));
     uint64_t k_desc[KV_STAGES], v_desc[KV_STAGES];
 #pragma unroll
     for (int st = 0; st < KV_STAGES; ++st) {
@@ -380,10 +393,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const uint32_t acc = tmem_o(x);
 #pragma unroll
         for (int k = 0; k < KEYS / 16; ++k) {
-          // A = P[rows][keys] K-major: 16 keys = 32 bytes inside a 64-key half.
+          // A = P[rows][keys] in tensor memory, where the scores of this key tile were: 16 keys = 8 columns.
           // B = V[keys][dims] MN-major: 16 keys = two 8-key groups of 1024 bytes; dims 64..127 in the second half.
-          umma_bf16(acc, p_desc + (uint64_t)(((k / 4) * P_HALF + (k % 4) * 32) >> 4), vd + (uint64_t)((k * 2048) >> 4),
-                    idesc_pv, (j > 0 || k > 0));
+          umma_bf16_tmem_a(acc, tmem_s(x, j) + k * 8, vd + (uint64_t)((k * 2048) >> 4), idesc_pv, (j > 0 || k > 0));
         }
         umma_commit(&kv_empty[st]);
         umma_commit(&pv_done[x]);
@@ -412,7 +424,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const bool row_ok = r < n_rows;
     const int row_pos = pos0 + r;
     const int row_lo = (p.window > 0 && row_pos - (p.window - 1) > 0) ? row_pos - (p.window - 1) : 0;
-    uint8_t* p_x = p_s + x * P_BYTES;
     float m = -INFINITY, l = 0.f;
     bool ok = x < nq;
     for (int j = 0; ok && j < n_tiles; ++j) {
@@ -454,31 +465,30 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       if (mx > m + 8.f || m == -INFINITY) m_new = fmaxf(m, mx);
       const float corr = (m_new == -INFINITY || m == m_new) ? 1.f : fast_exp2(m - m_new);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      // the previous P V of this tile must have finished before O is rescaled and P is overwritten
-      if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(&pv_done[x], (j - 1) & 1, p.err, abort_flag))) { ok = false; break; }
-      tc_fence_after();
-      // pass 2: P = exp2(s - m) as bf16 into shared memory (K-major, 128-byte swizzle), row sum
+      // pass 2: P = exp2(s - m) as bf16, two keys per 32-bit column, into the first columns of the tensor memory
+      // that held this tile's scores (every thread has read its row of them), and the row sum. The tensor core
+      // takes P from there as the A operand of P V: no trip through shared memory.
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t pw[KEYS / 2];
 #pragma unroll
       for (int c = 0; c < NC; ++c) {
-        uint8_t* half = p_x + (c / 2) * P_HALF + r * 128;
 #pragma unroll
-        for (int q8 = 0; q8 < 4; ++q8) {   // 8 keys = 16 bytes = one swizzle chunk
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float pa_ = fast_exp2(fmaf(__uint_as_float(raw[c][q8 * 8 + 2 * e]), p.scale_log2e, -m_use));
-            float pb_ = fast_exp2(fmaf(__uint_as_float(raw[c][q8 * 8 + 2 * e + 1]), p.scale_log2e, -m_use));
-            sum4[e] += pa_ + pb_;
-            __nv_bfloat162 t2 = __floats2bfloat162_rn(pa_, pb_);
-            w[e] = *reinterpret_cast<uint32_t*>(&t2);
-          }
-          const int chunk = (c % 2) * 4 + q8;                 // 16-byte chunk inside the 128-byte row
-          *reinterpret_cast<uint4*>(half + ((chunk ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        for (int e = 0; e < 16; ++e) {
+          float pa_ = fast_exp2(fmaf(__uint_as_float(raw[c][2 * e]), p.scale_log2e, -m_use));
+          float pb_ = fast_exp2(fmaf(__uint_as_float(raw[c][2 * e + 1]), p.scale_log2e, -m_use));
+          sum4[e & 3] += pa_ + pb_;
+          __nv_bfloat162 t2 = __floats2bfloat162_rn(pa_, pb_);
+          pw[c * 16 + e] = *reinterpret_cast<uint32_t*>(&t2);
         }
       }
+      static_assert(KEYS == 64, "one 32-column store holds the P row of a 64-key tile");
+      tmem_st32_raw(tmem_s(x, j) + lane_bits, pw);
       l = l * corr + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       m = m_new;
+      // the previous P V of this tile must have finished before O is rescaled (its phase is awaited every time, so
+      // that the barrier never runs two phases ahead of its waiters)
+      if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(&pv_done[x], (j - 1) & 1, p.err, abort_flag))) { ok = false; break; }
+      tc_fence_after();
       // rescale O (not yet written on the first tile).
       // tcgen05.ld/st are warp-wide: the whole warp rescales if any of its rows moved its maximum
       if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
@@ -490,10 +500,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           for (int i = 0; i < 32; ++i) o[i] *= corr;
           tmem_st32(tmem_o(x) + lane_bits + c * 32, o);
         }
-        tmem_st_wait();
       }
+      tmem_st_wait();
       tc_fence_before();
-      fence_async_smem();   // P was written through the generic proxy; the tensor core reads it through the async one
       mbar_arrive(&p_full[x]);
     }
     if (ok && __all_sync(0xffffffffu, mbar_wait(&pv_done[x], (n_tiles - 1) & 1, p.err, abort_flag))) {
