@@ -1,4 +1,4 @@
-// Paged causal attention for prompt portions on the 5th-generation tensor cores (bfloat16, head size 128).
+// Paged causal attention for prompt portions on the 5th-generation tensor cores (bfloat16, head size 64 or 128).
 //
 // A CTA takes up to 128 consecutive rows of one request and one query head and walks the request's keys in
 // tiles of 64 positions. Both contractions run as tcgen05.mma with accumulators in tensor memory:
@@ -20,32 +20,31 @@
 //
 // Every mbarrier wait is bounded; on a timeout the kernel records CUCA_ERR_WAIT_TIMEOUT, all roles stop, TMEM
 // is freed and the kernel returns.
-#include "common.cuh"
-#include <cuda.h>
+#include "tcgen05.cuh"
 #include <math.h>
 #include <stdlib.h>
-#include <mutex>
-#include <unordered_map>
 
 namespace {
 
-constexpr int D = 128;        // head size
 constexpr int ROWS = 128;     // query rows per tile = TMEM lanes
 constexpr int KEYS = 64;      // keys per tile
 constexpr int NQ = 2;         // query tiles per CTA (two query heads of one key/value group, same rows)
-constexpr int KV_STAGES = 5;
 // Tiles are stored as 64-element halves: [halves][rows][128 B], 128-byte swizzled.
-constexpr int Q_HALF = ROWS * 128;               // 16 KB; a Q tile has D / 64 = 2 of them
-constexpr int Q_BYTES = (D / 64) * Q_HALF;
-constexpr int KV_HALF = KEYS * 128;              // a K or V tile [keys][D] has D / 64 = 2 of them
-constexpr int KV_TILE = (D / 64) * KV_HALF;
-constexpr int TILES_BYTES = NQ * Q_BYTES + KV_STAGES * 2 * KV_TILE;   // 224 KB
+constexpr int Q_HALF = ROWS * 128;               // 16 KB; a Q tile has D / 64 of them
+constexpr int KV_HALF = KEYS * 128;              // a K or V tile [keys][D] has D / 64 of them
 constexpr int BAR_BYTES = 256;                   // mbarriers, the TMEM address, the abort flag: behind the tiles
-constexpr int DYN_SMEM = TILES_BYTES + BAR_BYTES + 1024;  // + what aligning the tiles to 1024 bytes may cost
-constexpr int TMEM_COLS = 512;                   // two S buffers per query tile (4 x 64 columns), O of both (2 x 128)
+constexpr int TMEM_COLS = 512;                   // two S buffers per query tile (4 x 64 columns), O of both (2 x D)
 constexpr int NTHREADS = 64 + NQ * 128 + 32;     // warp 0 TMA, warp 1 MMA of query tile 0, four softmax warps per query
                                                  // tile, last warp MMA of query tile 1
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+// What depends on the head size D (64 or 128).
+template <int D>
+struct Shape {
+  static constexpr int Q_BYTES = (D / 64) * Q_HALF;
+  static constexpr int KV_TILE = (D / 64) * KV_HALF;
+  static constexpr int KV_STAGES = D == 128 ? 5 : 8;
+  static constexpr int TILES_BYTES = NQ * Q_BYTES + KV_STAGES * 2 * KV_TILE;   // 224 KB / 192 KB
+  static constexpr int DYN_SMEM = TILES_BYTES + BAR_BYTES + 1024;  // + what aligning the tiles to 1024 bytes may cost
+};
 
 struct Params {
   __nv_bfloat16* out;
@@ -63,23 +62,6 @@ struct Params {
   int* err;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
 // test_wait never suspends the thread (try_wait may, for a time the hardware chooses): for loops that watch
 // several barriers at once
 __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
@@ -89,58 +71,12 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, volatile int* abort) {
-  if (mbar_try_wait(bar, parity)) return true;
-  unsigned long long t0 = global_ns();
-  unsigned spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 63u) == 0) {
-      if (*abort) return false;
-      if (global_ns() - t0 > WAIT_LIMIT_NS) {
-        if (err) atomicExch(err, CUCA_ERR_WAIT_TIMEOUT);
-        *abort = 1;
-        return false;
-      }
-    }
-  }
-  return true;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t* dst, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst)), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
 // the same with the A operand in tensor memory: row i in lane i, two bf16 per 32-bit column (K = 16 is 8 columns)
 __device__ __forceinline__ void umma_bf16_tmem_a(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
       ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   uint32_t r[32];
   asm volatile(
@@ -203,16 +139,6 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[3
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// K-major operand tile: rows of 128 bytes (64 bf16), 128-byte swizzle, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)1 << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
 // MN-major operand tile (the V tile as loaded: one key per 128-byte row of 64 head dimensions): 64 elements
 // of N contiguous, the next 64 at `lbo` bytes, 8-key groups `sbo` bytes apart.
 __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t lbo, uint32_t sbo) {
@@ -225,14 +151,17 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t lbo, ui
   return d;
 }
 // bf16 x bf16 -> f32, M = 128, N = n; b_mn: the B operand is MN-major
-__host__ __device__ constexpr uint32_t instr_desc(bool b_mn, int n) {
+__host__ __device__ constexpr uint32_t instr_desc_b(bool b_mn, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
          ((uint32_t)(128 >> 4) << 24);
 }
 
+template <int D>
 __global__ void __launch_bounds__(NTHREADS, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, const Params p) {
+  using SH = Shape<D>;
+  constexpr int Q_BYTES = SH::Q_BYTES, KV_TILE = SH::KV_TILE, KV_STAGES = SH::KV_STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* q_s = smem;                                  // NQ Q tiles
@@ -250,7 +179,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   pdl_trigger();
   pdl_wait();
-  if (smem + TILES_BYTES + BAR_BYTES > smem_raw + DYN_SMEM) {
+  if (smem + SH::TILES_BYTES + BAR_BYTES > smem_raw + SH::DYN_SMEM) {
     if (threadIdx.x == 0 && p.err) atomicExch(p.err, CUCA_ERR_SMEM_LAYOUT);
     return;
   }
@@ -300,8 +229,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     if (lane == 0) {
       mbar_expect_tx(q_full, nq * Q_BYTES);
       for (int x = 0; x < nq; ++x) {
-        tma_load_2d(q_s + x * Q_BYTES, &tmQ, q_full, (head0 + x) * D, row0);
-        tma_load_2d(q_s + x * Q_BYTES + Q_HALF, &tmQ, q_full, (head0 + x) * D + 64, row0);
+#pragma unroll
+        for (int h = 0; h < D / 64; ++h)
+          tma_load_2d(q_s + x * Q_BYTES + h * Q_HALF, &tmQ, q_full, (head0 + x) * D + h * 64, row0);
       }
     }
     const int pages = KEYS / p.bs;          // pages per key tile: 1..8
@@ -326,7 +256,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       // a single thread would need about as long to issue them as the tensor pipe needs for the tile
       const int pg = lane >> 2, which = lane & 3;
       int blk = __shfl_sync(0xffffffffu, entry, in_batch * pages + (pg < pages ? pg : 0));
-      if (pg < pages) {
+      if (pg < pages && (which & 1) < D / 64) {
         const int kp = (first_tile + j) * KEYS + pg * p.bs;
         if (blk < 0 || blk >= p.n_blocks) {
           // keys before the window may have given their page back; they are masked. Anything else is an error.
@@ -348,14 +278,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // needed 1,400 and the softmax threads waited 1,600 of their 3,000 for scores. A key/value stage goes back to
     // the producer after both tiles' P V of it (an arrival count of two).
     const int x = warp == 1 ? 0 : 1;
-    constexpr uint32_t idesc_qk = instr_desc(false, KEYS), idesc_pv = instr_desc(true, D);
+    constexpr uint32_t idesc_qk = instr_desc_b(false, KEYS), idesc_pv = instr_desc_b(true, D);
     bool ok = x < nq && mbar_wait(q_full, 0, p.err, abort_flag);
     // descriptors once: a tile's further K steps are constant offsets of its first (the address field counts 16 bytes)
-    const uint64_t q_desc = desc_kmajor(smem_u32(q_s + x * Q_BYTES));
+    const uint64_t q_desc = smem_desc(smem_u32(q_s + x * Q_BYTES));
     uint64_t k_desc[KV_STAGES], v_desc[KV_STAGES];
 #pragma unroll
     for (int st = 0; st < KV_STAGES; ++st) {
-      k_desc[st] = desc_kmajor(smem_u32(kv_s + st * 2 * KV_TILE));
+      k_desc[st] = smem_desc(smem_u32(kv_s + st * 2 * KV_TILE));
       v_desc[st] = desc_mnmajor(smem_u32(kv_s + st * 2 * KV_TILE + KV_TILE), KV_HALF, 1024);
     }
     auto stage_desc = [&](const uint64_t (&d)[KV_STAGES], int st) {  // registers, not local memory
@@ -538,59 +468,29 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)ptr;
-  });
-  return fn;
-}
-struct Key {
-  const void* ptr; uint64_t rows, cols, stride; uint32_t box_rows;
-  bool operator==(const Key& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && stride == o.stride && box_rows == o.box_rows; }
-};
-struct KeyHash { size_t operator()(const Key& k) const { return ((size_t)k.ptr * 1000003u) ^ (k.rows * 31 + k.cols * 17 + k.stride * 7 + k.box_rows); } };
-
-// [rows][cols] bf16 with `stride` elements between rows; box = box_rows x 64 columns, 128-byte swizzle
-bool tensor_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_t stride, uint32_t box_rows, CUtensorMap* out) {
-  static std::unordered_map<Key, CUtensorMap, KeyHash> cache;
-  static std::mutex mu;
-  Key key{ptr, rows, cols, stride, box_rows};
-  std::lock_guard<std::mutex> lock(mu);
-  auto it = cache.find(key);
-  if (it != cache.end()) { *out = it->second; return true; }
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return false;
-  cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {stride * 2};
-  cuuint32_t box[2] = {64, box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUtensorMap m;
-  if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-    return false;
-  if (cache.size() > 1024) cache.clear();
-  cache.emplace(key, m);
-  *out = m;
-  return true;
+template <int D>
+int launch_attn_tc(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const Params& p, int n_tiles,
+                   cudaStream_t stream) {
+  const int smem = Shape<D>::DYN_SMEM;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    CUCA_REQUIRE(e == cudaSuccess, "attention_prefill_tc: cannot reserve %d bytes of shared memory: %s", smem,
+                 cudaGetErrorString(e));
+    configured = true;
+  }
+  cuca_launch(attn_tc_kernel<D>, dim3(n_tiles, p.nh / p.heads_per_cta), dim3(NTHREADS), smem, stream, true, tmQ, tmK, tmV, p);
+  CUCA_CHECK_LAUNCH("attention_prefill_tc");
+  return 0;
 }
 
 }  // namespace
 
-// 1 if the tcgen05 prefill attention takes this shape: head size 128, pages of 8..64 positions (a power of
+// 1 if the tcgen05 prefill attention takes this shape: head size 64 or 128, pages of 8..64 positions (a power of
 // two), rows of the q buffer and the pools 16-byte aligned.
 CUCA_API int cuca_attention_tc_supported(int nh, int nkv, int d, int bs, int q_stride, int out_stride, const void* q,
                                          const void* kpool, const void* vpool) {
-  if (d != D || nkv <= 0 || nh % nkv != 0) return 0;
+  if ((d != 64 && d != 128) || nkv <= 0 || nh % nkv != 0) return 0;
   if (bs < 8 || bs > KEYS || (bs & (bs - 1)) != 0) return 0;
   if (q_stride % 8 != 0 || out_stride % 8 != 0) return 0;
   if (((uintptr_t)q & 15) || ((uintptr_t)kpool & 15) || ((uintptr_t)vpool & 15)) return 0;
@@ -610,25 +510,15 @@ CUCA_API int cuca_attention_prefill_tc(const void* q, int q_stride, int n_rows_t
                "attention_prefill_tc: unsupported shape (heads %d/%d, head size %d, page %d)", nh, nkv, d, bs);
   CUCA_REQUIRE(nh <= 65535, "attention_prefill_tc: too many heads");
   CUtensorMap tmQ, tmK, tmV;
-  CUCA_REQUIRE(tensor_map(q, n_rows_total, (uint64_t)nh * d, q_stride, ROWS, &tmQ), "attention_prefill_tc: q tensor map failed");
+  CUCA_REQUIRE(cuca_tensor_map_bf16(q, n_rows_total, (uint64_t)nh * d, q_stride, ROWS, &tmQ), "attention_prefill_tc: q tensor map failed");
   const uint64_t pool_rows = (uint64_t)n_blocks * nkv * bs;
-  CUCA_REQUIRE(tensor_map(kpool, pool_rows, d, d, bs, &tmK), "attention_prefill_tc: key tensor map failed");
-  CUCA_REQUIRE(tensor_map(vpool, pool_rows, d, d, bs, &tmV), "attention_prefill_tc: value tensor map failed");
+  CUCA_REQUIRE(cuca_tensor_map_bf16(kpool, pool_rows, d, d, bs, &tmK), "attention_prefill_tc: key tensor map failed");
+  CUCA_REQUIRE(cuca_tensor_map_bf16(vpool, pool_rows, d, d, bs, &tmV), "attention_prefill_tc: value tensor map failed");
   Params p;
   p.out = (__nv_bfloat16*)out; p.out_stride = out_stride; p.tables = tables; p.table_stride = table_stride;
   p.positions = positions; p.seq_of_row = seq_of_row; p.tile_row0 = tile_row0; p.tile_nrows = tile_nrows;
   p.n_blocks = n_blocks; p.bs = bs; p.nh = nh; p.nkv = nkv; p.scale_log2e = scale * 1.4426950408889634f;
   p.window = window; p.err = err;
   p.heads_per_cta = ((nh / nkv) % NQ == 0) ? NQ : 1;
-  const int smem = DYN_SMEM;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    CUCA_REQUIRE(e == cudaSuccess, "attention_prefill_tc: cannot reserve %d bytes of shared memory: %s", smem,
-                 cudaGetErrorString(e));
-    configured = true;
-  }
-  cuca_launch(attn_tc_kernel, dim3(n_tiles, nh / p.heads_per_cta), dim3(NTHREADS), smem, stream, true, tmQ, tmK, tmV, p);
-  CUCA_CHECK_LAUNCH("attention_prefill_tc");
-  return 0;
+  return d == 128 ? launch_attn_tc<128>(tmQ, tmK, tmV, p, n_tiles, stream) : launch_attn_tc<64>(tmQ, tmK, tmV, p, n_tiles, stream);
 }

@@ -485,11 +485,12 @@ def test_rope_store_from_partial_sums(dev):
 
 @pytest.mark.parametrize("nh,nkv,bs,window", [(4, 2, 16, None), (8, 8, 32, None), (8, 2, 16, 150), (2, 1, 8, None),
                                               (3, 1, 64, 40)])
-def test_attention_prefill_tcgen05(dev, nh, nkv, bs, window):
-    """Prefill attention on tcgen05 (head size 128): portions that start at position 0 and in the middle of a
+@pytest.mark.parametrize("d", [128, 64])
+def test_attention_prefill_tcgen05(dev, nh, nkv, bs, window, d):
+    """Prefill attention on tcgen05 (head size 128 or 64): portions that start at position 0 and in the middle of a
     request, tiles of 128 rows and ragged tails, several key tiles, against 32-bit attention."""
     from cuca_b200.kernels import ops
-    d, dtype = 128, torch.bfloat16
+    dtype = torch.bfloat16
     lens = [5, 128, 200, 390, 131]
     starts = [0, 0, 33, 129, 129]
     k, v, kpool, vpool, tables = _paged_setup(dev, dtype, lens, nh, nkv, d, bs,
