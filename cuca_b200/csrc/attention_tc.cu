@@ -398,22 +398,24 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       // pass 2: P = exp2(s - m) as bf16, two keys per 32-bit column, into the first columns of the tensor memory
       // that held this tile's scores (every thread has read its row of them), and the row sum. The tensor core
       // takes P from there as the A operand of P V: no trip through shared memory.
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      // (multiply-add and sum on pairs, in packed 32-bit arithmetic: the loop is bound by instruction issue)
+      float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
       uint32_t pw[KEYS / 2];
+      const float2 scale2 = make_float2(p.scale_log2e, p.scale_log2e), neg_m2 = make_float2(-m_use, -m_use);
 #pragma unroll
       for (int c = 0; c < NC; ++c) {
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-          float pa_ = fast_exp2(fmaf(__uint_as_float(raw[c][2 * e]), p.scale_log2e, -m_use));
-          float pb_ = fast_exp2(fmaf(__uint_as_float(raw[c][2 * e + 1]), p.scale_log2e, -m_use));
-          sum4[e & 3] += pa_ + pb_;
-          __nv_bfloat162 t2 = __floats2bfloat162_rn(pa_, pb_);
+          const float2 x2 = __ffma2_rn(make_float2(__uint_as_float(raw[c][2 * e]), __uint_as_float(raw[c][2 * e + 1])), scale2, neg_m2);
+          const float2 p2 = make_float2(fast_exp2(x2.x), fast_exp2(x2.y));
+          sum2[e & 1] = __fadd2_rn(sum2[e & 1], p2);
+          __nv_bfloat162 t2 = __floats2bfloat162_rn(p2.x, p2.y);
           pw[c * 16 + e] = *reinterpret_cast<uint32_t*>(&t2);
         }
       }
       static_assert(KEYS == 64, "one 32-column store holds the P row of a 64-key tile");
       tmem_st32_raw(tmem_s(x, j) + lane_bits, pw);
-      l = l * corr + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      l = l * corr + (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
       m = m_new;
       // the previous P V of this tile must have finished before O is rescaled (its phase is awaited every time, so
       // that the barrier never runs two phases ahead of its waiters)
