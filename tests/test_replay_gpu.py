@@ -1,5 +1,5 @@
-"""Trace replay on the GPU against the plain implementation: the four work splits, both tiny configurations,
-32-bit and bfloat16."""
+"""Trace replay on the GPU against the plain implementation: the four work splits, three tiny configurations and two
+small ones at the head sizes of real models, 32-bit and bfloat16."""
 import pytest
 import torch
 
@@ -10,13 +10,14 @@ pytestmark = pytest.mark.gpu
 
 # relative to the largest logit of a row; set from the measured error of a correct engine, with headroom
 TOL = {"float32": 2e-5, "bfloat16": 3e-2}
-LENGTHS = {"A": [1, 7, 16, 33, 65, 100, 128], "B": [3, 12, 40, 64, 90, 130, 255], "C": [2, 31, 77, 129, 300]}
+LENGTHS = {"A": [1, 7, 16, 33, 65, 100, 128], "B": [3, 12, 40, 64, 90, 130, 255], "C": [2, 31, 77, 129, 300],
+           "D": [5, 70, 130, 300, 700], "E": [33, 64, 200, 513, 640]}
 
 
 @pytest.fixture(scope="module")
 def models(tmp_path_factory):
     out = {}
-    for which in "ABC":
+    for which in "ABCDE":
         d = tmp_path_factory.mktemp(f"tiny_{which}")
         tiny.write_tiny(d, which)
         out[which] = d
@@ -29,7 +30,7 @@ def _requests(which):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["A", "B", "C"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D", "E"])
 def test_whole(models, which, dtype):
     reqs = _requests(which)
     steps = ru.trace_whole(reqs)
@@ -38,7 +39,7 @@ def test_whole(models, which, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["A", "B", "C"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D", "E"])
 def test_tail_one_by_one(models, which, dtype):
     reqs = _requests(which)
     steps = ru.trace_tail_one_by_one(reqs)
@@ -47,7 +48,7 @@ def test_tail_one_by_one(models, which, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["A", "B", "C"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D", "E"])
 def test_portions(models, which, dtype):
     reqs = _requests(which)
     steps = ru.trace_portions(reqs)
@@ -56,7 +57,7 @@ def test_portions(models, which, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["A", "B", "C"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D", "E"])
 def test_mixed_pages_reused(models, which, dtype):
     reqs = _requests(which)
     reqs.update({f"s{n}": tiny.random_tokens(n, tiny.CONFIGS[which]["vocab_size"], seed=200 + n)

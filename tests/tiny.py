@@ -27,8 +27,26 @@ TINY_C = {
     "rms_norm_eps": 3e-5, "rope_theta": 25000.0, "rope_scaling": {"rope_type": "linear", "factor": 2.0},
     "tie_word_embeddings": False, "attention_bias": True,
 }
-SEEDS = {"A": 0, "B": 2, "C": 9}
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# two small shapes at the head sizes of real models, so that in bfloat16 the replays run the serving kernels
+# (tensor-core attention over prompt portions, TMA-fed decode attention, contractions over more than 64 tokens):
+# head size 128 with two query heads per key/value head, head size 64 with three
+SMALL_D = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 256, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "head_dim": 128, "intermediate_size": 384, "vocab_size": 1000, "max_position_embeddings": 1024,
+    "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 256},
+    "tie_word_embeddings": False,
+}
+SMALL_E = {
+    "architectures": ["MistralForCausalLM"], "model_type": "mistral",
+    "num_hidden_layers": 2, "hidden_size": 192, "num_attention_heads": 6, "num_key_value_heads": 2,
+    "head_dim": 64, "intermediate_size": 456, "vocab_size": 777, "max_position_embeddings": 1024,
+    "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "rope_scaling": None, "tie_word_embeddings": True,
+}
+SEEDS = {"A": 0, "B": 2, "C": 9, "D": 4, "E": 11}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": SMALL_D, "E": SMALL_E}
 
 
 def write_tiny(folder, which: str, dtype=torch.bfloat16, std: float = 0.02):
