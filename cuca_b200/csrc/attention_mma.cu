@@ -278,6 +278,50 @@ attn_mma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tmK, con
       tma_load_2d(dst + lane * S::SUB_BYTES, values ? &tmV : &tmK, &w_full[warp][st], 64 * h, row);
     }
   };
+  // ---- fused form, whole heads rotated, 16-byte rows: a thread's work is four consecutive columns of each half of
+  // a head (or of v) over all slices. The loads of its first item (up to four slices, cosines and sines) are asked
+  // for here, before the ring is set up, so that the page-table lookups below and these round trips overlap; they
+  // are used further down. (One value at a time, as the general form below does it, the prologue took 6 us of the
+  // kernel's 20 at batch 8.)
+  const int f_half = FUSED ? p.rot / 2 : 0;
+  const size_t f_width = FUSED ? (size_t)(p.nh + (p.has_kv ? 2 * p.nkv : 0)) * D : 0;
+  const float* f_row = FUSED ? p.partial + (size_t)dec_row * f_width : nullptr;
+  const bool f_in_table = FUSED && P >= 0 && P < p.table_rows;
+  const bool f_vec = FUSED && p.rot == D && D % 8 == 0 && ((p.slice_stride | f_width) & 3) == 0 &&
+                     (((uintptr_t)p.partial | (uintptr_t)p.cos_t | (uintptr_t)p.sin_t) & 15) == 0;
+  const int f_hq = f_half / 4;                                   // items per rotated head
+  const int f_rope_items = (G + (owner ? 1 : 0)) * f_hq;
+  const int f_items = f_rope_items + (owner ? D / 4 : 0);       // then the row's own value
+  // columns of item `it`: ca (and ca + half for a rotated head); head index hh (G: the key), offset inside the head
+  auto f_item = [&](int it, int& ca, int& hh, int& off) {
+    if (it < f_rope_items) {
+      hh = it / f_hq;
+      off = (it - hh * f_hq) * 4;
+      ca = (hh < G ? (kvh * G + hh) * D : (p.nh + kvh) * D) + off;
+    } else {
+      hh = -1;
+      off = (it - f_rope_items) * 4;
+      ca = (p.nh + p.nkv + kvh) * D + off;
+    }
+  };
+  float4 pre_a[4], pre_b[4], pre_c = make_float4(1.f, 1.f, 1.f, 1.f), pre_s = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (FUSED && f_vec && (int)threadIdx.x < f_items) {
+    int ca, hh, off;
+    f_item(threadIdx.x, ca, hh, off);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      pre_a[u] = pre_b[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (u < p.n_slices) {
+        pre_a[u] = __ldcg(reinterpret_cast<const float4*>(f_row + (size_t)u * p.slice_stride + ca));
+        if (hh >= 0) pre_b[u] = __ldcg(reinterpret_cast<const float4*>(f_row + (size_t)u * p.slice_stride + ca + f_half));
+      }
+    }
+    if (hh >= 0 && f_in_table) {
+      pre_c = *reinterpret_cast<const float4*>(p.cos_t + (size_t)P * f_half + off);
+      pre_s = *reinterpret_cast<const float4*>(p.sin_t + (size_t)P * f_half + off);
+    }
+  }
+
   if (TMA) {
     if (threadIdx.x == 0) w_abort = 0;
     if (lane == 0) {
@@ -342,9 +386,54 @@ attn_mma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tmK, con
     const int half = p.rot / 2;
     const bool in_table = P >= 0 && P < p.table_rows;
     if (!in_table && half > 0 && threadIdx.x == 0 && p.err) atomicExch(p.err, CUCA_ERR_TOKEN_RANGE);
+    if (f_vec) {
+      auto add4 = [](float4& x, const float4 y) { x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w; };
+      auto put4 = [](__nv_bfloat16* dst, float a, float b, float c, float d) {
+        *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(a, b), pack_bf16(c, d));
+      };
+      for (int it = threadIdx.x; it < f_items; it += NTHREADS) {
+        int ca, hh, off;
+        f_item(it, ca, hh, off);
+        const bool first = it == (int)threadIdx.x;
+        auto bias4 = [&](int col) {
+          return p.bias ? make_float4(__bfloat162float(p.bias[col]), __bfloat162float(p.bias[col + 1]),
+                                      __bfloat162float(p.bias[col + 2]), __bfloat162float(p.bias[col + 3]))
+                        : make_float4(0.f, 0.f, 0.f, 0.f);
+        };
+        float4 a = bias4(ca), b = hh >= 0 ? bias4(ca + f_half) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k0 = 0; k0 < p.n_slices; k0 += 4) {  // four slices' loads in flight at once, added in slice order
+          float4 xa[4], xb[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            xa[u] = xb[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (first && k0 == 0) {
+              xa[u] = pre_a[u];
+              xb[u] = pre_b[u];
+            } else if (k0 + u < p.n_slices) {
+              xa[u] = __ldcg(reinterpret_cast<const float4*>(f_row + (size_t)(k0 + u) * p.slice_stride + ca));
+              if (hh >= 0) xb[u] = __ldcg(reinterpret_cast<const float4*>(f_row + (size_t)(k0 + u) * p.slice_stride + ca + f_half));
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) { add4(a, xa[u]); add4(b, xb[u]); }
+        }
+        if (hh < 0) {
+          put4(v_new + off, a.x, a.y, a.z, a.w);
+          continue;
+        }
+        float4 c = pre_c, sn = pre_s;
+        if (!first) {
+          c = in_table ? *reinterpret_cast<const float4*>(p.cos_t + (size_t)P * half + off) : make_float4(1.f, 1.f, 1.f, 1.f);
+          sn = in_table ? *reinterpret_cast<const float4*>(p.sin_t + (size_t)P * half + off) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        __nv_bfloat16* dst = (hh < G ? q_s + hh * S::RS : k_new) + off;
+        put4(dst, a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y, a.z * c.z - b.z * sn.z, a.w * c.w - b.w * sn.w);
+        put4(dst + half, a.x * sn.x + b.x * c.x, a.y * sn.y + b.y * c.y, a.z * sn.z + b.z * c.z, a.w * sn.w + b.w * c.w);
+      }
+    }
     // per head: `half` rotated pairs (i, i + half), then the values beyond the rotary part as they are
     const int units = D - half;
-    const int heads_here = G + (owner ? 1 : 0);
+    const int heads_here = f_vec ? 0 : G + (owner ? 1 : 0);
     for (int idx = threadIdx.x; idx < heads_here * units; idx += NTHREADS) {
       const int hh = idx / units, u = idx % units;
       const int col0 = hh < G ? (kvh * G + hh) * D : (p.nh + kvh) * D;
@@ -359,7 +448,7 @@ attn_mma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tmK, con
         dst[u + half] = __float2bfloat16_rn(value(col0 + u + half));
       }
     }
-    if (owner)
+    if (owner && !f_vec)
       for (int i = threadIdx.x; i < D; i += NTHREADS)
         v_new[i] = __float2bfloat16_rn(value((p.nh + p.nkv + kvh) * D + i));
     for (int idx = threadIdx.x; idx < (16 - G) * D; idx += NTHREADS)
