@@ -59,6 +59,8 @@ struct Params {
   int per_tile;  // mode 2: CTAs per tile
   int max_parts; // workspace slots per tile
   int tma_out;   // many tokens: whole tiles leave through shared memory and the copy engine (tensor map of `out`)
+  int ordered_add;  // mode 2 into the 32-bit stream over many tokens: the K slices of a tile add themselves in turn
+  int skew;         // ... and slice k + 1 has `skew` K steps more than slice k, so that it finishes when slice k has added
 };
 
 constexpr int STAGING_BUF = 32 * 128;  // 32 rows of 128 bytes
@@ -68,7 +70,7 @@ constexpr int STAGING_BUF = 32 * 128;  // 32 rows of 128 bytes
 template <int BN, bool DUAL, bool SWAP>
 struct Cfg {
   static constexpr int A_BYTES = TILE_A * TILE_K * 2 * ((SWAP && DUAL) ? 2 : 1);
-  static constexpr int B_ROWS = SWAP ? BN : 256;
+  static constexpr int B_ROWS = BN;  // many tokens: 256 weight rows a stage, or 128 for launches of column pieces up to 128 wide
   static constexpr int B_BYTES = B_ROWS * TILE_K * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   // deep rings in both orientations: the more weight bytes in flight, the closer the stream runs to the memory's
@@ -78,10 +80,10 @@ struct Cfg {
 #endif
   static constexpr int SMEM_BUDGET = (SWAP ? ((BN == 64 && DUAL && CUCA_SWAP_SMEM_KB < 124) ? 124 : CUCA_SWAP_SMEM_KB) : 192) * 1024;
   static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) > 12 ? 12 : (SMEM_BUDGET / STAGE_BYTES);
-  static constexpr int MMA_N = SWAP ? BN : 256;                    // N of one tcgen05.mma
-  static constexpr int NCOLS = SWAP ? BN * (DUAL ? 2 : 1) : 256;   // accumulator columns of one tile
+  static constexpr int MMA_N = BN;                                 // N of one tcgen05.mma
+  static constexpr int NCOLS = SWAP ? BN * (DUAL ? 2 : 1) : BN;    // accumulator columns of one tile
   static constexpr int TMEM_COLS = 2 * NCOLS < 32 ? 32 : 2 * NCOLS;  // two accumulators
-  static constexpr int OUT_COLS = SWAP ? BN : (DUAL ? 128 : 256);  // output columns of one tile
+  static constexpr int OUT_COLS = SWAP ? BN : (DUAL ? BN / 2 : BN);  // output columns of one tile
   // many tokens: each epilogue warp stages its 32 rows x 128 bytes of output twice over for the copy engine
   static constexpr int STAGING = SWAP ? 0 : 4 * 2 * STAGING_BUF;
   static constexpr int SMEM = STAGES * STAGE_BYTES + STAGING + 1024 /*alignment*/ + 512 /*barriers*/;
@@ -136,8 +138,15 @@ struct SegmentWalk {
       origin(s);
       s.part = (int)blockIdx.x % p.per_tile;
       s.nparts = p.per_tile;
-      s.ks0 = (int)((long long)s.part * p.ksteps / p.per_tile);
-      s.ks1 = (int)((long long)(s.part + 1) * p.ksteps / p.per_tile);
+      if (p.skew > 0) {
+        const int n = p.per_tile, tri = p.skew * n * (n - 1) / 2;
+        const int base = (p.ksteps - tri) / n;
+        s.ks0 = s.part * base + p.skew * s.part * (s.part - 1) / 2;
+        s.ks1 = s.part == n - 1 ? p.ksteps : s.ks0 + base + p.skew * s.part;
+      } else {
+        s.ks0 = (int)((long long)s.part * p.ksteps / p.per_tile);
+        s.ks1 = (int)((long long)(s.part + 1) * p.ksteps / p.per_tile);
+      }
       tile_cursor = -1;
       return true;
     }
@@ -245,7 +254,8 @@ __device__ __forceinline__ void store16(const Params& p, int a0, int b0, int lan
 // per lane and instruction: measured, 13 us per tile of the output projection against 26 us of main loop.
 template <bool DUAL>
 __device__ __forceinline__ void tma_epilogue(const Params& p, const CUtensorMap* tmO, uint32_t acc, int a0, int b0,
-                                             int width, int quarter, int lane, uint8_t* staging, int& chunk_no) {
+                                             int width, bool with_bias, int quarter, int lane, uint8_t* staging,
+                                             int& chunk_no) {
   const int y0 = a0 + quarter * 32;
   const int ch = p.out_f32 ? 32 : 64;  // the host cuts column pieces in whole runs
   uint8_t* const my_row = staging + lane * 128;
@@ -264,7 +274,7 @@ __device__ __forceinline__ void tma_epilogue(const Params& p, const CUtensorMap*
         tmem_ld16(acc + 128 + c + h, u);
 #pragma unroll
         for (int j = 0; j < 16; ++j) v[j] = silu_mul(v[j], u[j]);
-      } else if (p.bias) {
+      } else if (p.bias && with_bias) {
 #pragma unroll
         for (int j = 0; j < 16; ++j)
           if (b0 + c + h + j < p.N) v[j] += __bfloat162float(p.bias[b0 + c + h + j]);
@@ -348,7 +358,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint64_t once = SWAP ? l2_evict_first() : 0;
   // bytes a stage of this segment receives: a column piece of up to 128 weight rows needs one box of them only
   auto stage_tx = [&](const Segment& s) -> uint32_t {
-    return C::STAGE_BYTES - ((!SWAP && !DUAL && s.w <= 128) ? 128 * TILE_K * 2 : 0);
+    return C::STAGE_BYTES - ((!SWAP && !DUAL && BN == 256 && s.w <= 128) ? 128 * TILE_K * 2 : 0);
   };
   auto load_weights = [&](uint8_t* st, uint64_t* bar, const Segment& s, int kc) {
     if (SWAP) {
@@ -356,7 +366,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (DUAL) tma_load_2d_hint(st + TILE_A * TILE_K * 2, &tmA, bar, kc, p.N + s.a0, once);
     } else {
       tma_load_2d(st + C::A_BYTES, &tmB, bar, kc, s.b0);
-      if (DUAL || s.w > 128) tma_load_2d(st + C::A_BYTES + 128 * TILE_K * 2, &tmB, bar, kc, DUAL ? p.N + s.b0 : s.b0 + 128);
+      if (BN == 256 && (DUAL || s.w > 128)) tma_load_2d(st + C::A_BYTES + 128 * TILE_K * 2, &tmB, bar, kc, DUAL ? p.N + s.b0 : s.b0 + 128);
     }
   };
   auto load_activations = [&](uint8_t* st, uint64_t* bar, const Segment& s, int kc) {
@@ -469,10 +479,50 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         __syncwarp();
         if (lane == 0) mbar_arrive(&tmem_empty[buf]);
       } else if (!SWAP && s.nparts == 1 && p.tma_out) {
-        tma_epilogue<DUAL>(p, &tmO, acc, a0, b0, s.w, quarter, lane, staging + (warp - 2) * (2 * STAGING_BUF), chunk_no);
+        tma_epilogue<DUAL>(p, &tmO, acc, a0, b0, s.w, true, quarter, lane, staging + (warp - 2) * (2 * STAGING_BUF), chunk_no);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+      } else if (!SWAP && !DUAL && p.ordered_add) {
+        // One even K slice of a tile (every CTA has one, all CTAs are resident), added into the 32-bit stream by
+        // the copy engine: the slices of a tile take turns in K order, so the sum does not depend on who finished
+        // first, and nothing is parked in a workspace or read back. The turn is the tile's counter.
+        if (eidx == 0) {
+          int mine = 0;
+          const unsigned long long t0 = global_ns();
+          unsigned spins = 0;
+          while (true) {
+            if (*reinterpret_cast<volatile int*>(&p.counters[s.tile]) == s.part) { mine = 1; break; }
+            if ((++spins & 63u) == 0) {
+              if (*abort_flag) break;
+              if (global_ns() - t0 > WAIT_LIMIT_NS) {
+                if (p.err) atomicExch(p.err, CUCA_ERR_WAIT_TIMEOUT);
+                *abort_flag = 1;
+                break;
+              }
+            }
+          }
+          *last_flag = mine;
+        }
+        epilogue_sync();
+        const bool mine = *last_flag != 0;
+        epilogue_sync();  // everyone has read the flag before it is written again
+        if (!mine) break;
+        __threadfence();  // the slices before this one have added their sums
+        tma_epilogue<false>(p, &tmO, acc, a0, b0, s.w, s.part == 0, quarter, lane, staging + (warp - 2) * (2 * STAGING_BUF),
+                            chunk_no);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&tmem_empty[buf]);
+          bulk_wait_all();  // this warp's adds have been performed
+        }
+        __threadfence();
+        epilogue_sync();
+        if (eidx == 0) {
+          if (s.part == s.nparts - 1) atomicExch(&p.counters[s.tile], 0);  // ready for the next launch
+          else atomicAdd(&p.counters[s.tile], 1);
+        }
       } else if (s.nparts == 1) {
 #pragma unroll 1
         for (int c = 0; c < (SWAP ? C::OUT_COLS : s.w); c += 16) {
@@ -709,6 +759,8 @@ static int gemm_tc_impl(const void* A, const void* W, const void* bias, void* ou
   const long long units = (long long)p.tiles * p.ksteps;
   int grid = p.tiles < sms ? p.tiles : sms;
   p.tma_out = tma_out;
+  p.ordered_add = 0;
+  p.skew = 0;
   p.stream_k = 0;
   p.pieces = p.piece_w = 0;
   p.per_tile = 1;
@@ -755,6 +807,15 @@ static int gemm_tc_impl(const void* A, const void* W, const void* bias, void* ou
       size_t need = (size_t)p.tiles * per_tile * ncols * TILE_A * sizeof(float);
       if (per_tile == 1) {
         grid = p.tiles;  // one CTA per tile, nothing to add up
+      } else if (!swap && tma_out && epilogue == EPI_RESIDUAL) {
+        p.stream_k = 2;
+        p.per_tile = per_tile;
+        p.ordered_add = 1;
+        // a turn (adds performed, fence, counter, the next slice's poll) takes about as long as 14 K steps (measured
+        // at 256 tokens, K = 14336, four slices: 63.5 us with even slices, 55.3 with 14, 57.3 with 8 or 20)
+        const int most = p.ksteps / (per_tile * (per_tile + 1) / 2);  // the first slice keeps at least `skew` steps
+        p.skew = 14 < most ? 14 : most;
+        grid = per_tile * p.tiles;
       } else if (need <= ws_bytes) {
         p.stream_k = 2;
         p.per_tile = per_tile;
@@ -781,6 +842,9 @@ static int gemm_tc_impl(const void* A, const void* W, const void* bias, void* ou
     switch (bn) { GO(16) GO(32) GO(64) }
   }
 #undef GO
+  // column pieces up to 128 wide: stages of 128 weight rows, so that six instead of four fit (a piece's main loop
+  // runs at the pace of its loads)
+  if (pieced && p.piece_w <= 128) return launch_tc<128, false, false>(tmA, tmB, tmO, p, grid, stream);
   return dual ? launch_tc<256, true, false>(tmA, tmB, tmO, p, grid, stream)
               : launch_tc<256, false, false>(tmA, tmB, tmO, p, grid, stream);
 }

@@ -98,6 +98,30 @@ def test_gemm_tcgen05_column_pieces(dev, M, N, K, out_dtype, epilogue):
     assert torch.allclose(out.float(), ref, atol=tol, rtol=tol), float((out.float() - ref).abs().max())
 
 
+@pytest.mark.parametrize("M,N,K", [(130, 2048, 8256), (256, 4096, 8320), (65, 1024, 9000 // 8 * 8)])
+def test_gemm_tcgen05_k_slices_added_in_turn(dev, M, N, K):
+    """More than 64 tokens, few tiles, long K, into the 32-bit stream: every CTA takes one K slice of a tile and the
+    slices add themselves in K order. Same bits on every run; ragged M, a K tail, a bias that is added once."""
+    from cuca_b200.kernels import ops
+    g = torch.Generator(device=dev).manual_seed(M + N + K)
+    a = torch.randn(M, K, device=dev, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=dev, generator=g) / math.sqrt(K)).bfloat16()
+    bias = torch.randn(N, device=dev, generator=g).bfloat16() if M % 2 else None
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    prior = torch.randn(M, N, device=dev, generator=g)
+    outs = []
+    for _ in range(3):
+        out = prior.clone()
+        ops.gemm_tc(a, w, out, ops.EPI_RESIDUAL, bias, err)
+        torch.cuda.synchronize()
+        assert int(err.item()) == 0
+        outs.append(out)
+    ref = _ref_gemm(a, w, ops.EPI_RESIDUAL, bias, prior)
+    assert torch.allclose(outs[0], ref, atol=2e-3, rtol=2e-3), float((outs[0] - ref).abs().max())
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    assert int(ops.gemm_scratch(dev)[1].abs().sum().item()) == 0
+
+
 def test_gemm_tcgen05_refuses_unaligned(dev):
     from cuca_b200.kernels import ops
     a = torch.zeros(4, 100, device=dev, dtype=torch.bfloat16)  # K = 100 is no multiple of 8
