@@ -1,0 +1,62 @@
+"""Shapes off the beaten track through mixed replay against the plain implementation: head sizes 80, 96 and 112
+(no tensor-core attention over prompt portions, no TMA-fed decode), one key/value head for 8 and for 16 query heads,
+as many key/value heads as query heads, a width and vocabularies that are no powers of two, a bias, tied
+embeddings; pages of 8 and of 64 positions."""
+import pytest
+import torch
+
+import replay_util as ru
+import tiny
+
+pytestmark = pytest.mark.gpu
+
+
+def _cfg(layers, hidden, nh, nkv, d, ff, vocab, tie=False, bias=False):
+    return {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": layers,
+            "hidden_size": hidden, "num_attention_heads": nh, "num_key_value_heads": nkv, "head_dim": d,
+            "intermediate_size": ff, "vocab_size": vocab, "max_position_embeddings": 1024, "rms_norm_eps": 1e-5,
+            "rope_theta": 10000.0, "rope_scaling": None, "tie_word_embeddings": tie, "attention_bias": bias}
+
+
+SHAPES = {
+    "d80_mha": _cfg(2, 160, 2, 2, 80, 328, 515),
+    "d96_g2": _cfg(1, 200, 2, 1, 96, 264, 300, tie=True),
+    "d112_bias": _cfg(1, 224, 2, 2, 112, 136, 999, bias=True),
+    "d64_g8": _cfg(2, 512, 8, 1, 64, 520, 1001),
+    "d128_g16": _cfg(1, 2048, 16, 1, 128, 1032, 640),
+    "d128_g3": _cfg(2, 384, 3, 1, 128, 392, 2000, tie=True),
+}
+# relative to the largest logit of a row, from the measured error of a correct engine with headroom
+TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    from cuca_b200.weights.random_init import write_random_model
+    out = {}
+    for name, cfg in SHAPES.items():
+        d = tmp_path_factory.mktemp(name)
+        write_random_model(d, cfg, 3, std=0.02, dtype=torch.bfloat16)
+        out[name] = d
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("block_size", [8, 64])
+@pytest.mark.parametrize("name", list(SHAPES))
+def test_odd_shapes_mixed(folders, name, block_size, dtype):
+    vocab = SHAPES[name]["vocab_size"]
+    reqs = {f"r{n}": tiny.random_tokens(n, vocab, seed=n) for n in (3, 66, 150, 333, 520)}
+    steps = ru.trace_mixed(reqs, max_live=4, seed=5)
+    got = ru.run_in_process(folders[name], dtype, steps, ru.peak_tokens(steps), block_size=block_size)
+    ru.compare(steps, got, reqs, ru.Oracle(folders[name]), TOL[dtype])
+
+
+@pytest.mark.parametrize("name", ["d128_g16", "d64_g8", "d112_bias"])
+def test_odd_shapes_whole_prompts(folders, name):
+    """Whole prompts of several hundred tokens: the contractions over many tokens and the prompt attention."""
+    vocab = SHAPES[name]["vocab_size"]
+    reqs = {f"r{n}": tiny.random_tokens(n, vocab, seed=n) for n in (66, 333, 520)}
+    steps = ru.trace_whole(reqs)
+    got = ru.run_in_process(folders[name], "bfloat16", steps, ru.peak_tokens(steps))
+    ru.compare(steps, got, reqs, ru.Oracle(folders[name]), TOL["bfloat16"])
