@@ -5,11 +5,13 @@ configuration file (here JSON with `LocalModelConfig`'s field names), the reques
     python -m cuca_b200 --model-dir DIR --prompt-len 128
     python -m cuca_b200 --random-weights 5 --model-config config.json --dtype bfloat16
 
-Flags of the reference: --config, --prompt (token ids here: no tokenizer is part of this engine),
---max-tokens (default 1024), --temperature (0 is greedy; default: the model's own). `--thinking` is accepted
-and ignored: chat templates are outside this engine. Ours: --model-dir, --model-config, --random-weights SEED,
---dtype, --top-k, --top-p, --seed, --prompt-len.
-It prints `load:`, `loaded on`, the generated ids, and the reference's `timing:` line on standard error.
+Flags of the reference: --config, --prompt (token ids; text when the model folder brings a tokenizer.json and
+the prompt is not a list of numbers), --max-tokens (default 1024), --temperature (0 is greedy; default: the
+model's own). `--thinking` is accepted and ignored: chat templates are outside this engine. Ours: --model-dir,
+--model-config, --random-weights SEED, --dtype, --top-k, --top-p, --seed, --prompt-len, --stop (a stop string,
+may be given several times; needs the tokenizer).
+It prints `load:`, `loaded on`, the generated ids (the text, with a tokenizer), and the reference's `timing:` line
+on standard error.
 """
 from __future__ import annotations
 
@@ -22,7 +24,8 @@ import time
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m cuca_b200", description=__doc__.split("\n\n")[0])
     ap.add_argument("--config", help="JSON file holding the LocalModelConfig")
-    ap.add_argument("--prompt", help="token ids separated by spaces or commas")
+    ap.add_argument("--prompt", help="token ids separated by spaces or commas; text if the folder has a tokenizer")
+    ap.add_argument("--stop", action="append", default=[], help="stop string (needs the folder's tokenizer)")
     ap.add_argument("--prompt-len", type=int, help="use this many seeded random token ids as the prompt")
     ap.add_argument("--thinking", default=None, help="accepted for parity with the reference; ignored")
     ap.add_argument("--max-tokens", type=int, default=1024)
@@ -58,8 +61,13 @@ def main(argv=None) -> int:
           f"{model.kv_cache_bytes() / 2**20:.0f} MiB of K/V pages)", file=sys.stderr)
 
     vocab = model.core.spec.vocab_size
+    as_text = False
     if args.prompt:
-        prompt = [int(t) for t in args.prompt.replace(",", " ").split()]
+        words = args.prompt.replace(",", " ").split()
+        if model.text is not None and not all(w.lstrip("-").isdigit() for w in words):
+            prompt, as_text = model.tokenize(args.prompt), True
+        else:
+            prompt = [int(t) for t in words]
     else:
         import numpy as np
         prompt = np.random.default_rng(1).integers(0, vocab, size=args.prompt_len or 16).tolist()
@@ -70,10 +78,15 @@ def main(argv=None) -> int:
     def on_token(seq, tok):
         if first[0] is None:
             first[0] = time.perf_counter() - asked
-        print(tok, end=" ", flush=True)
+        if not as_text:
+            print(tok, end=" ", flush=True)
+
+    def on_text(seq, fragment):
+        if as_text:
+            print(fragment, end="", flush=True)
 
     gen = model.generate(prompt, max_tokens=args.max_tokens, temperature=args.temperature, top_k=args.top_k,
-                         top_p=args.top_p, seed=args.seed, on_token=on_token)
+                         top_p=args.top_p, seed=args.seed, on_token=on_token, stop=args.stop, on_text=on_text)
     print()
     usage = gen.report.usage
     if first[0] is not None:

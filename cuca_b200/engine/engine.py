@@ -21,6 +21,8 @@ from .core import EngineCore
 from .graphs import MAX_HISTORY, DecodeGraphs
 from .scheduler import Plan, Request, Scheduler, SchedulerConfig, Sequence_
 from .step import StepEntry
+from .stop import StopMatcher
+from .text import TextCodec, TextStream
 
 
 @dataclass
@@ -44,6 +46,7 @@ class GenerationReport:
 class LocalGeneration:
     tokens: list
     report: GenerationReport
+    text: Optional[str] = None  # with a tokenizer attached: the reply, cut before a stop string
 
 
 class GpuBackend:
@@ -198,6 +201,7 @@ class LocalModel:
         if suppressed:
             self.backend.suppress = torch.tensor([int(t) for t in suppressed], dtype=torch.int32,
                                                  device=core.rt.device)
+        self.text = TextCodec.find(model_dir)  # None: token ids only
         self.load_seconds = 0.0
 
     # ------------------------------------------------------------ loading
@@ -244,24 +248,82 @@ class LocalModel:
             top_p=float(pick(top_p, s.top_p, "top_p", SamplingConfig.DEFAULT_TOP_P)),
             seed=seed if seed is not None else s.seed, stop_token_ids=tuple(stop_token_ids or ()))
 
+    def tokenize(self, text: str) -> list:
+        """Token ids of `text` (src/provider/local/mod.rs:3213); needs the folder's tokenizer."""
+        if self.text is None:
+            raise ValueError("this model folder has no tokenizer.json: prompts are lists of token ids")
+        return self.text.encode(text)
+
     def generate(self, prompts, max_tokens: Optional[int] = None, temperature: Optional[float] = None,
                  top_k: Optional[int] = None, top_p: Optional[float] = None, seed: Optional[int] = None,
-                 stop_token_ids: Iterable[int] = (), on_token=None):
+                 stop_token_ids: Iterable[int] = (), on_token=None, stop: Iterable[str] = (), on_text=None):
         """Generate for one prompt (a list of token ids) or several (a list of lists); returns one
         `LocalGeneration` or a list of them, in the order given. All prompts run together under continuous
-        batching."""
-        single = len(prompts) > 0 and not isinstance(prompts[0], (list, tuple))
+        batching. With a tokenizer in the model folder a prompt may be a string, the results carry their text,
+        `on_text(sequence, fragment)` streams it, and `stop` strings cut the reply before their first occurrence
+        (finish reason "stop"; src/provider/local/engine/stop.rs, scheduler.rs:92-136)."""
+        single = isinstance(prompts, str) or (len(prompts) > 0 and not isinstance(prompts[0], (list, tuple, str)))
         batch = [prompts] if single else list(prompts)
+        batch = [self.tokenize(p) if isinstance(p, str) else p for p in batch]
+        stop = [s for s in (stop or ()) if s]
+        if stop and self.text is None:
+            raise ValueError("stop strings need the model folder's tokenizer.json; use stop_token_ids")
         seqs = [self.scheduler.submit(self._request(p, max_tokens, temperature, top_k, top_p, seed, stop_token_ids))
                 for p in batch]
-        self.scheduler.run_until_done(on_token)
+        if self.text is None:
+            self.scheduler.run_until_done(on_token)
+            texts = {}
+        else:
+            texts = self._run_with_text(seqs, stop, on_token, on_text)
         out = [LocalGeneration(list(s.completion), GenerationReport(
             Usage(s.prompt_tokens, len(s.completion)), s.finish_reason or "error",
-            max(0.0, s.started_at - s.queued_at), s.error, s.preemptions)) for s in seqs]
+            max(0.0, s.started_at - s.queued_at), s.error, s.preemptions), texts.get(id(s))) for s in seqs]
         for s in seqs:
             if s in self.scheduler.finished:
                 self.scheduler.finished.remove(s)
         return out[0] if single else out
+
+    def _run_with_text(self, seqs, stop, on_token, on_text) -> dict:
+        """Runs the scheduler until these requests are done, turning their tokens into text as they come. A
+        request whose text completes a stop string is cancelled after the turn that sampled it (the scheduler
+        reports tokens from inside its own bookkeeping, so nothing is cancelled from the callback) and ends as
+        "stop" with the text before the stop string."""
+        streams = {id(s): (TextStream(self.text), StopMatcher(stop)) for s in seqs}
+        texts = {id(s): "" for s in seqs}
+        stopped, stopped_ids = [], set()
+
+        def emit(seq, fragment):
+            if fragment:
+                texts[id(seq)] += fragment
+                if on_text:
+                    on_text(seq, fragment)
+
+        def token(seq, tok):
+            if on_token:
+                on_token(seq, tok)
+            pair = streams.get(id(seq))
+            if pair is None or id(seq) in stopped_ids:
+                return
+            fragment, done = pair[1].push(pair[0].push(seq.completion))
+            emit(seq, fragment)
+            if done:
+                stopped.append(seq)
+                stopped_ids.add(id(seq))
+
+        sched = self.scheduler
+        sched._on_token = token
+        while sched.has_work():
+            progressed = sched.turn()
+            for seq in stopped:
+                if not seq.done:
+                    sched.cancel(seq)
+                    seq.finish_reason = "stop"
+            if progressed == 0 and sched.has_work():
+                raise RuntimeError("the scheduler made no progress: the page pool is too small for the queue's head")
+        for s in seqs:
+            if id(s) not in stopped_ids:
+                emit(s, streams[id(s)][1].flush())
+        return texts
 
     def generate_tokens(self, prompt, **kw):
         """Stream one request's tokens as they are sampled (src/provider/local/mod.rs:3276)."""

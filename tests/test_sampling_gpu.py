@@ -190,6 +190,42 @@ def test_streaming_and_stop_token(folders):
     assert cut.tokens == whole.tokens[:first] and cut.report.finish_reason == "stop"
 
 
+def test_stop_strings_and_text_with_a_tokenizer(folders, tmp_path):
+    """A model folder with a tokenizer.json: prompts may be text, replies carry text, a stop string cuts the reply
+    before its first occurrence and ends that request alone; without a tokenizer stop strings are refused."""
+    import shutil
+    import tokenizers
+    from cuca_b200 import LocalModel, LocalModelConfig
+    folder = tmp_path / "with_tokenizer"
+    shutil.copytree(folders["A"], folder)
+    vocab = {f"w{i}": i for i in range(tiny.CONFIGS["A"]["vocab_size"])}
+    tok = tokenizers.Tokenizer(tokenizers.models.WordLevel(vocab, unk_token="w0"))
+    tok.pre_tokenizer = tokenizers.pre_tokenizers.WhitespaceSplit()
+    tok.save(str(folder / "tokenizer.json"))
+    model = LocalModel.load(LocalModelConfig(source=str(folder), dtype="float32"))
+    prompt = "w5 w9 w200 w31"
+    assert model.tokenize(prompt) == [5, 9, 200, 31]
+    whole = model.generate(prompt, max_tokens=12, temperature=0.0)
+    assert whole.tokens == model.generate([5, 9, 200, 31], max_tokens=12, temperature=0.0).tokens
+    words = whole.text.split()
+    assert words == [f"w{t}" for t in whole.tokens]
+    stop = " ".join(words[5:7])                      # two tokens: the stop string is split across fragments
+    at = whole.text.find(stop)
+    fragments = []
+    other = [7, 7, 7]
+    cut, free = model.generate([prompt, other], max_tokens=12, temperature=0.0, stop=[stop],
+                               on_text=lambda seq, frag: fragments.append((seq.id, frag)))
+    assert cut.report.finish_reason == "stop" and cut.text == whole.text[:at]
+    assert len(cut.tokens) < 12
+    assert free.report.finish_reason == "length" and len(free.tokens) == 12 and stop not in free.text
+    assert "".join(f for i, f in fragments if i == fragments[0][0]) in (cut.text, free.text)
+    plain = LocalModel.load(LocalModelConfig(source=str(folders["A"]), dtype="float32"))
+    with pytest.raises(ValueError, match="tokenizer"):
+        plain.generate([5, 9], max_tokens=2, stop=["x"])
+    with pytest.raises(ValueError, match="tokenizer"):
+        plain.generate("w5 w9", max_tokens=2)
+
+
 def test_command_line(folders):
     import subprocess, sys
     from pathlib import Path
