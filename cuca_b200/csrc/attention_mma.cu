@@ -732,6 +732,19 @@ attn_mma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tmK, con
   // costs a few memory round trips, not one per chunk.
   constexpr int MAXS = 32;
   __shared__ float s_m[16][MAXS], s_f[16][MAXS], s_inv[16];
+  // Up to four output elements per thread and eight chunks (the common case): their partial sums are asked for
+  // now, together with the maxima and sums below, so that the merge pays one trip to memory, not two.
+  constexpr int PE = 4, PS = 8;
+  const bool pre = G * D <= PE * NTHREADS && n_used <= PS;
+  float v0[PE][PS];
+#pragma unroll
+  for (int e = 0; e < PE; ++e) {
+    const int idx = threadIdx.x + e * NTHREADS;
+    const float* src0 = part_row + (size_t)(idx / D) * n_splits * FR + idx % D;
+#pragma unroll
+    for (int sidx = 0; sidx < PS; ++sidx)
+      v0[e][sidx] = (pre && idx < G * D && sidx < n_used) ? __ldcg(src0 + (size_t)sidx * FR) : 0.f;
+  }
   for (int qd = threadIdx.x; qd < G * MAXS; qd += NTHREADS) {
     int item = qd / MAXS, sidx = qd % MAXS;
     float ms = -INFINITY, ls = 0.f;
@@ -757,16 +770,29 @@ attn_mma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tmK, con
     s_inv[item] = L > 0.f ? 1.f / L : 0.f;
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < G * D; idx += NTHREADS) {
-    int item = idx / D, dim = idx % D;
-    const float* src0 = part_row + (size_t)item * n_splits * FR + dim;
-    float v[MAXS];
+  if (pre) {
 #pragma unroll
-    for (int sidx = 0; sidx < MAXS; ++sidx) v[sidx] = sidx < n_used ? __ldcg(src0 + (size_t)sidx * FR) : 0.f;
-    float O = 0.f;
+    for (int e = 0; e < PE; ++e) {
+      const int idx = threadIdx.x + e * NTHREADS;
+      if (idx >= G * D) break;
+      const int item = idx / D, dim = idx % D;
+      float O = 0.f;
 #pragma unroll
-    for (int sidx = 0; sidx < MAXS; ++sidx) O += v[sidx] * s_f[item][sidx];
-    p.out[(size_t)dec_row * p.out_stride + (size_t)(kvh * G + item) * D + dim] = __float2bfloat16_rn(O * s_inv[item]);
+      for (int sidx = 0; sidx < PS; ++sidx) O += v0[e][sidx] * s_f[item][sidx];  // chunks past n_used: 0 x 0
+      p.out[(size_t)dec_row * p.out_stride + (size_t)(kvh * G + item) * D + dim] = __float2bfloat16_rn(O * s_inv[item]);
+    }
+  } else {
+    for (int idx = threadIdx.x; idx < G * D; idx += NTHREADS) {
+      int item = idx / D, dim = idx % D;
+      const float* src0 = part_row + (size_t)item * n_splits * FR + dim;
+      float v[MAXS];
+#pragma unroll
+      for (int sidx = 0; sidx < MAXS; ++sidx) v[sidx] = sidx < n_used ? __ldcg(src0 + (size_t)sidx * FR) : 0.f;
+      float O = 0.f;
+#pragma unroll
+      for (int sidx = 0; sidx < MAXS; ++sidx) O += v[sidx] * s_f[item][sidx];
+      p.out[(size_t)dec_row * p.out_stride + (size_t)(kvh * G + item) * D + dim] = __float2bfloat16_rn(O * s_inv[item]);
+    }
   }
   if (threadIdx.x == 0) p.counters[blockIdx.z * p.nkv + kvh] = 0;
 }
