@@ -294,6 +294,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       for (int i = 1; i < KV_STAGES; ++i) r = st == i ? d[i] : r;
       return r;
     };
+    // The second query tile starts when the first has handed over its first P: from then on one tile's exponents
+    // (XU pipe) run while the other's contractions do (tensor pipe), instead of both tiles doing the same thing at
+    // the same time and leaving the other pipe idle.
+    if (ok && x == 1 && n_tiles > 1) ok = mbar_wait(&p_full[0], 0, p.err, abort_flag);
     int next_sc = 0, next_pv = 0;
     unsigned long long idle_since = 0;
     unsigned spins = 0;
