@@ -98,3 +98,26 @@ def test_codec_round_trip_and_stream(word_tokenizer):
 
 def test_a_folder_without_tokenizer_has_no_codec(tmp_path):
     assert TextCodec.find(tmp_path) is None
+
+
+def test_a_character_split_over_two_tokens_is_held_until_it_is_whole(tmp_path):
+    """A byte-level vocabulary trained on ASCII alone: "é" is two tokens; the first alone decodes to the
+    replacement character, which must not be streamed."""
+    tokenizers = pytest.importorskip("tokenizers")
+    tok = tokenizers.Tokenizer(tokenizers.models.BPE())
+    tok.pre_tokenizer = tokenizers.pre_tokenizers.ByteLevel(add_prefix_space=False)
+    tok.decoder = tokenizers.decoders.ByteLevel()
+    trainer = tokenizers.trainers.BpeTrainer(vocab_size=300, initial_alphabet=tokenizers.pre_tokenizers.ByteLevel.alphabet(),
+                                             show_progress=False)
+    tok.train_from_iterator(["plain ascii text only", "more plain text"], trainer)
+    tok.save(str(tmp_path / "tokenizer.json"))
+    codec = TextCodec.find(tmp_path)
+    ids = codec.encode("caf\u00e9 ok")
+    assert codec.decode(ids) == "caf\u00e9 ok" and len(ids) >= 5
+    stream, seen, pieces = TextStream(codec), [], []
+    for t in ids:
+        seen.append(t)
+        pieces.append(stream.push(seen))
+    assert "".join(pieces) == "caf\u00e9 ok"
+    assert all("\ufffd" not in piece for piece in pieces)
+    assert "" in pieces  # the first half of the character gave nothing
