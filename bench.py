@@ -191,6 +191,8 @@ def main() -> int:
     prefill = {"value": round(T / (prefill_ms / 1e3), 1), "tokens": T, "ms": round(prefill_ms, 3),
                "frac": round(prefill_flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
                "tflops": round(prefill_flops / (prefill_ms / 1e3) / 1e12, 1)}
+    if "bf16_tflops_sustained" in pk:  # the prompts are timed back to back, under the power cap
+        prefill["frac_of_sustained"] = round(prefill_flops / (prefill_ms / 1e3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
 
     # ------------------------------------------------------------ decode, device only: K captured steps
     def decode_device(batch, steps, warmup):
