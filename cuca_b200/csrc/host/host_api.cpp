@@ -41,6 +41,7 @@ HOST_API void cuca_host_pools_drop_seq(void* h, int seq) { ((KvPools*)h)->drop_s
 HOST_API void cuca_host_pools_owed(void* h, int seq, int tokens, int* out) { ((KvPools*)h)->owed(seq, tokens, out); }
 HOST_API int cuca_host_pools_can_give(void* h, const int* owed) { return ((KvPools*)h)->can_give(owed) ? 1 : 0; }
 static int pool_status(KvPools* p, Status s) { return s == OK ? 0 : fail(s, p->error()); }
+static bool group_ok(void* h, int g) { return g >= 0 && g < ((KvPools*)h)->n_groups(); }
 HOST_API int cuca_host_pools_reserve(void* h, int seq, int upto) { return pool_status((KvPools*)h, ((KvPools*)h)->reserve(seq, upto)); }
 HOST_API int cuca_host_pools_release_window(void* h, int seq) {
   const int n = ((KvPools*)h)->release_window(seq);
@@ -52,12 +53,12 @@ HOST_API int cuca_host_pools_release(void* h, int seq) { return pool_status((KvP
 HOST_API int cuca_host_pools_publish(void* h, int seq, const int* ids, int n) { return pool_status((KvPools*)h, ((KvPools*)h)->publish(seq, ids, n)); }
 HOST_API int cuca_host_pools_finish(void* h, int seq, const int* ids, int n) { return pool_status((KvPools*)h, ((KvPools*)h)->finish(seq, ids, n)); }
 HOST_API int cuca_host_pools_new_seq_with_prefix(void* h, const int* prompt, int n) { return ((KvPools*)h)->new_seq_with_prefix(prompt, n); }
-HOST_API int cuca_host_pools_cached_blocks(void* h, int g) { return ((KvPools*)h)->pool(g).cached_count(); }
+HOST_API int cuca_host_pools_cached_blocks(void* h, int g) { return group_ok(h, g) ? ((KvPools*)h)->pool(g).cached_count() : -1; }
 HOST_API void cuca_host_pools_reset(void* h) { ((KvPools*)h)->reset(); }
 HOST_API int cuca_host_pools_check(void* h) { return pool_status((KvPools*)h, ((KvPools*)h)->check()); }
 HOST_API int cuca_host_pools_live(void* h) { return ((KvPools*)h)->live(); }
-HOST_API int cuca_host_pools_free_blocks(void* h, int g) { return ((KvPools*)h)->pool(g).free_count(); }
-HOST_API int cuca_host_pools_total_blocks(void* h, int g) { return ((KvPools*)h)->pool(g).n_blocks(); }
+HOST_API int cuca_host_pools_free_blocks(void* h, int g) { return group_ok(h, g) ? ((KvPools*)h)->pool(g).free_count() : -1; }
+HOST_API int cuca_host_pools_total_blocks(void* h, int g) { return group_ok(h, g) ? ((KvPools*)h)->pool(g).n_blocks() : -1; }
 
 // a request's record: field 0 length, 1 released, 2 + g first_live, 2 + G + g dirty_from (get / set)
 HOST_API int cuca_host_seq_get(void* h, int seq, int field) {
@@ -85,7 +86,7 @@ HOST_API int cuca_host_seq_set(void* h, int seq, int field, int value) {
 // the request's table in group g: its length; entries copied into `out` (up to cap)
 HOST_API int cuca_host_seq_table(void* h, int seq, int g, int* out, int cap) {
   SeqBlocks* s = ((KvPools*)h)->seq(seq);
-  if (!s) return -1;
+  if (!s || !group_ok(h, g)) return -1;
   const std::vector<int>& t = s->tables[g];
   for (int i = 0; i < (int)t.size() && i < cap; ++i) out[i] = t[i];
   return (int)t.size();
@@ -128,6 +129,10 @@ HOST_API int cuca_host_step_pack(void* pools, int n, const int* seqs, const int*
   return st == OK ? 0 : fail(st, "the staging buffer is too small for this step");
 }
 HOST_API int cuca_host_table_updates(void* pools, const int* seqs, const int* slots, int n, int table_width, int group, int* out, int cap) {
+  if (!group_ok(pools, group)) {  // -2: not the "buffer too small" answer
+    fail(INVALID, "no such group of caches");
+    return -2;
+  }
   return table_updates(*(KvPools*)pools, seqs, slots, n, table_width, group, out, cap);
 }
 HOST_API int cuca_host_step_advance(void* pools, const int* seqs, const int* n_tokens, int n) {

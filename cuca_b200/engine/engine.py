@@ -96,6 +96,8 @@ class GpuBackend:
                 buf = staging.take(2 * n * core.cache.table_width)
                 count = lib.cuca_host_table_updates(core.pools._h, handles, slots, n, core.cache.table_width, gi,
                                                     buf.data_ptr(), buf.shape[0])
+            if count < 0:
+                raise RuntimeError(host.last_error() or "page-table updates do not fit their staging buffer")
             if count > 0:
                 dev = staging.send(2 * count)
                 ops.scatter_int(core.cache.tables[gi], dev[:count], dev[count:])
