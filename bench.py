@@ -219,7 +219,7 @@ def main() -> int:
         w = time.perf_counter()
         torch.cuda.nvtx.range_push("decode_timed_b%d" % batch)
         a.record()
-        hist = backend.burst(seqs, tokens, steps)
+        hist = backend.burst(seqs, tokens, steps, check=False)
         b.record()
         torch.cuda.synchronize()
         torch.cuda.nvtx.range_pop()

@@ -143,6 +143,12 @@ class LlamaConfig:
             # the reference has no name for an mlp bias tensor
             # (src/provider/local/convert/tensors.rs:899-904)
             raise ConfigError("config.json `mlp_bias` = true: feed-forward biases are not part of this architecture")
+        for key in ("hidden_act", "hidden_activation"):
+            act = cfg.get(key)
+            if act is not None and str(act).lower() not in ("silu", "swish"):
+                # the reference fixes the activation by the architecture's row: SiLU for this one
+                # (src/provider/local/model/arch.rs:283-319); another one here would run SiLU without a word
+                raise ConfigError(f"config.json `{key}` = {act!r}: this architecture's feed-forward is SiLU-gated")
         eps = _opt(cfg, "rms_norm_eps", 1e-6, float)
         if not eps > 0.0:
             raise ConfigError(f"config.json `rms_norm_eps` must be positive, found {eps}")

@@ -556,3 +556,47 @@ CUCA_API int cuca_rope_store_partial(const float* partial, int n_slices, size_t 
   CUCA_CHECK_LAUNCH("rope_store_partial");
   return 0;
 }
+
+// ---------------------------------------------------------------- random weights
+// Element i of a tensor is a function of (key, i) alone, so the same values come out on the host and on the
+// device, whole or in pieces: outputs 3i, 3i+1, 3i+2 of a SplitMix64 stream that starts at `key` give twelve
+// 16-bit fields whose sum is near-normal (Irwin-Hall); v = (2 sum - 12 * 65535) * scale, then mean + v, each a
+// single 32-bit rounding (no fused multiply-add, so the host restates it exactly).
+__device__ __forceinline__ unsigned long long splitmix_out(unsigned long long state) {
+  unsigned long long z = state;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+template <typename T>
+__global__ void random_normal_kernel(T* __restrict__ out, size_t n, size_t first, unsigned long long key, float mean,
+                                     float scale) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const unsigned long long e = first + i;
+  int sum = 0;
+#pragma unroll
+  for (int j = 0; j < 3; ++j) {
+    unsigned long long h = splitmix_out(key + (3ull * e + (unsigned long long)j + 1ull) * 0x9E3779B97F4A7C15ull);
+    sum += (int)(h & 0xFFFF) + (int)((h >> 16) & 0xFFFF) + (int)((h >> 32) & 0xFFFF) + (int)(h >> 48);
+  }
+  float v = __fadd_rn(mean, __fmul_rn((float)(2 * sum - 12 * 65535), scale));
+  out[i] = from_f32<T>(v);
+}
+
+// out[i] = mean + normal(first + i) * std for i < n (`first`: the element number out[0] has in its tensor).
+CUCA_API int cuca_random_normal(void* out, int dtype, size_t n, size_t first, unsigned long long key, float mean,
+                                float scale, cudaStream_t stream) {
+  if (n == 0) return 0;
+  CUCA_REQUIRE(n < ((size_t)1 << 40), "random_normal: %zu elements in one call", n);
+  unsigned blocks = (unsigned)((n + 255) / 256);
+  if (dtype == CUCA_F32)
+    random_normal_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, n, first, key, mean, scale);
+  else if (dtype == CUCA_BF16)
+    random_normal_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)out, n, first, key, mean, scale);
+  else
+    CUCA_REQUIRE(false, "random_normal: unknown dtype %d", dtype);
+  CUCA_CHECK_LAUNCH("random_normal");
+  return 0;
+}

@@ -490,11 +490,13 @@ CUCA_API int cuca_sample(const float* logits, size_t row_stride, int n_rows, int
 namespace {
 __global__ void decode_advance_kernel(int* __restrict__ tokens, int* __restrict__ positions,
                                       const int* __restrict__ slot_of_row, const int* __restrict__ sampled,
-                                      int* __restrict__ history, int* __restrict__ counter, int n, int max_steps) {
+                                      int* __restrict__ history, int* __restrict__ counter, int n, int max_steps,
+                                      const int* __restrict__ err, int* __restrict__ err_out) {
   pdl_trigger();
   pdl_wait();
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   int step = *counter;
+  if (i == 0 && err && err_out) *err_out = *err;
   if (i < n) {
     if (slot_of_row[i] >= 0) {
       tokens[i] = sampled[i];
@@ -509,13 +511,16 @@ __global__ void decode_advance_kernel(int* __restrict__ tokens, int* __restrict_
 
 // After a decode step: every live row's sampled token becomes its next input and its position moves on, so the
 // same captured step can run again without the host; sampled tokens are also appended to history[step][row].
-// One block only (n <= 1024), so the counter update is ordered after every read of it.
+// One block only (n <= 1024), so the counter update is ordered after every read of it. `err_out` (may be null)
+// receives the device error word as it stands after the step's kernels, so that the host's one read of the
+// sampled tokens can bring it along.
 CUCA_API int cuca_decode_advance(int* tokens, int* positions, const int* slot_of_row, const int* sampled,
-                                 int* history, int* counter, int n, int max_steps, cudaStream_t stream) {
+                                 int* history, int* counter, int n, int max_steps, const int* err, int* err_out,
+                                 cudaStream_t stream) {
   if (n == 0) return 0;
   CUCA_REQUIRE(n <= 1024, "decode_advance: at most 1024 rows");
   cuca_launch(decode_advance_kernel, dim3(1), dim3(1024), 0, stream, true, tokens, positions, slot_of_row, sampled,
-              history, counter, n, max_steps);
+              history, counter, n, max_steps, err, err_out);
   CUCA_CHECK_LAUNCH("decode_advance");
   return 0;
 }

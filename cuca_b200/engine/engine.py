@@ -68,6 +68,7 @@ class GpuBackend:
         self.graphs = DecodeGraphs(core, self)
         self.graph_steps = 0
         self.eager_steps = 0
+        self.last_graph = None  # the captured step that ran last
 
     def start(self, seq: Sequence_) -> None:
         """A request takes its slot: clear its state, set its sampling constants and its generator."""
@@ -111,7 +112,11 @@ class GpuBackend:
         self._table_updates(seqs)
         g.load_rows([p.tokens[0] for p in plans], starts, [s.slot for s in seqs])
         g.replay()
-        tokens = g.sampled[:n].tolist()  # the one synchronisation of a step
+        self.last_graph = g
+        out = g.sampled.tolist()  # the one synchronisation of a step; its last word is the device error word
+        if out[g.bucket]:
+            self.core.rt.raise_device_error(out[g.bucket])  # before anything is applied: the step is lost
+        tokens = out[:n]
         self._advance(seqs, 1)
         self.core.stepper.steps += 1
         self.graph_steps += 1
@@ -123,9 +128,11 @@ class GpuBackend:
                                               host.ints([n_steps] * len(seqs)), len(seqs)):
             raise RuntimeError(host.last_error())
 
-    def burst(self, seqs, tokens, n_steps: int):
+    def burst(self, seqs, tokens, n_steps: int, check: bool = True):
         """`n_steps` decode steps back to back on the device, each feeding its sampled tokens to the next; the
-        host only reserves pages ahead and reads the tokens at the end. Returns a [n_steps, requests] tensor."""
+        host only reserves pages ahead and reads the tokens at the end. Returns a [n_steps, requests] tensor.
+        With `check` the device error word is read after the last step (one synchronisation) and a recorded fault
+        raises before any request advances."""
         core = self.core
         n = len(seqs)
         if n_steps > MAX_HISTORY:
@@ -140,6 +147,10 @@ class GpuBackend:
         g.counter.zero_()
         for _ in range(n_steps):
             g.replay()
+        if check:
+            code = int(g.sampled[g.bucket].item())
+            if code:
+                self.core.rt.raise_device_error(code)
         self._advance(seqs, n_steps)
         self.graph_steps += n_steps
         return g.history[:n_steps, :n]

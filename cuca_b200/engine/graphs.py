@@ -38,7 +38,9 @@ class DecodeGraph:
         self.positions = self.meta[bucket:2 * bucket]
         self.slot_of_row = self.meta[2 * bucket:]
         self.logit_rows = torch.arange(bucket, dtype=torch.int32, device=dev)
-        self.sampled = torch.full((bucket,), -1, dtype=torch.int32, device=dev)
+        # the sampled token of every row, then the device error word as it stood at the end of the step
+        self.sampled = torch.full((bucket + 1,), -1, dtype=torch.int32, device=dev)
+        self.sampled[bucket] = 0
         self.history = torch.zeros(MAX_HISTORY, bucket, dtype=torch.int32, device=dev)
         self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
         self.pinned = torch.zeros(3 * bucket, dtype=torch.int32).pin_memory()
@@ -52,16 +54,17 @@ class DecodeGraph:
             attention_plan=AttentionPlan(None, bucket, max_len, None, None, 0, fixed_chunking=chunking))
         self.graph = None
         self.scratch = None
+        self.logits = None  # [bucket, vocab]: what the last replay's model pass left (valid until the next replay)
         self.launches = 0
 
     def _body(self):
-        logits = self.core.model.forward(self.batch, self.core.cache)
+        logits = self.logits = self.core.model.forward(self.batch, self.core.cache)
         be = self.backend
         if be.suppress is not None:
             ops.suppress_tokens(logits, be.suppress)
         ops.sample(logits, be.temperature, be.top_k, be.top_p, be.rng, self.slot_of_row, self.sampled, self.scratch)
         ops.decode_advance(self.tokens, self.positions, self.slot_of_row, self.sampled, self.history, self.counter,
-                           MAX_HISTORY)
+                           MAX_HISTORY, self.core.rt.err, self.sampled[self.bucket:])
 
     def capture(self, needs_scratch: bool) -> None:
         if needs_scratch:

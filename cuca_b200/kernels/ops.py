@@ -67,6 +67,15 @@ def rope_store(qkv, positions, seq_of_row, tables, cos, sin, rotary_dim, kpool, 
         _p(err), _stream()), "rope_store")
 
 
+def random_normal(out: torch.Tensor, key: int, first: int, mean: float, scale: float) -> None:
+    """out.view(-1)[i] = mean + normal(key, first + i) * (2 * 65536 * scale): the counter-based generator of the
+    random-weights mode (`weights/loader.py:host_normal` is its host form, bit for bit)."""
+    _cuda(out)
+    lib = library.load()
+    library.check(lib.cuca_random_normal(_p(out), dtype_code(out.dtype), out.numel(), int(first), int(key),
+                                         float(mean), float(scale), _stream()), "random_normal")
+
+
 def swiglu(gate_up, out) -> None:
     _cuda(gate_up, out)
     lib = library.load()
@@ -151,18 +160,27 @@ def gemm(a, w, out, epilogue=EPI_STORE, bias=None, err=None) -> None:
 
 
 _attn_scratch: dict = {}
+_attn_scratch_retired: list = []  # superseded buffers: a captured graph may still hold their addresses
 USE_TC_ATTENTION = True  # prompt portions through the tcgen05 attention where the shape allows
 
 
 def attention_scratch(device, floats: int, counters: int):
     """Scratch of the split-key decode attention: partial (acc, max, sum) per chunk, arrival counters
-    (zeroed once; the kernel leaves them zeroed). Grows when a step needs more."""
+    (zeroed once; the kernel leaves them zeroed). Grows (by doubling at least) when a step needs more. A captured
+    graph keeps the addresses it was captured with, so a superseded buffer is never freed: replays of an older
+    graph go on writing into memory that is still this module's, and its counters still start at zero."""
     key = (device.type, device.index)
     part, cnt = _attn_scratch.get(key, (None, None))
     if part is None or part.numel() < floats:
-        part = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
+        if part is not None:
+            _attn_scratch_retired.append(part)
+        part = torch.empty(max(floats, 1 << 20, 2 * (part.numel() if part is not None else 0)), dtype=torch.float32,
+                           device=device)
     if cnt is None or cnt.numel() < counters:
-        cnt = torch.zeros(max(counters, 4096), dtype=torch.int32, device=device)
+        if cnt is not None:
+            _attn_scratch_retired.append(cnt)
+        cnt = torch.zeros(max(counters, 4096, 2 * (cnt.numel() if cnt is not None else 0)), dtype=torch.int32,
+                          device=device)
     _attn_scratch[key] = (part, cnt)
     return part, cnt
 
@@ -311,11 +329,14 @@ def sample(logits, temperature, top_k, top_p, rng_state, slot_of_row, out, scrat
                                   0 if scratch is None else scratch.shape[1], _stream()), "sample")
 
 
-def decode_advance(tokens, positions, slot_of_row, sampled, history, counter, max_steps) -> None:
-    """tokens <- sampled, positions += 1 for live rows; history[counter] <- sampled; counter += 1."""
+def decode_advance(tokens, positions, slot_of_row, sampled, history, counter, max_steps, err=None,
+                   err_out=None) -> None:
+    """tokens <- sampled, positions += 1 for live rows; history[counter] <- sampled; counter += 1;
+    err_out[0] <- err[0] (the device error word rides along with the sampled tokens)."""
     lib = library.load()
     library.check(lib.cuca_decode_advance(_p(tokens), _p(positions), _p(slot_of_row), _p(sampled), _p(history),
-                                          _p(counter), tokens.shape[0], int(max_steps), _stream()), "decode_advance")
+                                          _p(counter), tokens.shape[0], int(max_steps), _p(err), _p(err_out),
+                                          _stream()), "decode_advance")
 
 
 # ------------------------------------------------------------------ partial sums (decode)

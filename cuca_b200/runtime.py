@@ -75,5 +75,10 @@ class Runtime:
         """Read the error word (synchronises); raise if a kernel recorded a fault."""
         code = int(self.err.item())
         if code:
-            self.err.zero_()
-            raise DeviceFault(_ERR_TEXT.get(code, f"device error {code}"))
+            self.raise_device_error(code)
+
+    def raise_device_error(self, code: int) -> None:
+        """A kernel recorded `code` (read by the caller, e.g. along with a step's sampled tokens): clear the
+        word and raise."""
+        self.err.zero_()
+        raise DeviceFault(_ERR_TEXT.get(code, f"device error {code}"))

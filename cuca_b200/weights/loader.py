@@ -10,15 +10,18 @@ bfloat16, 32-bit stays 32-bit, integer tables become int32); binding then casts
 matrices to the compute dtype and leaves vectors marked `keep_fp32` in 32-bit.
 
 Sources: a model folder (`FolderSource`) or seeded random weights
-(`RandomSource`: N(0, std) per tensor from (seed, tensor name); norm weights 1).
+(`RandomSource`: N(0, std) per element from (seed, tensor name, element number); norm weights 1
+or 1 + N(0, norm_std)).
 """
 from __future__ import annotations
 
 import hashlib
 import json
+import math
 from pathlib import Path
 from typing import Callable
 
+import numpy as np
 import torch
 
 from ..parts.base import TensorNeed
@@ -83,36 +86,78 @@ class FolderSource(WeightSource):
         return str(self.dir)
 
 
-def _tensor_seed(seed: int, name: str) -> int:
+def tensor_key(seed: int, name: str) -> int:
+    """64-bit key of one tensor's random stream, from (seed, tensor name)."""
     h = hashlib.sha256(f"{seed}:{name}".encode()).digest()
-    return int.from_bytes(h[:8], "little") & ((1 << 63) - 1)
+    return int.from_bytes(h[:8], "little")
+
+
+_GOLDEN = np.uint64(0x9E3779B97F4A7C15)
+_SUM_SIGMA = math.sqrt(65536.0 ** 2 - 1.0)  # deviation of the sum of twelve uniform 16-bit fields
+
+
+def normal_scale(std: float) -> np.float32:
+    return np.float32(std / (2.0 * _SUM_SIGMA))
+
+
+def host_normal(key: int, first: int, n: int, mean: float, std: float) -> np.ndarray:
+    """Elements first..first+n-1 of the tensor with this key as float32: element i is a function of (key, i)
+    alone. Outputs 3i, 3i+1, 3i+2 of a SplitMix64 stream that starts at `key` give twelve 16-bit fields whose sum
+    is near-normal; v = (2 sum - 12 * 65535) * scale, then mean + v, each one 32-bit rounding. The device kernel
+    (`cuca_random_normal`) does the same arithmetic, so host-drawn and device-drawn weights are the same bits."""
+    out = np.empty(n, dtype=np.float32)
+    scale, mean32 = normal_scale(std), np.float32(mean)
+    chunk = 1 << 16  # temporaries stay in cache
+    with np.errstate(over="ignore"):
+        for lo in range(0, n, chunk):
+            m = min(chunk, n - lo)
+            e = np.arange(first + lo, first + lo + m, dtype=np.uint64)
+            total = np.zeros(m, dtype=np.int64)
+            for j in range(3):
+                z = np.uint64(key) + (np.uint64(3) * e + np.uint64(j + 1)) * _GOLDEN
+                z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+                z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+                z = z ^ (z >> np.uint64(31))
+                for shift in (0, 16, 32, 48):
+                    total += ((z >> np.uint64(shift)) & np.uint64(0xFFFF)).astype(np.int64)
+            v = (2 * total - 12 * 65535).astype(np.float32) * scale
+            out[lo:lo + m] = mean32 + v
+    return out
 
 
 class RandomSource(WeightSource):
-    """Seeded random weights for the tensors a model needs: every weight N(0, std), norm weights 1.0.
-
-    Values depend on (seed, tensor name) and on the device they are drawn on; the
-    model-folder writer always draws on the CPU, so a folder is reproducible.
-    """
+    """Seeded random weights for the tensors a model needs: every weight N(0, std); norm weights
+    (`init="ones"`) 1.0, or 1 + N(0, norm_std) when `norm_std` is given so that a swapped or dropped norm
+    weight changes the logits. Optional tensors that the model lists (biases that its configuration
+    switches on) are drawn too. A value depends on (seed, tensor name, element number) only: drawn on the host
+    or by the device kernel, whole or in pieces, the bits are the same."""
 
     def __init__(self, needs: dict[str, TensorNeed], seed: int, std: float = 0.02, device="cpu",
-                 dtype: torch.dtype = torch.bfloat16):
-        self.needs = {n: t for n, t in needs.items() if not t.optional}
+                 dtype: torch.dtype = torch.bfloat16, norm_std: float = 0.0):
+        self.needs = dict(needs)
         self.seed, self.std, self.device, self.dtype = int(seed), float(std), torch.device(device), dtype
+        self.norm_std = float(norm_std)
 
     def shapes(self):
         return {n: tuple(t.shape) for n, t in self.needs.items()}
 
     def read(self, name):
         need = self.needs[name]
-        if need.init == "ones":
+        ones = need.init == "ones"
+        if ones and self.norm_std == 0.0:
             return torch.ones(need.shape, dtype=torch.float32, device=self.device)
-        g = torch.Generator(device=self.device)
-        g.manual_seed(_tensor_seed(self.seed, name))
-        t = torch.empty(need.shape, dtype=torch.float32 if self.device.type == "cpu" else self.dtype,
-                        device=self.device)
-        t.normal_(0.0, self.std, generator=g)
-        return t.to(self.dtype)
+        mean, std = (1.0, self.norm_std) if ones else (0.0, self.std)
+        dtype = self.dtype  # what a folder of this dtype would hold (binding widens norm weights to 32-bit)
+        n = 1
+        for s in need.shape:
+            n *= int(s)
+        key = tensor_key(self.seed, name)
+        if self.device.type == "cuda":
+            from ..kernels import ops
+            t = torch.empty(need.shape, dtype=dtype, device=self.device)
+            ops.random_normal(t, key, 0, mean, float(normal_scale(std)))
+            return t
+        return torch.from_numpy(host_normal(key, 0, n, mean, std)).view(need.shape).to(dtype)
 
     def describe(self):
         return f"random weights (seed {self.seed}, std {self.std})"
@@ -149,16 +194,17 @@ def binder(needs: dict[str, TensorNeed], source: WeightSource, device, compute_d
 
 
 def write_model_folder(folder, config_json: dict, needs: dict[str, TensorNeed], seed: int, std: float = 0.02,
-                       dtype: torch.dtype = torch.bfloat16) -> Path:
-    """Random-weights mode: write `config.json` and `model.safetensors` for a configuration and a seed."""
+                       dtype: torch.dtype = torch.bfloat16, norm_std: float = 0.0, device="cpu") -> Path:
+    """Random-weights mode: write `config.json` and `model.safetensors` for a configuration and a seed.
+    `device`: where the values are drawn (the bits are the same; a CUDA device draws a large model in seconds)."""
     folder = Path(folder)
     folder.mkdir(parents=True, exist_ok=True)
-    src = RandomSource(needs, seed, std, device="cpu", dtype=dtype)
+    src = RandomSource(needs, seed, std, device=device, dtype=dtype, norm_std=norm_std)
     tensors = {}
     for name in src.shapes():
-        t = src.read(name)
+        t = src.read(name).cpu()
         tensors[name] = t if needs[name].init == "ones" and dtype == torch.float32 else t.to(dtype)
     (folder / "config.json").write_text(json.dumps(config_json, indent=2))
     st.write_safetensors(folder / "model.safetensors", tensors,
-                         metadata={"format": "pt", "seed": seed, "std": std})
+                         metadata={"format": "pt", "seed": seed, "std": std, "norm_std": norm_std})
     return folder

@@ -42,6 +42,7 @@ def test_round_trip_through_config_json():
     ("num_key_value_heads", 3, "divide"), ("head_dim", 15, "even"), ("num_hidden_layers", 0, "positive"),
     ("rms_norm_eps", 0.0, "positive"), ("rope_scaling", {"rope_type": "yarn9"}, "yarn9"),
     ("mlp_bias", True, "mlp_bias"), ("hidden_size", "wide", "hidden_size"),
+    ("hidden_act", "gelu", "SiLU"), ("hidden_activation", "gelu_pytorch_tanh", "SiLU"),
 ])
 def test_bad_values_are_refused(key, value, word):
     cfg = copy.deepcopy(tiny.TINY_A)

@@ -34,8 +34,74 @@ def test_graph_decode_equals_eager_decode(folder, dtype):
         cfgj, weights = plain_llama.load_model_dir(folder)
         assert a[1].tokens == plain_llama.generate_greedy(cfgj, weights, prompts[1], 40)
     else:
-        agree = sum(x == y for o, p in zip(a, b) for x, y in zip(o.tokens, p.tokens))
-        assert agree >= 100  # bf16: the split of keys over chunks differs between the two paths
+        # bfloat16 may take another branch where two logits nearly tie (the split of keys over chunks differs
+        # between the two paths): every token of either path must be a near-maximum of the oracle's logits
+        cfgj, weights = plain_llama.load_model_dir(folder)
+        for outs in (a, b):
+            for prompt, out in zip(prompts, outs):
+                ref = plain_llama.forward(cfgj, weights, prompt + out.tokens)
+                for i, tok in enumerate(out.tokens):
+                    row = ref[len(prompt) - 1 + i]
+                    assert float(row.max() - row[tok]) < 0.03 * float(row.abs().max()), f"token {i}: no near-maximum"
+
+
+@pytest.mark.parametrize("which", ["D", "E"])
+def test_logits_inside_captured_graphs_match_plain(tmp_path_factory, which):
+    """Head sizes 128 and 64 in bfloat16: a decode step is one captured graph whose attention is the fused,
+    TMA-fed decode form reading unadded K slices. The logits each replay leaves are compared with the plain
+    implementation at that position, and every sampled token is the first maximum of those logits."""
+    import torch
+    from cuca_b200 import BatchingConfig, LocalModel, LocalModelConfig
+    d = tmp_path_factory.mktemp(f"graph_{which}")
+    tiny.write_tiny(d, which)
+    cfgj, weights = plain_llama.load_model_dir(d)
+    vocab = cfgj["vocab_size"]
+    prompts = [tiny.random_tokens(n, vocab, seed=500 + n) for n in (2, 61, 200, 500)]
+    m = LocalModel.load(LocalModelConfig(source=str(d), dtype="bfloat16", batching=BatchingConfig(max_sequences=4)))
+    be, seen = m.backend, []
+    run_graph = be._run_decode_graph
+
+    def spy(plans):
+        tokens = run_graph(plans)
+        logits = be.last_graph.logits[:len(plans)].float().cpu()
+        seen.extend((p.seq, p.seq.blocks.length - 1, logits[i], tokens[i]) for i, p in enumerate(plans))
+        return tokens
+
+    be._run_decode_graph = spy
+    outs = m.generate(prompts, max_tokens=40, temperature=0.0)
+    assert be.graph_steps >= 30 and len(seen) >= 100  # steps that also carry a prompt portion run eagerly
+    refs = {}
+    for seq, pos, logits, tok in seen:
+        if id(seq) not in refs:
+            refs[id(seq)] = plain_llama.forward(cfgj, weights, list(seq.request.prompt) + list(seq.completion))
+        ref = refs[id(seq)][pos]
+        err = float((logits - ref).abs().max()) / float(ref.abs().max())
+        assert err <= 3e-2, f"position {pos}: relative error {err:.3e} inside the captured step"
+        assert tok == int(torch.argmax(logits)), f"position {pos}: the sampled token is not the maximum"
+    assert all(len(o.tokens) == 40 for o in outs)
+
+
+def test_an_older_graph_survives_the_growth_of_the_attention_scratch(tmp_path_factory):
+    """A captured step keeps the addresses of the decode attention's scratch. When a later, larger step makes that
+    scratch grow, the older graph must still find its buffers alive and its counters zeroed."""
+    from cuca_b200 import BatchingConfig, LocalModel, LocalModelConfig
+    from cuca_b200.kernels import ops
+    d = tmp_path_factory.mktemp("graph_grow")
+    tiny.write_tiny(d, "D")
+    vocab = tiny.CONFIGS["D"]["vocab_size"]
+    prompt = tiny.random_tokens(300, vocab, seed=9)
+    cfg = LocalModelConfig(source=str(d), dtype="bfloat16", batching=BatchingConfig(max_sequences=2))
+    m = LocalModel.load(cfg)
+    first = m.generate(prompt, max_tokens=12, temperature=0.0).tokens      # captures the one-row graph
+    import torch
+    dev = torch.device("cuda:0")
+    part, cnt = ops.attention_scratch(dev, 1, 1)
+    grown = ops.attention_scratch(dev, 2 * part.numel() + 1, 2 * cnt.numel() + 1)  # what a larger step would ask for
+    assert grown[0].data_ptr() != part.data_ptr() and grown[1].data_ptr() != cnt.data_ptr()
+    junk = [torch.full((part.numel(),), float("nan"), device=dev) for _ in range(4)]  # takes freed memory, if any
+    again = m.generate(prompt, max_tokens=12, temperature=0.0).tokens      # replays the older graph
+    assert again == first
+    del junk
 
 
 def test_sampled_decode_through_graphs_keeps_each_requests_generator(folder):

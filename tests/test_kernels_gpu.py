@@ -122,6 +122,29 @@ def test_gemm_tcgen05_k_slices_added_in_turn(dev, M, N, K):
     assert int(ops.gemm_scratch(dev)[1].abs().sum().item()) == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 20000, 4096), (8, 33000, 4096), (33, 20008, 4096), (64, 50000, 1024),
+                                   (8, 128256, 4096), (64, 128256, 4096)])
+def test_gemm_tcgen05_many_tiles_per_cta_few_tokens(dev, M, N, K):
+    """The output head's shape: up to 64 tokens against a vocabulary-sized weight, 32-bit logits out. With the
+    weight rows as the 128-row operand there are far more tiles (1,002 at 128,256 rows) than persistent CTAs, so
+    every CTA walks several tiles and alternates its two accumulators; a ragged last tile at N = 20,008."""
+    from cuca_b200.kernels import ops
+    g = torch.Generator(device=dev).manual_seed(M + N + K)
+    a = torch.randn(M, K, device=dev, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=dev, generator=g) / math.sqrt(K)).bfloat16()
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    for trial in range(2):  # the second launch finds the scratch as the first one left it
+        out = torch.full((M, N), float("nan"), device=dev)
+        ops.gemm_tc(a, w, out, ops.EPI_STORE, None, err)
+        torch.cuda.synchronize()
+        assert int(err.item()) == 0
+        ref = a.float() @ w.float().T
+        bad = ~torch.isclose(out, ref, atol=2e-3, rtol=2e-3)
+        assert not bool(bad.any()), (f"{int(bad.sum())} wrong logits; first at row, column "
+                                     f"{bad.nonzero()[0].tolist()} (tile {int(bad.nonzero()[0][1]) // 128})")
+    assert int(ops.gemm_scratch(dev)[1].abs().sum().item()) == 0
+
+
 def test_gemm_tcgen05_refuses_unaligned(dev):
     from cuca_b200.kernels import ops
     a = torch.zeros(4, 100, device=dev, dtype=torch.bfloat16)  # K = 100 is no multiple of 8

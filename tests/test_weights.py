@@ -36,7 +36,7 @@ def test_random_folder_is_reproducible_and_complete(tmp_path):
     cfg, w = plain_llama.load_model_dir(d1)
     assert "lm_head.weight" not in w                      # tied
     assert sum(t.numel() for t in w.values()) == 400032
-    assert torch.all(w["model.norm.weight"].float() == 1.0)
+    assert torch.all(w["model.norm.weight"].float() == 1.0)             # the default: norm weights 1.0
     q = w["model.layers.0.self_attn.q_proj.weight"].float()
     assert q.shape == (96, 96) and abs(float(q.std()) - 0.02) < 2e-3 and abs(float(q.mean())) < 2e-3
     Model(build_spec(cfg)).check_weights(FolderSource(d1))
@@ -99,3 +99,33 @@ def test_no_gpu_means_a_loud_error_not_a_fallback():
     from cuca_b200.runtime import Runtime
     with pytest.raises(KernelLibraryError, match="no CPU path"):
         Runtime("cuda:0", torch.float32)
+
+
+def test_random_values_hang_on_seed_name_and_element_only():
+    from cuca_b200.weights.loader import host_normal, tensor_key
+    key = tensor_key(7, "model.layers.0.mlp.up_proj.weight")
+    whole = host_normal(key, 0, 200_000, 0.0, 0.02)
+    piece = host_normal(key, 123_457, 1000, 0.0, 0.02)
+    assert (piece == whole[123_457:124_457]).all()                       # a piece equals that part of the whole
+    assert abs(float(whole.mean())) < 2e-4 and abs(float(whole.std()) - 0.02) < 2e-4
+    assert float(abs(whole).max()) > 3.5 * 0.02                          # tails are there
+    other = host_normal(tensor_key(7, "model.layers.1.mlp.up_proj.weight"), 0, 1000, 0.0, 0.02)
+    assert not (other == whole[:1000]).any()
+
+
+def test_switched_on_biases_are_drawn_and_norm_weights_can_differ(tmp_path):
+    """A configuration with `attention_bias` gets its eight bias tensors, non-zero; the tests' folders carry norm
+    weights that differ from 1 and from one another, so that a swapped or dropped norm weight shows in the logits."""
+    d = tiny.write_tiny(tmp_path / "c", "C")
+    _, w = plain_llama.load_model_dir(d)
+    biases = sorted(n for n in w if n.endswith(".bias"))
+    assert len(biases) == 8 and all(float(w[n].float().abs().max()) > 0.01 for n in biases)
+    norms = [w[n].float() for n in sorted(w) if "norm" in n]
+    assert len(norms) == 5
+    for i, a in enumerate(norms):
+        assert float((a - 1).abs().mean()) > 0.05
+        for b in norms[i + 1:]:
+            assert not torch.equal(a, b)
+    Model(build_spec(tiny.TINY_C)).check_weights(FolderSource(d))
+    a_cfg, a_w = plain_llama.load_model_dir(tiny.write_tiny(tmp_path / "a", "A"))
+    assert not any(n.endswith(".bias") for n in a_w)                       # no biases unless switched on

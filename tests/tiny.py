@@ -49,9 +49,11 @@ SEEDS = {"A": 0, "B": 2, "C": 9, "D": 4, "E": 11}
 CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": SMALL_D, "E": SMALL_E}
 
 
-def write_tiny(folder, which: str, dtype=torch.bfloat16, std: float = 0.02):
+def write_tiny(folder, which: str, dtype=torch.bfloat16, std: float = 0.02, norm_std: float = 0.2):
+    """Norm weights are 1 + N(0, 0.2), different in every layer: with all of them 1.0 a swapped, dropped or
+    wrongly bound norm weight would change nothing."""
     from cuca_b200.weights.random_init import write_random_model
-    return write_random_model(folder, CONFIGS[which], SEEDS[which], std=std, dtype=dtype)
+    return write_random_model(folder, CONFIGS[which], SEEDS[which], std=std, dtype=dtype, norm_std=norm_std)
 
 
 def random_tokens(n: int, vocab: int, seed: int) -> list[int]:
