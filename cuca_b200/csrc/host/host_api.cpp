@@ -112,8 +112,8 @@ static void entries_of(int n, const int* seqs, const int* slots, const int* n_to
   }
 }
 
-// Validates the batch, then packs it. meta: rows, requests, wanted, n_decode, max_len, identity, n_tiles,
-// n_tiles128, total. sizes: one per section (10 fixed, then two per group).
+// Validates the batch, then packs it. meta: rows, requests, wanted, total. sizes: one per section (8 fixed, then
+// two per group).
 HOST_API int cuca_host_step_pack(void* pools, int n, const int* seqs, const int* slots, const int* n_tokens, const int* tokens,
                                  const int* n_want, const int* want, int context_length, int vocab, int max_sequences,
                                  int table_width, int* out, int cap, int* sizes, int* meta) {
@@ -124,9 +124,20 @@ HOST_API int cuca_host_step_pack(void* pools, int n, const int* seqs, const int*
   if (st != OK) return fail(st, why);
   StepMeta m;
   st = pack_step(*(KvPools*)pools, entries, table_width, out, cap, sizes, m);
-  const int mm[9] = {m.rows, m.requests, m.wanted, m.n_decode, m.max_len, m.identity, m.n_tiles, m.n_tiles128, m.total};
+  const int mm[4] = {m.rows, m.requests, m.wanted, m.total};
   std::memcpy(meta, mm, sizeof(mm));
   return st == OK ? 0 : fail(st, "the staging buffer is too small for this step");
+}
+// Validation alone, for a step whose rows already live on the device (a captured decode step): one token per
+// request. Same refusals as cuca_host_step_pack; nothing is packed or marked.
+HOST_API int cuca_host_step_validate(void* pools, int n, const int* seqs, const int* slots, const int* n_tokens,
+                                     const int* tokens, int context_length, int vocab, int max_sequences) {
+  std::vector<StepEntryView> entries;
+  std::vector<int> none(n > 0 ? n : 1, 0);
+  entries_of(n, seqs, slots, n_tokens, tokens, none.data(), none.data(), entries);
+  std::string why;
+  const Status st = validate_step(*(KvPools*)pools, entries, context_length, vocab, max_sequences, why);
+  return st == OK ? 0 : fail(st, why);
 }
 HOST_API int cuca_host_table_updates(void* pools, const int* seqs, const int* slots, int n, int table_width, int group, int* out, int cap) {
   if (!group_ok(pools, group)) {  // -2: not the "buffer too small" answer

@@ -1,7 +1,6 @@
 #include "step_pack.hpp"
 
 #include <algorithm>
-#include <numeric>
 
 namespace cuca {
 
@@ -50,118 +49,89 @@ Status validate_step(KvPools& pools, const std::vector<StepEntryView>& entries, 
   return OK;
 }
 
+// Appends, for one group, the page-table entries of these requests that changed since they were last sent
+// (index into the device table, page id) and marks them as sent. The one routine behind both `pack_step` and
+// `table_updates`.
+static int append_table_updates(KvPools& pools, const int* seqs, const int* slots, int n, int table_width, int g,
+                                int* idx, int* val) {
+  int k = 0;
+  for (int i = 0; i < n; ++i) {
+    SeqBlocks* s = pools.seq(seqs[i]);
+    if (!s) continue;
+    const std::vector<int>& table = s->tables[g];
+    for (int j = s->dirty_from[g]; j < (int)table.size(); ++j, ++k) {
+      idx[k] = slots[i] * table_width + j;
+      val[k] = table[j];
+    }
+    s->dirty_from[g] = std::max(s->dirty_from[g], (int)table.size());
+  }
+  return k;
+}
+
+static int count_table_updates(KvPools& pools, const int* seqs, int n, int g) {
+  int count = 0;
+  for (int i = 0; i < n; ++i) {
+    SeqBlocks* s = pools.seq(seqs[i]);
+    if (s) count += std::max(0, (int)s->tables[g].size() - s->dirty_from[g]);
+  }
+  return count;
+}
+
 Status pack_step(KvPools& pools, const std::vector<StepEntryView>& entries, int table_width, int* out, int cap,
                  int* sizes, StepMeta& meta) {
   const int G = pools.n_groups();
-  int rows = 0, wanted = 0, n_decode = 0, n_tiles = 0, n_tiles128 = 0, max_len = 1;
-  std::vector<int> upd(G, 0);
-  for (const StepEntryView& e : entries) {
-    SeqBlocks* s = pools.seq(e.seq);
-    if (!s) return INVALID;
-    rows += e.n_tokens;
-    wanted += e.n_want;
-    if (e.n_tokens == 1) {
-      ++n_decode;
-      max_len = std::max(max_len, s->length + 1);
-    } else {
-      n_tiles += (e.n_tokens + 63) / 64;
-      n_tiles128 += (e.n_tokens + 127) / 128;
-    }
-    for (int g = 0; g < G; ++g) upd[g] += std::max(0, (int)s->tables[g].size() - s->dirty_from[g]);
+  const int n = (int)entries.size();
+  int rows = 0, wanted = 0;
+  std::vector<int> seqs(n), slot_list(n);
+  for (int i = 0; i < n; ++i) {
+    if (!pools.seq(entries[i].seq)) return INVALID;
+    rows += entries[i].n_tokens;
+    wanted += entries[i].n_want;
+    seqs[i] = entries[i].seq;
+    slot_list[i] = entries[i].slot;
   }
-  const bool identity = n_decode == rows;
   sizes[SEC_TOKENS] = sizes[SEC_POSITIONS] = sizes[SEC_SLOT_OF_ROW] = rows;
-  sizes[SEC_SLOTS] = (int)entries.size();
+  sizes[SEC_SLOTS] = sizes[SEC_REQ_ROW0] = sizes[SEC_REQ_COUNT] = sizes[SEC_REQ_START] = n;
   sizes[SEC_LOGIT_ROWS] = wanted;
-  sizes[SEC_DECODE_ROWS] = identity ? 0 : n_decode;
-  sizes[SEC_TILE_ROW0] = sizes[SEC_TILE_NROWS] = n_tiles;
-  sizes[SEC_TILE128_ROW0] = sizes[SEC_TILE128_NROWS] = n_tiles128;
-  for (int g = 0; g < G; ++g) sizes[SEC_FIXED + 2 * g] = sizes[SEC_FIXED + 2 * g + 1] = upd[g];
+  for (int g = 0; g < G; ++g)
+    sizes[SEC_FIXED + 2 * g] = sizes[SEC_FIXED + 2 * g + 1] = count_table_updates(pools, seqs.data(), n, g);
   const int n_sections = SEC_FIXED + 2 * G;
   int total = 0;
   std::vector<int> at(n_sections);
   for (int i = 0; i < n_sections; ++i) { at[i] = total; total += sizes[i]; }
-  meta = StepMeta{rows, (int)entries.size(), wanted, n_decode, max_len, identity ? 1 : 0, n_tiles, n_tiles128, total};
+  meta = StepMeta{rows, n, wanted, total};
   if (total > cap) return TOO_SMALL;
 
   int* tokens = out + at[SEC_TOKENS];
   int* positions = out + at[SEC_POSITIONS];
   int* slot_of_row = out + at[SEC_SLOT_OF_ROW];
-  int* slots = out + at[SEC_SLOTS];
   int* logit_rows = out + at[SEC_LOGIT_ROWS];
-  int* decode_rows = out + at[SEC_DECODE_ROWS];
-  struct Tile { int row0, n, pos; };
-  std::vector<Tile> tiles, tiles128;
-  tiles.reserve(n_tiles);
-  tiles128.reserve(n_tiles128);
-  int row = 0, w = 0, d = 0;
-  for (size_t i = 0; i < entries.size(); ++i) {
+  int row = 0, w = 0;
+  for (int i = 0; i < n; ++i) {
     const StepEntryView& e = entries[i];
-    SeqBlocks* s = pools.seq(e.seq);
-    const int start = s->length, t = e.n_tokens;
+    const int start = pools.seq(e.seq)->length, t = e.n_tokens;
     for (int k = 0; k < t; ++k) {
       tokens[row + k] = e.tokens[k];
       positions[row + k] = start + k;
       slot_of_row[row + k] = e.slot;
     }
-    slots[i] = e.slot;
+    out[at[SEC_SLOTS] + i] = e.slot;
+    out[at[SEC_REQ_ROW0] + i] = row;
+    out[at[SEC_REQ_COUNT] + i] = t;
+    out[at[SEC_REQ_START] + i] = start;
     for (int k = 0; k < e.n_want; ++k) logit_rows[w++] = row + e.want[k];
-    if (t == 1) {
-      if (!identity) decode_rows[d++] = row;
-    } else {
-      for (int off = 0; off < t; off += 64) tiles.push_back({row + off, std::min(64, t - off), start + off});
-      for (int off = 0; off < t; off += 128) tiles128.push_back({row + off, std::min(128, t - off), start + off});
-    }
     row += t;
   }
-  // heavy tiles (late positions see most keys) first; equal positions keep their order
-  auto heavy_first = [](const Tile& a, const Tile& b) { return a.pos > b.pos; };
-  std::stable_sort(tiles.begin(), tiles.end(), heavy_first);
-  std::stable_sort(tiles128.begin(), tiles128.end(), heavy_first);
-  for (int i = 0; i < n_tiles; ++i) {
-    out[at[SEC_TILE_ROW0] + i] = tiles[i].row0;
-    out[at[SEC_TILE_NROWS] + i] = tiles[i].n;
-  }
-  for (int i = 0; i < n_tiles128; ++i) {
-    out[at[SEC_TILE128_ROW0] + i] = tiles128[i].row0;
-    out[at[SEC_TILE128_NROWS] + i] = tiles128[i].n;
-  }
-  // page-table entries that changed since they were last sent
-  for (int g = 0; g < G; ++g) {
-    int* idx = out + at[SEC_FIXED + 2 * g];
-    int* val = out + at[SEC_FIXED + 2 * g + 1];
-    int n = 0;
-    for (const StepEntryView& e : entries) {
-      SeqBlocks* s = pools.seq(e.seq);
-      const std::vector<int>& table = s->tables[g];
-      for (int i = s->dirty_from[g]; i < (int)table.size(); ++i, ++n) {
-        idx[n] = e.slot * table_width + i;
-        val[n] = table[i];
-      }
-      s->dirty_from[g] = std::max(s->dirty_from[g], (int)table.size());
-    }
-  }
+  for (int g = 0; g < G; ++g)
+    append_table_updates(pools, seqs.data(), slot_list.data(), n, table_width, g, out + at[SEC_FIXED + 2 * g],
+                         out + at[SEC_FIXED + 2 * g + 1]);
   return OK;
 }
 
 int table_updates(KvPools& pools, const int* seqs, const int* slots, int n, int table_width, int group, int* out, int cap) {
-  int count = 0;
-  for (int i = 0; i < n; ++i) {
-    SeqBlocks* s = pools.seq(seqs[i]);
-    if (s) count += std::max(0, (int)s->tables[group].size() - s->dirty_from[group]);
-  }
+  const int count = count_table_updates(pools, seqs, n, group);
   if (2 * count > cap) return -1;
-  int k = 0;
-  for (int i = 0; i < n; ++i) {
-    SeqBlocks* s = pools.seq(seqs[i]);
-    if (!s) continue;
-    const std::vector<int>& table = s->tables[group];
-    for (int j = s->dirty_from[group]; j < (int)table.size(); ++j, ++k) {
-      out[k] = slots[i] * table_width + j;
-      out[count + k] = table[j];
-    }
-    s->dirty_from[group] = std::max(s->dirty_from[group], (int)table.size());
-  }
+  append_table_updates(pools, seqs, slots, n, table_width, group, out, out + count);
   return count;
 }
 

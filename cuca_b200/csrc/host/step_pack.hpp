@@ -17,15 +17,18 @@ struct StepEntryView {
   int n_want;
 };
 
-// Sections of the packed buffer, in order; `sizes` of pack_step has one entry per section.
+// Sections of the packed buffer, in order; `sizes` of pack_step has one entry per section. Per row: its token,
+// position and request slot. Per request, in the order given: its slot, the row its tokens start at, how many
+// tokens it brings and how many positions it had cached before. How the rows are handed to kernels (tiles,
+// lists of single-token rows, scans) is not decided here: every mixer plans that for itself from the
+// per-request sections.
 enum Section {
-  SEC_TOKENS = 0, SEC_POSITIONS, SEC_SLOT_OF_ROW, SEC_SLOTS, SEC_LOGIT_ROWS, SEC_DECODE_ROWS,
-  SEC_TILE_ROW0, SEC_TILE_NROWS, SEC_TILE128_ROW0, SEC_TILE128_NROWS,
+  SEC_TOKENS = 0, SEC_POSITIONS, SEC_SLOT_OF_ROW, SEC_SLOTS, SEC_LOGIT_ROWS, SEC_REQ_ROW0, SEC_REQ_COUNT, SEC_REQ_START,
   SEC_FIXED  // then, per group: indices into the device page table, and the page ids that go there
 };
 
 struct StepMeta {
-  int rows, requests, wanted, n_decode, max_len, identity, n_tiles, n_tiles128, total;
+  int rows, requests, wanted, total;
 };
 
 // Empty batch, empty token list, context overflow, token id out of range, missing or returned pages, wanted
@@ -34,10 +37,8 @@ struct StepMeta {
 Status validate_step(KvPools& pools, const std::vector<StepEntryView>& entries, int context_length, int vocab,
                      int max_sequences, std::string& error);
 
-// Packs the step into `out` (capacity `cap` integers). Single-token requests are decode rows; longer portions are
-// cut into tiles of 64 and of 128 rows, heaviest (latest positions) first. Page-table entries that changed since
-// they were last sent are appended per group and marked as sent. TOO_SMALL: meta.total says what is needed and
-// nothing was marked.
+// Packs the step into `out` (capacity `cap` integers). Page-table entries that changed since they were last sent
+// are appended per group and marked as sent. TOO_SMALL: meta.total says what is needed and nothing was marked.
 Status pack_step(KvPools& pools, const std::vector<StepEntryView>& entries, int table_width, int* out, int cap,
                  int* sizes, StepMeta& meta);
 

@@ -94,14 +94,12 @@ class Model:
     def forward(self, step, cache) -> torch.Tensor | None:
         """Run the step's rows through the model; logits [wanted rows, vocab] in 32-bit, or None."""
         x = torch.empty(step.n_rows, self.spec.width, dtype=torch.float32, device=self.rt.device)
-        self.rt.pending.clear()
         self.embedding.forward(step.tokens, x)
+        stream = self.rt.stream(x)
         for run in self.spec.schedule:
-            self.blocks[run.layer].forward(x, step, cache.view(run.cache, step))
+            self.blocks[run.layer].forward(stream, step, cache.view(run.cache, step))
         if step.logit_rows is None or step.n_logit_rows == 0:
-            self.rt.pending.clear()
+            stream.drop_pending()
             return None
-        if not getattr(self.final_norm, "consumes_partials", False):
-            self.rt.flush(x)
-        h = self.final_norm.forward(x, rows=step.logit_rows)
+        h = self.final_norm.forward(stream, rows=step.logit_rows)
         return self.head.forward(h)

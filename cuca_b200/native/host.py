@@ -88,6 +88,7 @@ _SIGNATURES = {
     "cuca_host_slots_release": (_I, [_P, _I]), "cuca_host_slots_free_count": (_I, [_P]),
     "cuca_host_slots_reset": (None, [_P]),
     "cuca_host_step_pack": (_I, [_P, _I, _IP, _IP, _IP, _IP, _IP, _IP, _I, _I, _I, _I, _P, _I, _IP, _IP]),
+    "cuca_host_step_validate": (_I, [_P, _I, _IP, _IP, _IP, _IP, _I, _I, _I]),
     "cuca_host_table_updates": (_I, [_P, _IP, _IP, _I, _I, _I, _P, _I]),
     "cuca_host_step_advance": (_I, [_P, _IP, _IP, _I]),
     "cuca_host_sched_new": (_P, [_P, _P, _I, _I, _I, _I, _IP, _I, _I]), "cuca_host_sched_free": (None, [_P]),

@@ -84,6 +84,7 @@ class PagedAttention(Mixer):
 
     # ------------------------------------------------------------ step
     def forward(self, h, stream, step, cache) -> None:
+        stream = self.rt.stream(stream)
         nh, d = self.n_heads, self.head_dim
         nkv = 0 if self.shares_cache else self.n_kv_heads
         fused = self.position.fused_tables() if self.position is not None else None
@@ -101,7 +102,7 @@ class PagedAttention(Mixer):
                                            step.positions, step.seq_of_row, cache.tables, plan.decode_rows,
                                            plan.n_decode, nh, self.n_kv_heads, d, self.scale, self.window, chunk,
                                            n_splits, self.rt.err)
-                self.rt.linear_into_stream(attn, self.w_o, stream, bias=self.b_o)
+                stream.add_linear(attn, self.w_o, bias=self.b_o)
                 return
             q = self.rt.empty(h.shape[0], nh * d)
             ops.rope_store_partial(parts, self.b_qkv, q, step.positions, step.seq_of_row, cache.tables, cos, sin, rot,
@@ -119,4 +120,4 @@ class PagedAttention(Mixer):
                            cache.block_size, nh, nkv, d, self.rt.err)
         attn = self.rt.empty(h.shape[0], nh * d)
         ops.attention(q, attn, cache, step, nh, self.n_kv_heads, d, self.scale, self.window, self.rt.err)
-        self.rt.linear_into_stream(attn, self.w_o, stream, bias=self.b_o)
+        stream.add_linear(attn, self.w_o, bias=self.b_o)

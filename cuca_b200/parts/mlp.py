@@ -37,4 +37,4 @@ class SwiGLU(FeedForward):
 
     def forward(self, h, stream, step) -> None:
         act = self.rt.linear(h, self.w_gate_up, epilogue=ops.EPI_SWIGLU)
-        self.rt.linear_into_stream(act, self.w_down, stream)
+        self.rt.stream(stream).add_linear(act, self.w_down)

@@ -25,12 +25,11 @@ class RMSNorm(Norm):
     def weight_bytes(self):
         return self.weight.numel() * self.weight.element_size()
 
-    consumes_partials = True  # adds the K slices a contraction left on the stream while it reads the stream
-
-    def forward(self, x, rows=None):
+    def forward(self, stream, rows=None):
+        # this kernel adds the K slices a contraction left on the stream while it reads the stream
+        x, pending = self.rt.stream(stream).take()
         n = x.shape[0] if rows is None else rows.shape[0]
         out = self.rt.empty(n, self.width)
-        pending = self.rt.take_pending(x)
         if pending is not None:
             ops.add_partials_rmsnorm(x, pending, self.weight, out, self.eps, rows)
         else:

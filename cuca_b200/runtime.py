@@ -34,9 +34,7 @@ class Runtime:
         library.load()
         torch.cuda.set_device(self.device)
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
-        # residual streams whose last contraction left its K slices unadded (decode): stream address -> PartialSums
-        self.pending: dict = {}
-        self.use_partials = True
+        self.use_partials = True  # few-token contractions may leave their K slices unadded for the next reader
 
     # ---------------------------------------------------------------- helpers
     def empty(self, *shape, dtype=None) -> torch.Tensor:
@@ -50,26 +48,9 @@ class Runtime:
         ops.gemm(a, w, out, epilogue, bias, self.err)
         return out
 
-    # ---------------------------------------------------------------- partial sums on the residual stream
-    def linear_into_stream(self, a, w, stream, bias=None) -> None:
-        """stream += a @ w.T. Over few tokens the contraction is cut along K over the SMs and leaves its slices
-        unadded; the next reader of the stream (a norm) adds them while it reads, which spares the contraction a
-        second pass through memory at its end. `take_pending` / `flush` hand the slices over."""
-        if self.use_partials and bias is None and ops.gemm_partial_supported(a, w):
-            if stream.data_ptr() in self.pending:
-                self.flush(stream)
-            self.pending[stream.data_ptr()] = ops.gemm_partial(a, w, self.err)
-        else:
-            ops.gemm(a, w, stream, ops.EPI_RESIDUAL, bias, self.err)
-
-    def take_pending(self, stream):
-        return self.pending.pop(stream.data_ptr(), None)
-
-    def flush(self, stream) -> None:
-        """Add pending slices into the stream now (for a reader that does not add them itself)."""
-        ps = self.pending.pop(stream.data_ptr(), None)
-        if ps is not None:
-            ops.add_partials(stream, ps)
+    def stream(self, x) -> "ResidualStream":
+        """`x` as a residual stream: itself if it is one already, else a 32-bit tensor wrapped."""
+        return x if isinstance(x, ResidualStream) else ResidualStream(self, x)
 
     def check_device_errors(self) -> None:
         """Read the error word (synchronises); raise if a kernel recorded a fault."""
@@ -82,3 +63,56 @@ class Runtime:
         word and raise."""
         self.err.zero_()
         raise DeviceFault(_ERR_TEXT.get(code, f"device error {code}"))
+
+
+class ResidualStream:
+    """The 32-bit residual stream of a step, `[rows, width]`, as blocks and parts get it.
+
+    Over few tokens a contraction into the stream is cut along K over the SMs and leaves its slices unadded
+    (`add_linear`); whoever reads the stream next adds them. That hand-over is this object's business, not the
+    parts': `data` adds pending slices before it returns the tensor, so a part written against `data` (read it,
+    update it in place) is always right. A reader that can add the slices while it reads, in the same pass over
+    memory (the RMSNorm kernel), asks for `take()` instead and gets the tensor and the slices."""
+
+    def __init__(self, runtime: Runtime, tensor: torch.Tensor):
+        if tensor.dtype != torch.float32:
+            raise ValueError("the residual stream is 32-bit in every mode")
+        self.rt = runtime
+        self._tensor = tensor
+        self._pending = None
+
+    @property
+    def shape(self):
+        return self._tensor.shape
+
+    @property
+    def data(self) -> torch.Tensor:
+        """The stream's tensor with everything added; it may be read and updated in place."""
+        if self._pending is not None:
+            ps, self._pending = self._pending, None
+            ops.add_partials(self._tensor, ps)
+        return self._tensor
+
+    def take(self):
+        """(tensor, pending slices or None) for a reader that adds the slices itself, in the stream too: after
+        the reader's kernel the tensor must hold the sum."""
+        ps, self._pending = self._pending, None
+        return self._tensor, ps
+
+    def add_linear(self, a, w, bias=None) -> None:
+        """stream += a @ w.T (+ bias). Over few tokens the slices may stay pending until the next reader."""
+        rt = self.rt
+        if rt.use_partials and bias is None and ops.gemm_partial_supported(a, w):
+            x = self.data  # slices of an earlier contraction go in first
+            self._pending = ops.gemm_partial(a, w, rt.err)
+            assert x is self._tensor
+        else:
+            ops.gemm(a, w, self.data, ops.EPI_RESIDUAL, bias, rt.err)
+
+    def add(self, delta: torch.Tensor) -> None:
+        """stream += delta (any float dtype, same shape)."""
+        self.data.add_(delta)
+
+    def drop_pending(self) -> None:
+        """Forget unadded slices: the stream will not be read again (no logits are wanted)."""
+        self._pending = None

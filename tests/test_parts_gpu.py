@@ -48,7 +48,7 @@ def _register_toy_parts():
                 cs = torch.cumsum(h[r:r + count].float(), 0) + cache.state[slot]
                 cache.state[slot] = cs[-1]
                 # 64-bit products: torch's 32-bit matmul may run in a reduced-precision tensor-core mode
-                stream[r:r + count] += (cs.double() @ self.w.double().T).float()
+                stream.data[r:r + count] += (cs.double() @ self.w.double().T).float()
                 r += count
 
     @register_feed_forward("toy_routed")
@@ -80,7 +80,7 @@ def _register_toy_parts():
                 rows = (choice == e).nonzero().flatten()
                 if rows.numel():
                     y = torch.relu(x[rows] @ self.up[e].double().T) @ self.down[e].double().T
-                    stream.index_add_(0, rows, y.float())
+                    stream.data.index_add_(0, rows, y.float())
 
     @register_position("toy_adjacent_rope")
     class AdjacentRope(PositionEncoding):
@@ -274,6 +274,133 @@ def test_toy_architecture_is_registered_built_and_stepped(dtype):
     finish("c")
     core.pools.check()
     assert all(p.free == p.n_blocks for p in core.pools.pools)
+
+
+# ------------------------------------------------------------------------------------------ other arrangements
+def _register_parallel_parts():
+    from cuca_b200.config.registry import register_architecture
+    from cuca_b200.models.spec import LayerSpec, ModelSpec, default_schedule
+    from cuca_b200.parts.base import BLOCKS, Block, Mixer, PartSpec, TensorNeed, register_block, register_mixer
+    if "toy_parallel" in BLOCKS:
+        return
+
+    @register_block("toy_parallel")
+    class ParallelBlock(Block):
+        """x += mixer(n) + ffn(n) with one norm n = norm(x): both branches add into the stream one after the other,
+        neither reads what the other added."""
+
+        def forward(self, stream, step, cache):
+            h = self.mixer_norm.forward(stream)
+            self.mixer.forward(h, stream, step, cache)
+            self.feed_forward.forward(h, stream, step)
+
+    @register_mixer("toy_stream_reader")
+    class StreamReader(Mixer):
+        """y = (h W^T) * mean|x| of the row's residual stream: a mixer that reads the stream itself."""
+
+        def tensors(self):
+            E = self.spec.params["width"]
+            return {self.spec.tensors["w"]: TensorNeed((E, E))}
+
+        def load(self, get):
+            self.w = get(self.spec.tensors["w"])
+
+        def forward(self, h, stream, step, cache):
+            x = stream.data
+            y = (h.double() @ self.w.double().T) * x.double().abs().mean(-1, keepdim=True)
+            stream.add(y.float())
+
+    @register_architecture("ToyParallelForCausalLM")
+    def build(cfg):
+        E, d, nh, nkv, V = cfg["width"], cfg["head_dim"], cfg["heads"], cfg["kv_heads"], cfg["vocab"]
+        rope = PartSpec("rope", {"head_dim": d, "rotary_dim": d, "theta": 10000.0, "scaling": {"kind": "default"}})
+
+        def norm(name):
+            return PartSpec("rmsnorm", {"width": E, "eps": cfg["eps"]}, {"weight": name})
+
+        def attn(i):
+            return PartSpec("attention", {"width": E, "n_heads": nh, "n_kv_heads": nkv, "head_dim": d, "window": None,
+                                          "scale": None, "position": rope},
+                            {"q": f"l{i}.q", "o": f"l{i}.o", "k": f"l{i}.k", "v": f"l{i}.v"})
+
+        def swiglu(i):
+            return PartSpec("swiglu", {"width": E, "inner": cfg["inner"]},
+                            {"gate": f"l{i}.gate", "up": f"l{i}.up", "down": f"l{i}.down"})
+
+        layers = [LayerSpec(PartSpec("pre_norm"), attn(0), norm("l0.n1"), swiglu(0), norm("l0.n2")),
+                  LayerSpec(PartSpec("toy_parallel"), attn(1), norm("l1.n1"), swiglu(1), None),
+                  LayerSpec(PartSpec("pre_norm"), PartSpec("toy_stream_reader", {"width": E}, {"w": "l2.w"}),
+                            norm("l2.n1"), swiglu(2), norm("l2.n2"))]
+        return ModelSpec("ToyParallelForCausalLM", V, E, cfg["max_positions"],
+                         PartSpec("embedding", {"vocab": V, "width": E}, {"weight": "embed"}), layers,
+                         default_schedule(3), norm("final"), PartSpec("head", {"vocab": V, "width": E}, {"weight": "out"}))
+
+
+PAR = {"architectures": ["ToyParallelForCausalLM"], "width": 128, "head_dim": 64, "heads": 2, "kv_heads": 1,
+       "vocab": 211, "inner": 192, "eps": 1e-5, "max_positions": 256}
+
+
+def _parallel_reference(w, tokens):
+    c = PAR
+    E, d, nh, nkv = c["width"], c["head_dim"], c["heads"], c["kv_heads"]
+    t = len(tokens)
+    f = {k: v.float() for k, v in w.items()}
+    cos, sin = plain_llama.rope_tables(t, d, 10000.0, None)
+
+    def attn(i, h):
+        q = plain_llama.rotate_half_split((h @ f[f"l{i}.q"].T).view(t, nh, d), cos, sin)
+        k = plain_llama.rotate_half_split((h @ f[f"l{i}.k"].T).view(t, nkv, d), cos, sin)
+        v = (h @ f[f"l{i}.v"].T).view(t, nkv, d)
+        return plain_llama.causal_attention(q, k, v, 1.0 / math.sqrt(d)).reshape(t, nh * d) @ f[f"l{i}.o"].T
+
+    def ffn(i, h):
+        return plain_llama.swiglu(h, f[f"l{i}.gate"], f[f"l{i}.up"], f[f"l{i}.down"])
+
+    x = f["embed"][torch.tensor(tokens)]
+    x = x + attn(0, plain_llama.rms_norm(x, f["l0.n1"], c["eps"]))
+    x = x + ffn(0, plain_llama.rms_norm(x, f["l0.n2"], c["eps"]))
+    h = plain_llama.rms_norm(x, f["l1.n1"], c["eps"])
+    x = x + attn(1, h) + ffn(1, h)
+    h = plain_llama.rms_norm(x, f["l2.n1"], c["eps"])
+    x = x + (h @ f["l2.w"].T) * x.abs().mean(-1, keepdim=True)
+    x = x + ffn(2, plain_llama.rms_norm(x, f["l2.n2"], c["eps"]))
+    return plain_llama.rms_norm(x, f["final"], c["eps"]) @ f["out"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_parallel_block_and_a_mixer_that_reads_the_stream(dtype):
+    """Other arrangements written against the documented interface only: a parallel-residual block (two
+    contractions add into the stream back to back) and a mixer that reads the stream itself. In bfloat16 with up to
+    64 rows a contraction into the stream leaves its K slices unadded; the stream object hands them to whoever
+    reads next, so these parts see the full sum without knowing about slices."""
+    _register_parallel_parts()
+    from cuca_b200.config.registry import build_spec
+    from cuca_b200.engine.core import EngineCore
+    from cuca_b200.engine.step import StepEntry
+    from cuca_b200.models.model import Model
+    from cuca_b200.weights.loader import RandomSource
+    spec = build_spec(PAR)
+    needs = Model(spec).tensor_needs()
+    assert "l1.n2" not in needs
+    source = RandomSource(needs, seed=3, std=0.06, device="cpu", dtype=torch.bfloat16, norm_std=0.2)
+    weights = {n: source.read(n) for n in source.shapes()}
+    core = EngineCore(spec, source, dtype=dtype, kv_tokens=256, max_sequences=2, block_size=16)
+    if dtype == "bfloat16":
+        from cuca_b200.kernels import ops
+        probe = torch.zeros(8, PAR["width"], dtype=torch.bfloat16, device="cuda:0")
+        assert ops.gemm_partial_supported(probe, core.model.blocks[0].mixer.w_o), "the case must leave slices unadded"
+    tokens = tiny.random_tokens(60, PAR["vocab"], seed=8)
+    ref = _parallel_reference(weights, tokens)
+    tol = 3e-5 if dtype == "float32" else 4e-2
+    blocks, slot, pos = core.pools.new_seq(), core.slots.alloc(), 0
+    for n in (40, 1, 1, 5, 1, 12):
+        core.pools.reserve(blocks, pos + n)
+        logits = core.stepper.step([StepEntry(blocks, slot, tokens[pos:pos + n], list(range(n)))]).float().cpu()
+        want = ref[pos:pos + n]
+        err = float((logits - want).abs().max() / want.abs().max())
+        assert err < tol, (pos, n, err)
+        pos += n
+    core.rt.check_device_errors()
 
 
 # ------------------------------------------------------------------------------------------ built-in parts alone

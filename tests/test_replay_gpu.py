@@ -159,3 +159,41 @@ def test_a_far_key_among_hundreds_is_found_after_cuts(tmp_path_factory, dtype):
     for steps in (ru.trace_portions(reqs, sizes=(100, 2, 60, 7, 64, 3, 2, 2)), ru.trace_tail_one_by_one(reqs)):
         got = ru.run_in_process(d, dtype, steps, 256)
         ru.compare(steps, got, reqs, ru.Oracle(d), TOL[dtype])
+
+
+@pytest.mark.parametrize("which", ["B", "D"])
+def test_fp32_a_row_beside_neighbours_equals_the_row_alone_to_the_bit(models, which):
+    """The exactness contract at the step level (the reference's `check_batched`,
+    src/provider/local/model/cpu.rs:4072-4141): three requests over five steps, mixing a joint prefill, single
+    tokens, a request that sits a step out and a four-token portion beside single tokens. In 32-bit every logit of
+    every step equals, bit for bit, what the same request gives when it runs alone and whole."""
+    import numpy as np
+    vocab = tiny.CONFIGS[which]["vocab_size"]
+    reqs = {"a": tiny.random_tokens(9, vocab, seed=41), "b": tiny.random_tokens(14, vocab, seed=42),
+            "c": tiny.random_tokens(8, vocab, seed=43)}
+
+    def ent(rid, lo, hi):
+        return {"id": rid, "tokens": reqs[rid][lo:hi], "want": list(range(hi - lo))}
+
+    steps = [
+        {"step": 0, "entries": [ent("a", 0, 5), ent("b", 0, 9), ent("c", 0, 2)], "end": []},
+        {"step": 1, "entries": [ent("a", 5, 6), ent("b", 9, 10), ent("c", 2, 3)], "end": []},
+        {"step": 2, "entries": [ent("a", 6, 7), ent("c", 3, 7)], "end": []},            # b sits out
+        {"step": 3, "entries": [ent("c", 7, 8), ent("b", 10, 11), ent("a", 7, 8)], "end": ["c"]},
+        {"step": 4, "entries": [ent("b", 11, 14), ent("a", 8, 9)], "end": ["a", "b"]},
+    ]
+    got = ru.run_in_process(models[which], "float32", steps, ru.peak_tokens(steps))
+    alone = {}
+    for rid, toks in reqs.items():
+        whole = ru.trace_whole({rid: toks})
+        alone[rid] = ru.run_in_process(models[which], "float32", whole, 64)[0]
+    pos = {rid: 0 for rid in reqs}
+    for s in steps:
+        row = 0
+        for e in s["entries"]:
+            for w in e["want"]:
+                p = pos[e["id"]] + w
+                assert np.array_equal(got[s["step"]][row], alone[e["id"]][p]), \
+                    f"step {s['step']}, request {e['id']}, position {p}: not the bits of the request alone"
+                row += 1
+            pos[e["id"]] += len(e["tokens"])
