@@ -27,6 +27,10 @@ class PoolExhausted(RuntimeError):
     """No free page is left in a group's pool."""
 
 
+class StatefulCacheError(ValueError):
+    """Asked of pages what only works when pages are all a request keeps: some mixer also keeps state."""
+
+
 class CacheBookkeepingError(AssertionError):
     """A page was freed twice, is held twice, or got lost."""
 
@@ -218,6 +222,9 @@ class KvPools:
         if not self._h:
             raise ValueError("the page pools could not be made")
         self.pools = [_GroupPool(self, gi) for gi in range(self.n_groups)]
+        # True when some mixer of the model keeps per-request state of fixed size besides these pages: what
+        # rests on "the pages are all a request has" (rolling back, starting from cached pages) is refused then
+        self.stateful = False
 
     def __del__(self):
         if getattr(self, "_h", None):
@@ -278,7 +285,11 @@ class KvPools:
         return n
 
     def truncate(self, seq: SeqBlocks, length: int) -> None:
-        """Roll the request back to `length` positions, giving back the pages beyond."""
+        """Roll the request back to `length` positions, giving back the pages beyond. Refused when some mixer
+        keeps per-request state of fixed size: pages can be cut back, a running state cannot."""
+        if self.stateful:
+            raise StatefulCacheError("a request cannot be rolled back: a mixer of this model keeps per-request state "
+                            "besides its pages, and that state has moved on")
         code = self._lib.cuca_host_pools_truncate(self._h, seq.handle, int(length))
         if code:
             _raise(code)

@@ -615,6 +615,9 @@ int cuca_device_sms() {
   return sms;
 }
 
+// How many SMs the current device has (the Python side sizes its split choices by it too).
+CUCA_API int cuca_sm_count() { return cuca_device_sms(); }
+
 namespace {
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,

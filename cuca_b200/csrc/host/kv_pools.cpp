@@ -1,11 +1,11 @@
 #include "kv_pools.hpp"
 
 #include <algorithm>
-#include <set>
 
 namespace cuca {
 
-// FNV-1a over the previous hash and the ids of one page (src/provider/local/model/paged.rs:257-272).
+// FNV-1a over the previous page's hash (eight bytes, low first) and then the ids of the page (four bytes each,
+// low first): the hash the reference names its pages by (src/provider/local/model/paged.rs:257-272).
 uint64_t chain_hash(uint64_t prev, const int* ids, int n) {
   const uint64_t prime = 0x00000100000001b3ull;
   uint64_t h = 0xcbf29ce484222325ull;
@@ -18,85 +18,148 @@ uint64_t chain_hash(uint64_t prev, const int* ids, int n) {
 }
 
 // ------------------------------------------------------------------ BlockPool
-BlockPool::BlockPool(int n_blocks) : refcount_(n_blocks > 0 ? n_blocks : 0, 0) { reset(); }
+BlockPool::BlockPool(int n_blocks) : refs_(n_blocks > 0 ? n_blocks : 0, 0) { reset(); }
 
 void BlockPool::reset() {
-  const int n = (int)refcount_.size();
-  free_.resize(n);
-  for (int i = 0; i < n; ++i) free_[i] = n - 1 - i;  // page 0 is handed out first
-  std::fill(refcount_.begin(), refcount_.end(), 0);
+  const int n = n_blocks();
+  std::fill(refs_.begin(), refs_.end(), 0);
   named_.assign(n, 0);
-  key_.assign(n, BlockKey());
-  lru_.clear();
-  stamp_.assign(n, 0);
-  next_stamp_ = 1;
-  cached_ = 0;
-  by_hash_.clear();
+  link_.assign(n, -1);
+  back_.assign(n, -1);
+  hash_.assign(n, 0);
+  parent_.assign(n, 0);
+  ids_.assign(n, {});
+  size_t cap = 8;
+  while (cap < 2 * (size_t)n) cap <<= 1;  // at most half full, so probes stay short
+  table_.assign(cap, -1);
+  free_top_ = -1;
+  for (int b = n - 1; b >= 0; --b) { link_[b] = free_top_; free_top_ = b; }  // page 0 on top
+  n_free_ = n;
+  oldest_ = newest_ = -1;
+  n_cached_ = 0;
+}
+
+size_t BlockPool::slot_of(uint64_t hash, uint64_t parent) const {
+  uint64_t x = hash ^ (parent * 0x9E3779B97F4A7C15ull);
+  x ^= x >> 29;
+  return (size_t)x & (table_.size() - 1);
+}
+
+int BlockPool::find(const PageName& name) const {
+  for (size_t i = slot_of(name.hash, name.parent);; i = (i + 1) & (table_.size() - 1)) {
+    const int b = table_[i];
+    if (b < 0) return -1;
+    if (hash_[b] == name.hash && parent_[b] == name.parent) {
+      const std::vector<int>& ids = ids_[b];
+      if ((int)ids.size() == name.n_ids && std::equal(ids.begin(), ids.end(), name.ids)) return b;
+      return -1;  // same hashes, other tokens: the name belongs to the page that took it first
+    }
+  }
+}
+
+// Takes the page's entry out of the name table, closing the gap so that later entries of the same run of probes
+// stay reachable (backward-shift deletion: no tombstones).
+void BlockPool::forget_name(int b) {
+  const size_t mask = table_.size() - 1;
+  size_t i = slot_of(hash_[b], parent_[b]);
+  while (table_[i] != b) {
+    if (table_[i] < 0) { named_[b] = 0; ids_[b].clear(); return; }  // (not reachable: a named page is in the table)
+    i = (i + 1) & mask;
+  }
+  size_t hole = i;
+  for (size_t j = (i + 1) & mask; table_[j] >= 0; j = (j + 1) & mask) {
+    const size_t home = slot_of(hash_[table_[j]], parent_[table_[j]]);
+    // entry j may move into the hole unless its home lies cyclically in (hole, j]
+    const bool stays = hole <= j ? (home > hole && home <= j) : (home > hole || home <= j);
+    if (!stays) { table_[hole] = table_[j]; hole = j; }
+  }
+  table_[hole] = -1;
+  named_[b] = 0;
+  ids_[b].clear();
+}
+
+void BlockPool::unlink_cached(int b) {
+  const int older = back_[b], newer = link_[b];
+  if (older >= 0) link_[older] = newer; else oldest_ = newer;
+  if (newer >= 0) back_[newer] = older; else newest_ = older;
+  link_[b] = back_[b] = -1;
+  --n_cached_;
 }
 
 int BlockPool::alloc() {
-  if (!free_.empty()) {
-    const int b = free_.back();
-    free_.pop_back();
-    if (refcount_[b] != 0) return -2;
-    refcount_[b] = 1;
-    return b;
+  int b;
+  if (free_top_ >= 0) {
+    b = free_top_;
+    if (refs_[b] != 0 || named_[b]) return -2;  // a held or cached page on the free stack: the books are wrong
+    free_top_ = link_[b];
+    link_[b] = -1;
+    --n_free_;
+  } else if (oldest_ >= 0) {
+    b = oldest_;
+    unlink_cached(b);
+    forget_name(b);  // whoever gets the page writes new tokens into it
+  } else {
+    return -1;
   }
-  while (!lru_.empty()) {
-    const std::pair<int, uint64_t> e = lru_.front();
-    lru_.pop_front();
-    const int b = e.first;
-    if (stamp_[b] != e.second) continue;  // a stale entry: the page was taken out of the cache meanwhile
-    stamp_[b] = 0;
-    --cached_;
-    if (named_[b]) {
-      auto it = by_hash_.find(key_[b].hash);
-      if (it != by_hash_.end() && it->second == b) by_hash_.erase(it);
-      named_[b] = 0;
-      key_[b] = BlockKey();
-    }
-    refcount_[b] = 1;
-    return b;
-  }
-  return -1;
+  refs_[b] = 1;
+  return b;
 }
 
 bool BlockPool::release(int b) {
-  if (b < 0 || b >= (int)refcount_.size() || refcount_[b] == 0) return false;
-  if (--refcount_[b] > 0) return true;
-  if (named_[b]) {
-    stamp_[b] = next_stamp_;
-    lru_.emplace_back(b, next_stamp_);
-    ++next_stamp_;
-    ++cached_;
+  if (b < 0 || b >= n_blocks() || refs_[b] == 0) return false;
+  if (--refs_[b] > 0) return true;
+  if (named_[b]) {  // keeps its tokens and its name until an allocation needs the page
+    back_[b] = newest_;
+    link_[b] = -1;
+    if (newest_ >= 0) link_[newest_] = b; else oldest_ = b;
+    newest_ = b;
+    ++n_cached_;
   } else {
-    free_.push_back(b);
+    link_[b] = free_top_;
+    free_top_ = b;
+    ++n_free_;
   }
   return true;
 }
 
-bool BlockPool::register_key(int b, const BlockKey& key) {
-  if (b < 0 || b >= (int)refcount_.size() || refcount_[b] == 0 || named_[b] || by_hash_.count(key.hash)) return false;
+bool BlockPool::give_name(int b, const PageName& name) {
+  if (b < 0 || b >= n_blocks() || refs_[b] == 0 || named_[b]) return false;
+  const size_t mask = table_.size() - 1;
+  size_t i = slot_of(name.hash, name.parent);
+  for (; table_[i] >= 0; i = (i + 1) & mask)
+    if (hash_[table_[i]] == name.hash && parent_[table_[i]] == name.parent) return false;  // the name is taken
+  table_[i] = b;
+  hash_[b] = name.hash;
+  parent_[b] = name.parent;
+  ids_[b].assign(name.ids, name.ids + name.n_ids);
   named_[b] = 1;
-  key_[b] = key;
-  by_hash_[key.hash] = b;
   return true;
 }
 
-bool BlockPool::holds(const BlockKey& key) const {
-  auto it = by_hash_.find(key.hash);
-  return it != by_hash_.end() && named_[it->second] && key_[it->second] == key;
+int BlockPool::take(const PageName& name) {
+  const int b = find(name);
+  if (b < 0) return -1;
+  if (refs_[b] == 0) unlink_cached(b);
+  ++refs_[b];
+  return b;
 }
 
-int BlockPool::lookup(const BlockKey& key) {
-  if (!holds(key)) return -1;
-  const int b = by_hash_[key.hash];
-  if (refcount_[b] == 0) {  // out of the cache
-    stamp_[b] = 0;
-    --cached_;
+bool BlockPool::walk_free(std::vector<int>& seen) const {
+  int steps = 0;
+  for (int b = free_top_; b >= 0; b = link_[b]) {
+    if (++steps > n_blocks() || !is_free(b)) return false;
+    ++seen[b];
   }
-  ++refcount_[b];
-  return b;
+  return steps == n_free_;
+}
+
+bool BlockPool::walk_cached(std::vector<int>& seen) const {
+  int steps = 0, prev = -1;
+  for (int b = oldest_; b >= 0; prev = b, b = link_[b]) {
+    if (++steps > n_blocks() || !is_cached(b) || back_[b] != prev) return false;
+    ++seen[b];
+  }
+  return steps == n_cached_ && prev == newest_;
 }
 
 // ------------------------------------------------------------------ KvPools
@@ -246,23 +309,42 @@ void KvPools::reset() {
   live_ = 0;
 }
 
+// The names of a token sequence's whole pages, one after the other: each page's hash chains from the one before.
+namespace {
+struct NameWalker {
+  const int* ids;
+  int page_tokens;
+  uint64_t prev = 0;
+  int index = 0;
+  PageName next() {
+    PageName nm;
+    nm.parent = prev;
+    nm.ids = ids + (size_t)index * page_tokens;
+    nm.n_ids = page_tokens;
+    nm.hash = chain_hash(prev, nm.ids, page_tokens);
+    prev = nm.hash;
+    ++index;
+    return nm;
+  }
+};
+}  // namespace
+
 Status KvPools::publish(int handle, const int* ids, int n) {
   SeqBlocks* s = seq(handle);
   if (!s || s->released) return fail(BOOKKEEPING, "publish on a request without pages");
-  const int full = std::min(s->length, n) / block_size_;
-  while ((int)s->chain.size() < full) {
-    const int i = (int)s->chain.size();
-    s->chain.push_back(chain_hash(i ? s->chain[i - 1] : 0, ids + (size_t)i * block_size_, block_size_));
-  }
-  for (size_t g = 0; g < groups_.size(); ++g) {
-    const std::vector<int>& table = s->tables[g];
-    for (int i = 0; i < (int)table.size() && i < (int)s->chain.size(); ++i) {
-      if (table[i] == NO_BLOCK || pools_[g].is_named(table[i])) continue;
-      BlockKey key;
-      key.hash = s->chain[i];
-      key.parent = i ? s->chain[i - 1] : 0;
-      key.ids.assign(ids + (size_t)i * block_size_, ids + (size_t)(i + 1) * block_size_);
-      pools_[g].register_key(table[i], key);
+  const int whole = std::min(s->length, n) / block_size_;  // pages that are full and whose tokens are known
+  NameWalker walk{ids, block_size_};
+  for (int i = 0; i < whole; ++i) {
+    if (i < (int)s->chain.size()) {  // named at an earlier call: only move the walker on
+      walk.prev = s->chain[i];
+      walk.index = i + 1;
+      continue;
+    }
+    const PageName nm = walk.next();
+    s->chain.push_back(nm.hash);
+    for (size_t g = 0; g < groups_.size(); ++g) {
+      const std::vector<int>& table = s->tables[g];
+      if (i < (int)table.size() && table[i] != NO_BLOCK) pools_[g].give_name(table[i], nm);  // refused if taken
     }
   }
   return OK;
@@ -270,89 +352,79 @@ Status KvPools::publish(int handle, const int* ids, int n) {
 
 Status KvPools::finish(int handle, const int* ids, int n) {
   const Status st = publish(handle, ids, n);
-  if (st != OK) return st;
-  return release(handle);
+  return st == OK ? release(handle) : st;
 }
 
 int KvPools::new_seq_with_prefix(const int* prompt, int n) {
-  const int max_blocks = n > 0 ? (n - 1) / block_size_ : 0;  // the last prompt token is always computed
-  std::vector<BlockKey> keys(max_blocks);
-  uint64_t prev = 0;
-  for (int i = 0; i < max_blocks; ++i) {
-    keys[i].parent = prev;
-    keys[i].hash = chain_hash(prev, prompt + (size_t)i * block_size_, block_size_);
-    keys[i].ids.assign(prompt + (size_t)i * block_size_, prompt + (size_t)(i + 1) * block_size_);
-    prev = keys[i].hash;
+  // Whole pages strictly below the last prompt token: that token's logits are what the request is after, so it
+  // is always computed.
+  const int limit = n > 0 ? (n - 1) / block_size_ : 0;
+  std::vector<PageName> names;
+  names.reserve(limit);
+  NameWalker walk{prompt, block_size_};
+  // as deep as every group that keeps all keys can follow
+  while ((int)names.size() < limit) {
+    const PageName nm = walk.next();
+    bool everywhere = true;
+    for (size_t g = 0; g < groups_.size() && everywhere; ++g)
+      if (groups_[g].window < 0) everywhere = pools_[g].holds(nm);
+    if (!everywhere) break;
+    names.push_back(nm);
   }
-  // the longest chain every full-attention group holds
-  int nb = max_blocks;
-  for (size_t g = 0; g < groups_.size(); ++g) {
-    if (groups_[g].window >= 0) continue;
-    int have = 0;
-    while (have < nb && pools_[g].holds(keys[have])) ++have;
-    nb = have;
-  }
-  // a windowed group must hold the pages of the window before the prefix's end
-  auto first_needed = [&](int window, int blocks) { return std::max(0, blocks * block_size_ - (window - 1)) / block_size_; };
-  while (nb > 0) {
-    bool ok = true;
-    for (size_t g = 0; g < groups_.size() && ok; ++g) {
+  // a windowed group needs only the pages its window still reaches from the prefix's end; pages before that
+  // may be gone. Shrink the prefix until every windowed group has the tail it needs.
+  auto tail_begin = [&](int g, int depth) {
+    return std::max(0, depth * block_size_ - (groups_[g].window - 1)) / block_size_;
+  };
+  int depth = (int)names.size();
+  for (; depth > 0; --depth) {
+    bool tails = true;
+    for (size_t g = 0; g < groups_.size() && tails; ++g) {
       if (groups_[g].window < 0) continue;
-      for (int i = first_needed(groups_[g].window, nb); i < nb && ok; ++i) ok = pools_[g].holds(keys[i]);
+      for (int i = tail_begin((int)g, depth); i < depth && tails; ++i) tails = pools_[g].holds(names[i]);
     }
-    if (ok) break;
-    --nb;
+    if (tails) break;
   }
   const int h = new_seq();
   SeqBlocks& s = seqs_[h];
   for (size_t g = 0; g < groups_.size(); ++g) {
-    const int from = groups_[g].window >= 0 ? first_needed(groups_[g].window, nb) : 0;
+    const int from = groups_[g].window >= 0 ? tail_begin((int)g, depth) : 0;
     s.tables[g].assign(from, NO_BLOCK);
-    for (int i = from; i < nb; ++i) {
-      const int b = pools_[g].lookup(keys[i]);
-      if (b < 0) { nb = i; break; }  // cannot happen after the checks above; never hand out a hole
-      s.tables[g].push_back(b);
-    }
+    for (int i = from; i < depth; ++i) s.tables[g].push_back(pools_[g].take(names[i]));  // found above: never -1
     s.first_live[g] = from;
   }
-  for (size_t g = 0; g < groups_.size(); ++g)  // (only after a miss above: keep the groups equally long)
-    while ((int)s.tables[g].size() > nb) {
-      const int b = s.tables[g].back();
-      s.tables[g].pop_back();
-      if (b != NO_BLOCK) pools_[g].release(b);
-    }
-  s.length = nb * block_size_;
-  s.chain.clear();
-  for (int i = 0; i < nb; ++i) s.chain.push_back(keys[i].hash);
+  s.length = depth * block_size_;
+  for (int i = 0; i < depth; ++i) s.chain.push_back(names[i].hash);
   return h;
 }
 
 Status KvPools::check() {
   for (size_t g = 0; g < groups_.size(); ++g) {
-    const int n = pools_[g].n_blocks();
+    const BlockPool& pool = pools_[g];
+    const int n = pool.n_blocks();
+    const std::string where = "group " + std::to_string(g) + ": ";
     std::vector<int> holders(n, 0);
     for (const SeqBlocks& s : seqs_) {
       if (!s.in_use || s.released) continue;
       for (int b : s.tables[g]) {
         if (b == NO_BLOCK) continue;
-        if (b < 0 || b >= n) return fail(BOOKKEEPING, "group " + std::to_string(g) + ": page id " + std::to_string(b) + " is out of range");
-        ++holders[b];
-        if (holders[b] > 1 && !pools_[g].is_named(b))
-          return fail(BOOKKEEPING, "group " + std::to_string(g) + ": page " + std::to_string(b) + " is held twice");
+        if (b < 0 || b >= n) return fail(BOOKKEEPING, where + "page id " + std::to_string(b) + " is out of range");
+        if (++holders[b] > 1 && !pool.is_named(b))
+          return fail(BOOKKEEPING, where + "page " + std::to_string(b) + " is held twice");
       }
     }
-    std::vector<int> on_free(n, 0);
-    for (int b : pools_[g].free_list()) {
-      if (++on_free[b] > 1) return fail(BOOKKEEPING, "group " + std::to_string(g) + ": a page is on the free list twice");
-      if (holders[b]) return fail(BOOKKEEPING, "group " + std::to_string(g) + ": page " + std::to_string(b) + " is free and held");
-    }
+    std::vector<int> on_free(n, 0), in_cache(n, 0);
+    if (!pool.walk_free(on_free)) return fail(BOOKKEEPING, where + "the free pages' links are broken, or a page that is held or cached is among them");
+    if (!pool.walk_cached(in_cache)) return fail(BOOKKEEPING, where + "the cached pages' links are broken, or a page that is held or free is among them");
     for (int b = 0; b < n; ++b) {
-      if (holders[b] != pools_[g].refcount(b))
-        return fail(BOOKKEEPING, "group " + std::to_string(g) + ": page " + std::to_string(b) + " has " + std::to_string(pools_[g].refcount(b)) +
-                                     " references but " + std::to_string(holders[b]) + " tables name it");
-      const bool cached = pools_[g].in_cache(b);
-      if (cached && (holders[b] || on_free[b])) return fail(BOOKKEEPING, "group " + std::to_string(g) + ": page " + std::to_string(b) + " is cached and also held or free");
-      if (!on_free[b] && !holders[b] && !cached) return fail(BOOKKEEPING, "group " + std::to_string(g) + ": page " + std::to_string(b) + " is lost");
+      const std::string page = where + "page " + std::to_string(b);
+      if (on_free[b] > 1) return fail(BOOKKEEPING, page + " is on the free list twice");
+      if (on_free[b] && holders[b]) return fail(BOOKKEEPING, page + " is free and held");
+      if (holders[b] != pool.refcount(b))
+        return fail(BOOKKEEPING, page + " has " + std::to_string(pool.refcount(b)) + " references but " +
+                                     std::to_string(holders[b]) + " tables name it");
+      if (in_cache[b] && (holders[b] || on_free[b])) return fail(BOOKKEEPING, page + " is cached and also held or free");
+      if (!on_free[b] && !holders[b] && !in_cache[b]) return fail(BOOKKEEPING, page + " is lost");
     }
   }
   return OK;

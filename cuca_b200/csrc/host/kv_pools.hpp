@@ -6,20 +6,18 @@
 // when a request ends and, in a windowed group, as soon as the window has passed them (model/paged.rs:736-761).
 // No device memory lives here: the page ids index slabs that the Python side allocates.
 //
-// Prefix store (model/paged.rs:18-35,257-321,344-480,831-928): a full page is named by a hash chain over the
+// Prefix store (behaviour of model/paged.rs:18-35,257-321,344-480,831-928): a full page is named by a hash chain over the
 // token ids it holds (FNV-1a over the previous page's hash, then the page's ids; the first page chains from 0), so
 // two requests with the same token prefix name the same pages. `publish` files a request's full pages under
 // their names; a named page whose last reference goes stays in the pool as *cached* (least recently used first
-// out) and is what an allocation takes when no free page is left. `lookup` finds the longest page-aligned prefix
+// out) and is what an allocation takes when no free page is left. `new_seq_with_prefix` finds the longest page-aligned prefix
 // of a prompt whose pages every group still holds, at most prompt - 1 positions, and takes a reference to each.
 // A name is the hash, the parent's hash and the ids themselves, so a collision of hashes never shares pages.
 // A named page is read-only: a hit covers whole pages below the prompt's last token, and the request appends
 // after them.
 #pragma once
 #include <cstdint>
-#include <deque>
 #include <string>
-#include <unordered_map>
 #include <vector>
 
 namespace cuca {
@@ -28,42 +26,52 @@ constexpr int NO_BLOCK = -1;  // a table entry whose page was given back (behind
 
 uint64_t chain_hash(uint64_t prev, const int* ids, int n);
 
-// What names a full page: its chain hash, the hash of the page before it, and its token ids.
-struct BlockKey {
+// What names a full page: its chain hash, the hash of the page before it, and (a view of) its token ids.
+struct PageName {
   uint64_t hash = 0, parent = 0;
-  std::vector<int> ids;
-  bool operator==(const BlockKey& o) const { return hash == o.hash && parent == o.parent && ids == o.ids; }
+  const int* ids = nullptr;
+  int n_ids = 0;
 };
 
-// One group's pages: free list (popped from the back, as the reference's), reference counts, names, and the
-// least-recently-used order of unreferenced named pages.
+// One group's pages. A page is in exactly one of three states: free (on an intrusive last-in first-out stack
+// through `link_`), held (one or more tables name it; `refs_` says how many), or cached (it carries a name, nothing
+// holds it; it sits in an intrusive doubly linked list in least-recently-used order, so taking it out on a hit and
+// evicting the oldest are both O(1) with no stale entries to skip). Names live in one open-addressed table keyed by
+// (hash, parent) that stores page numbers; a hit also compares the token ids, so equal hashes never share pages.
 class BlockPool {
  public:
   explicit BlockPool(int n_blocks);
-  int n_blocks() const { return (int)refcount_.size(); }
-  int free_count() const { return (int)free_.size() + cached_; }  // what allocations can still get
-  int cached_count() const { return cached_; }
+  int n_blocks() const { return (int)refs_.size(); }
+  int free_count() const { return n_free_ + n_cached_; }  // what allocations can still get
+  int cached_count() const { return n_cached_; }
   int alloc();            // a page with one reference: a free one, else the least recently used cached one; -1: none
   bool release(int b);    // drops one reference; false: the page has none (freed twice, or out of range)
-  bool register_key(int b, const BlockKey& key);  // false: already named, or the name is taken
-  bool holds(const BlockKey& key) const;
-  int lookup(const BlockKey& key);                // takes a reference; -1 unless holds(key)
+  bool give_name(int b, const PageName& name);  // false: not held, already named, or another page has the name
+  bool holds(const PageName& name) const { return find(name) >= 0; }
+  int take(const PageName& name);               // one more reference to the page of this name; -1 if there is none
   bool is_named(int b) const { return named_[b] != 0; }
-  int refcount(int b) const { return refcount_[b]; }
+  int refcount(int b) const { return refs_[b]; }
+  bool is_cached(int b) const { return named_[b] && refs_[b] == 0; }
+  bool is_free(int b) const { return !named_[b] && refs_[b] == 0; }
+  // Walks the free stack and the cached list and counts every page it meets into `seen`; false when a walk does
+  // not end after n_blocks() pages (a loop in the links) or meets a page in the wrong state.
+  bool walk_free(std::vector<int>& seen) const;
+  bool walk_cached(std::vector<int>& seen) const;
   void reset();
-  const std::vector<int>& free_list() const { return free_; }
-  bool in_cache(int b) const { return stamp_[b] != 0; }
 
  private:
-  std::vector<int> free_;
-  std::vector<int> refcount_;
+  int find(const PageName& name) const;          // the page of this name, or -1
+  size_t slot_of(uint64_t hash, uint64_t parent) const;
+  void forget_name(int b);
+  void unlink_cached(int b);
+  std::vector<int> refs_;
   std::vector<char> named_;
-  std::vector<BlockKey> key_;
-  std::deque<std::pair<int, uint64_t>> lru_;  // (page, stamp): an entry is live while the page's stamp equals it
-  std::vector<uint64_t> stamp_;               // 0: not in the cache
-  uint64_t next_stamp_ = 1;
-  int cached_ = 0;
-  std::unordered_map<uint64_t, int> by_hash_;
+  std::vector<int> link_, back_;                 // free stack: link_ = next; cached list: link_ = newer, back_ = older
+  int free_top_ = -1, n_free_ = 0;
+  int oldest_ = -1, newest_ = -1, n_cached_ = 0;
+  std::vector<uint64_t> hash_, parent_;          // per page: its name
+  std::vector<std::vector<int>> ids_;
+  std::vector<int> table_;                       // open addressing, linear probing; -1 empty
 };
 
 struct Group {

@@ -60,6 +60,7 @@ class EngineCore:
         needs = self.model.cache_needs()
         self.groups = plan_groups(needs, kv_tokens, block_size, max_sequences, self.max_step_tokens, window_pools)
         self.pools = KvPools(self.groups, block_size)
+        self.pools.stateful = any(n.state is not None for n in needs.values())
         self.slots = StateSlots(max_sequences)
         self.cache = DeviceCache(self.rt, self.groups, block_size, needs, max_sequences, self.context_length)
         self.stepper = Stepper(self.model, self.pools, self.cache, self.context_length)

@@ -83,50 +83,27 @@ class GpuBackend:
         self._needs_scratch[s] = r.temperature > 0 and ((ranked and r.top_k > 1024) or (not ranked and r.top_p < 1.0))
 
     # ------------------------------------------------------------ decode through a captured graph
-    def _table_updates(self, seqs) -> None:
-        """Upload page-table entries that changed (new pages) for these requests."""
-        core = self.core
-        lib, staging = host.load(), core.stepper._staging
-        n = len(seqs)
-        handles, slots = host.ints(s.blocks.handle for s in seqs), host.ints(s.slot for s in seqs)
-        for gi in range(core.pools.n_groups):
-            buf = staging.take()
-            count = lib.cuca_host_table_updates(core.pools._h, handles, slots, n, core.cache.table_width, gi,
-                                                buf.data_ptr(), buf.shape[0])
-            if count < 0:  # more new pages than the buffer holds: the widest case is every entry of every table
-                buf = staging.take(2 * n * core.cache.table_width)
-                count = lib.cuca_host_table_updates(core.pools._h, handles, slots, n, core.cache.table_width, gi,
-                                                    buf.data_ptr(), buf.shape[0])
-            if count < 0:
-                raise RuntimeError(host.last_error() or "page-table updates do not fit their staging buffer")
-            if count > 0:
-                dev = staging.send(2 * count)
-                ops.scatter_int(core.cache.tables[gi], dev[:count], dev[count:])
-
     def _run_decode_graph(self, plans: Sequence[Plan]) -> list:
         seqs = [p.seq for p in plans]
         n = len(seqs)
         starts = [p.start if p.start >= 0 else p.seq.blocks.length for p in plans]
         max_len = max(starts) + 1
         g = self.graphs.get(n, max_len, any(self._needs_scratch[s.slot] for s in seqs))
-        self._table_updates(seqs)
-        g.load_rows([p.tokens[0] for p in plans], starts, [s.slot for s in seqs])
+        stepper = self.core.stepper
+        handles, slots, tokens = [s.blocks.handle for s in seqs], [s.slot for s in seqs], [p.tokens[0] for p in plans]
+        stepper.check_single_tokens(handles, slots, tokens)  # the refusals of an eager step, before anything runs
+        stepper.upload_table_updates(handles, slots)
+        g.load_rows(tokens, starts, slots)
         g.replay()
         self.last_graph = g
         out = g.sampled.tolist()  # the one synchronisation of a step; its last word is the device error word
         if out[g.bucket]:
             self.core.rt.raise_device_error(out[g.bucket])  # before anything is applied: the step is lost
         tokens = out[:n]
-        self._advance(seqs, 1)
+        stepper.advance(handles, [1] * n)
         self.core.stepper.steps += 1
         self.graph_steps += 1
         return tokens
-
-    def _advance(self, seqs, n_steps: int) -> None:
-        """Every request has `n_steps` more positions cached; pages behind windows go back."""
-        if host.load().cuca_host_step_advance(self.core.pools._h, host.ints(s.blocks.handle for s in seqs),
-                                              host.ints([n_steps] * len(seqs)), len(seqs)):
-            raise RuntimeError(host.last_error())
 
     def burst(self, seqs, tokens, n_steps: int, check: bool = True):
         """`n_steps` decode steps back to back on the device, each feeding its sampled tokens to the next; the
@@ -142,8 +119,11 @@ class GpuBackend:
             core.pools.reserve(s.blocks, start + n_steps)
         max_len = max(starts) + n_steps
         g = self.graphs.get(n, max_len, any(self._needs_scratch[s.slot] for s in seqs))
-        self._table_updates(seqs)
-        g.load_rows(tokens, starts, [s.slot for s in seqs])
+        stepper = core.stepper
+        handles, slots = [s.blocks.handle for s in seqs], [s.slot for s in seqs]
+        stepper.check_single_tokens(handles, slots, tokens)
+        stepper.upload_table_updates(handles, slots)
+        g.load_rows(tokens, starts, slots)
         g.counter.zero_()
         for _ in range(n_steps):
             g.replay()
@@ -151,7 +131,7 @@ class GpuBackend:
             code = int(g.sampled[g.bucket].item())
             if code:
                 self.core.rt.raise_device_error(code)
-        self._advance(seqs, n_steps)
+        stepper.advance(handles, [n_steps] * n)
         self.graph_steps += n_steps
         return g.history[:n_steps, :n]
 

@@ -14,7 +14,7 @@ from typing import Sequence
 import torch
 
 from ..kernels import ops
-from .step import AttentionPlan, StepBatch
+from .step import StepBatch
 
 LEN_BUCKET = 512
 MAX_HISTORY = 1024
@@ -45,13 +45,8 @@ class DecodeGraph:
         self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
         self.pinned = torch.zeros(3 * bucket, dtype=torch.int32).pin_memory()
         self.pinned_np = self.pinned.numpy()
-        nkv = max((g.n_kv_heads for g in core.groups), default=1)
-        hd = max((g.head_dim for g in core.groups), default=128)
-        chunking = ops.decode_chunking(bucket, nkv, max_len, hd)
-        self.batch = StepBatch(
-            n_rows=bucket, n_seqs=bucket, tokens=self.tokens, positions=self.positions,
-            seq_of_row=self.slot_of_row, slots=self.slot_of_row, logit_rows=self.logit_rows, n_logit_rows=bucket,
-            attention_plan=AttentionPlan(None, bucket, max_len, None, None, 0, fixed_chunking=chunking))
+        # the same description of a step that the step function builds, over static buffers; mixers plan from it
+        self.batch = StepBatch.single_tokens(self.tokens, self.positions, self.slot_of_row, self.logit_rows, max_len)
         self.graph = None
         self.scratch = None
         self.logits = None  # [bucket, vocab]: what the last replay's model pass left (valid until the next replay)

@@ -30,7 +30,7 @@ from collections import deque
 from dataclasses import dataclass, field
 from typing import Callable, Optional, Sequence
 
-from ..cache.pages import KvPools, StateSlots
+from ..cache.pages import KvPools, StateSlots, StatefulCacheError
 from ..native import host
 
 PREFILL, DECODE, ENDED = "prefill", "decode", "ended"
@@ -147,6 +147,12 @@ class Scheduler:
 
     def __init__(self, pools: KvPools, slots: StateSlots, backend, config: SchedulerConfig,
                  seed_source: Optional[Callable[[], int]] = None):
+        if config.prefix_cache and getattr(pools, "stateful", False):
+            # a request that starts from cached pages skips the tokens they hold; a mixer with state of its own
+            # would start with empty state in the middle of its sequence. The reference keeps snapshots of such
+            # state beside the pages (src/provider/local/engine/scheduler.rs:813-830); this engine refuses.
+            raise StatefulCacheError("prefix_cache cannot be used with this model: a mixer keeps per-request state "
+                                     "besides its pages, and cached pages do not bring that state back")
         self.pools = pools
         self.slots = slots
         self.backend = backend

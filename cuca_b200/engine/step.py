@@ -11,8 +11,9 @@ before a kernel runs, and a failed validation leaves the cache untouched
 (model/cpu.rs:1822-1837,4154-4185).
 
 Rows carry their request's slot; page tables live on the device per slot and a
-step uploads only the entries that changed, together with tokens and positions,
-in one copy from pinned memory.
+step uploads only the entries that changed, together with tokens, positions and
+the per-request description of the step, in one copy from pinned memory. The
+step function does not plan for any kernel: mixers do that from `StepBatch`.
 """
 from __future__ import annotations
 
@@ -27,6 +28,9 @@ from ..cache.device import DeviceCache
 from ..cache.pages import KvPools, SeqBlocks
 from ..kernels import ops
 from ..native import host
+
+
+N_FIXED_SECTIONS = 8  # sections of the packed buffer before the per-group page-table updates
 
 
 class StepError(ValueError):
@@ -44,42 +48,44 @@ class StepEntry:
 
 
 @dataclass
-class AttentionPlan:
-    """How the step's rows are handed to the attention kernels: single-token requests to the decode form,
-    longer portions in tiles of up to 64 rows to the prefill form."""
-
-    decode_rows: Optional[torch.Tensor]  # [n_decode] int32 row numbers; None: rows 0..n_decode-1
-    n_decode: int
-    max_len: int  # largest position + 1 among the decode rows (bounds the key chunks)
-    tile_row0: Optional[torch.Tensor]
-    tile_nrows: Optional[torch.Tensor]
-    n_tiles: int
-    fixed_chunking: Optional[tuple] = None  # (chunk, n_splits) frozen for a captured graph
-    tile128_row0: Optional[torch.Tensor] = None  # the same portions cut into tiles of up to 128 rows (tcgen05 form)
-    tile128_nrows: Optional[torch.Tensor] = None
-    n_tiles128: int = 0
-
-    def chunk(self, n_kv_heads: int, head_dim: int = 128):
-        if self.fixed_chunking is not None:
-            return self.fixed_chunking
-        from ..kernels.ops import decode_chunking
-        return decode_chunking(self.n_decode, n_kv_heads, self.max_len, head_dim)
-
-
-@dataclass
 class StepBatch:
-    """The step as the parts see it (device tensors unless said otherwise)."""
+    """The step as the parts see it (device tensors unless said otherwise).
+
+    Per row: `tokens`, `positions`, `seq_of_row` (the slot of the row's request; < 0: padding). Per request, in the
+    order given: `slots`, `req_row0` (the row its tokens start at), `req_count` (how many tokens it brings),
+    `req_start` (how many positions it had cached before). The same per-request lists stand in `host` as Python
+    lists (`slots`, `counts`, `starts`, `tokens`) for parts that plan on the host. How rows are handed to kernels
+    (tiles, lists of single-token rows, scans over whole portions) is each mixer's own business: it derives what it
+    needs from these arrays, once per step, and keeps it in `plans` under a key of its own for the other layers of
+    its kind."""
 
     n_rows: int
     n_seqs: int
     tokens: torch.Tensor  # [rows] int32
     positions: torch.Tensor  # [rows] int32
-    seq_of_row: torch.Tensor  # [rows] int32: the slot of the row's request (< 0: padding)
+    seq_of_row: torch.Tensor  # [rows] int32
     slots: torch.Tensor  # [requests] int32
     logit_rows: Optional[torch.Tensor]  # [wanted] int32 row numbers
     n_logit_rows: int
-    host: dict = field(default_factory=dict)  # the same lists on the host, for parts that plan there
-    attention_plan: Optional[AttentionPlan] = None
+    host: dict = field(default_factory=dict)
+    req_row0: Optional[torch.Tensor] = None  # [requests] int32
+    req_count: Optional[torch.Tensor] = None
+    req_start: Optional[torch.Tensor] = None
+    static_max_len: Optional[int] = None  # a captured step: every request brings one token, none is longer than this
+    plans: dict = field(default_factory=dict)
+
+    @classmethod
+    def single_tokens(cls, tokens, positions, slot_of_row, row_numbers, max_len: int) -> "StepBatch":
+        """A step of static device buffers in which every row is one request's single next token (rows with slot
+        -1 are padding) and every row's logits are wanted: the form a captured decode step has. `row_numbers` is
+        0..rows-1 on the device; `positions` doubles as the requests' cached lengths."""
+        n = tokens.shape[0]
+        return cls(n_rows=n, n_seqs=n, tokens=tokens, positions=positions, seq_of_row=slot_of_row, slots=slot_of_row,
+                   logit_rows=row_numbers, n_logit_rows=n, host={"counts": [1] * n}, req_row0=row_numbers,
+                   req_count=torch.ones_like(row_numbers), req_start=positions, static_max_len=int(max_len))
+
+    def all_single(self) -> bool:
+        return self.static_max_len is not None or all(c == 1 for c in self.host.get("counts", [0]))
 
 
 class _Staging:
@@ -136,7 +142,8 @@ class Stepper:
         """Validate the batch and pack it (the host core does both, `csrc/host/step_pack.cpp`): empty batch, empty
         token list, context overflow, token id out of range, missing or returned pages, wanted places and duplicate
         slots are refused before anything changes. Then one copy from pinned memory brings tokens, positions,
-        slots, wanted rows, the attention plan and the page-table entries that changed."""
+        slots, wanted rows, the per-request description (first row, count, cached length) and the page-table entries
+        that changed."""
         lib, pools = host.load(), self.pools
         n = len(entries)
         counts = [len(e.tokens) for e in entries]
@@ -145,36 +152,67 @@ class Stepper:
         flat_want = [int(w) for e in entries for w in e.want]
         seqs = host.ints(e.blocks.handle for e in entries)
         slots_c = host.ints(e.slot for e in entries)
-        sizes = (ctypes.c_int * (10 + 2 * pools.n_groups))()
-        meta = (ctypes.c_int * 9)()
+        sizes = (ctypes.c_int * (N_FIXED_SECTIONS + 2 * pools.n_groups))()
+        meta = (ctypes.c_int * 4)()
         args = (pools._h, n, seqs, slots_c, host.ints(counts), host.ints(flat_tokens), host.ints(n_want),
                 host.ints(flat_want), self.context_length, self.vocab, self.cache.max_sequences, self.cache.table_width)
         buf = self._staging.take()
         code = lib.cuca_host_step_pack(*args, buf.data_ptr(), buf.shape[0], sizes, meta)
         if code == host.TOO_SMALL:
-            buf = self._staging.take(meta[8])
+            buf = self._staging.take(meta[3])
             code = lib.cuca_host_step_pack(*args, buf.data_ptr(), buf.shape[0], sizes, meta)
         if code:
             raise StepError(host.last_error())
-        T, S, R, n_decode, max_len, identity, n_tiles, n_tiles128, total = list(meta)
+        T, S, R, total = list(meta)
+        at_start = 3 * T + S + R + 2 * S  # where the requests' cached lengths stand in the buffer
+        starts = buf[at_start:at_start + S].tolist()
         dev = self._staging.send(total)
         views, off = [], 0
         for k in sizes:
             views.append(dev[off:off + k])
             off += k
         for gi in range(pools.n_groups):
-            idx, val = views[10 + 2 * gi], views[11 + 2 * gi]
+            idx, val = views[N_FIXED_SECTIONS + 2 * gi], views[N_FIXED_SECTIONS + 2 * gi + 1]
             if idx.shape[0]:
                 ops.scatter_int(self.cache.tables[gi], idx, val)
-        starts, row = [], 0
         return StepBatch(n_rows=T, n_seqs=S, tokens=views[0], positions=views[1], seq_of_row=views[2],
                          slots=views[3], logit_rows=views[4] if R else None, n_logit_rows=R,
-                         host={"counts": counts, "slots": [e.slot for e in entries], "tokens": flat_tokens},
-                         attention_plan=AttentionPlan(None if identity else views[5], n_decode, max_len,
-                                                      views[6] if n_tiles else None, views[7] if n_tiles else None,
-                                                      n_tiles, tile128_row0=views[8] if n_tiles128 else None,
-                                                      tile128_nrows=views[9] if n_tiles128 else None,
-                                                      n_tiles128=n_tiles128))
+                         host={"counts": counts, "slots": [e.slot for e in entries], "tokens": flat_tokens,
+                               "starts": starts},
+                         req_row0=views[5], req_count=views[6], req_start=views[7])
+
+    # ------------------------------------------------------------ steps whose rows already live on the device
+    def check_single_tokens(self, handles, slots, tokens) -> None:
+        """The host-side refusals of `build`, for a captured step that brings one token per request."""
+        n = len(handles)
+        if host.load().cuca_host_step_validate(self.pools._h, n, host.ints(handles), host.ints(slots),
+                                               host.ints([1] * n), host.ints(tokens), self.context_length, self.vocab,
+                                               self.cache.max_sequences):
+            raise StepError(host.last_error())
+
+    def upload_table_updates(self, handles, slots) -> None:
+        """Page-table entries of these requests that changed since they were last sent, to the device tables."""
+        lib, staging, pools = host.load(), self._staging, self.pools
+        n = len(handles)
+        hs, ss = host.ints(handles), host.ints(slots)
+        for gi in range(pools.n_groups):
+            buf = staging.take()
+            count = lib.cuca_host_table_updates(pools._h, hs, ss, n, self.cache.table_width, gi, buf.data_ptr(),
+                                                buf.shape[0])
+            if count == -1:  # more new pages than the buffer holds: the widest case is every entry of every table
+                buf = staging.take(2 * n * self.cache.table_width)
+                count = lib.cuca_host_table_updates(pools._h, hs, ss, n, self.cache.table_width, gi, buf.data_ptr(),
+                                                    buf.shape[0])
+            if count < 0:
+                raise StepError(host.last_error() or "page-table updates do not fit their staging buffer")
+            if count > 0:
+                dev = staging.send(2 * count)
+                ops.scatter_int(self.cache.tables[gi], dev[:count], dev[count:])
+
+    def advance(self, handles, counts) -> None:
+        """Every request has `counts[i]` more positions cached; pages behind windows go back."""
+        if host.load().cuca_host_step_advance(self.pools._h, host.ints(handles), host.ints(counts), len(handles)):
+            raise StepError(host.last_error())
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run one step; returns logits [wanted, vocab] (32-bit, on the device) or None if nothing is wanted."""
@@ -182,9 +220,6 @@ class Stepper:
             raise StepError("a step needs at least one request")
         batch = self.build(entries)
         logits = self.model.forward(batch, self.cache)
-        # every request has its tokens cached now; pages behind windows go back
-        if host.load().cuca_host_step_advance(self.pools._h, host.ints(e.blocks.handle for e in entries),
-                                              host.ints(len(e.tokens) for e in entries), len(entries)):
-            raise StepError(host.last_error())
+        self.advance([e.blocks.handle for e in entries], [len(e.tokens) for e in entries])
         self.steps += 1
         return logits

@@ -159,6 +159,90 @@ def gemm(a, w, out, epilogue=EPI_STORE, bias=None, err=None) -> None:
         gemm_simt(a, w, out, epilogue, bias)
 
 
+class AttentionPlan:
+    """How a step's rows are handed to the attention kernels, derived from the step's per-request description:
+    requests that bring one token go to the split-key decode form (their row numbers; None when every row is
+    one), longer portions in tiles of consecutive rows to a prefill form. The tile heights are the kernel
+    library's; the lists are made on the device (`cuca_attention_plan`), the counts on the host from the same
+    per-request counts. One plan serves every attention layer of a step; tiles of a height and the key chunking
+    for a (key heads, head size) pair are made when first asked for."""
+
+    def __init__(self, step):
+        counts = step.host["counts"]
+        self.step = step
+        self.static = step.static_max_len is not None
+        if self.static:
+            self.n_decode, self.max_len = step.n_rows, step.static_max_len
+            self.n_portions = 0
+        else:
+            starts = step.host["starts"]
+            single = [s + 1 for c, s in zip(counts, starts) if c == 1]
+            self.n_decode, self.max_len = len(single), max(single, default=1)
+            self.n_portions = len(counts) - self.n_decode
+        self.identity = self.n_portions == 0  # every row is a single token: decode rows are 0..rows-1
+        self._counts = counts
+        self._decode_rows = None
+        self._tiles: dict = {}
+        self._chunking: dict = {}
+
+    @property
+    def decode_rows(self):
+        if self.identity or self.n_decode == 0:
+            return None
+        if self._decode_rows is None:
+            self._make(tile_rows(0))  # the list of single rows comes with the first tiling asked for
+        return self._decode_rows
+
+    def tiles(self, rows_per_tile: int):
+        """(first rows, row counts, number of tiles) of the portions cut into tiles of this height."""
+        if rows_per_tile not in self._tiles:
+            self._make(rows_per_tile)
+        return self._tiles[rows_per_tile]
+
+    def _make(self, rows_per_tile: int) -> None:
+        step = self.step
+        n_tiles = sum(-(-c // rows_per_tile) for c in self._counts if c > 1)
+        want_rows = self._decode_rows is None and not self.identity and self.n_decode > 0
+        buf = torch.empty(2 * n_tiles + (self.n_decode if want_rows else 0), dtype=torch.int32,
+                          device=step.positions.device)
+        row0, nrows, rows = buf[:n_tiles], buf[n_tiles:2 * n_tiles], buf[2 * n_tiles:]
+        lib = library.load()
+        library.check(lib.cuca_attention_plan(_p(step.req_row0), _p(step.req_count), _p(step.req_start), step.n_seqs,
+                                              rows_per_tile, _p(rows) if want_rows else None,
+                                              self.n_decode if want_rows else 0, _p(row0), _p(nrows), n_tiles,
+                                              _stream()), "attention_plan")
+        self._tiles[rows_per_tile] = (row0, nrows, n_tiles)
+        if want_rows:
+            self._decode_rows = rows
+
+    def chunk(self, n_kv_heads: int, head_dim: int):
+        key = (n_kv_heads, head_dim)
+        if key not in self._chunking:
+            self._chunking[key] = decode_chunking(self.n_decode, n_kv_heads, self.max_len, head_dim)
+        return self._chunking[key]
+
+
+def attention_plan(step):
+    """The step's plan for the attention kernels (made once per step), or None for a hand-made batch that carries
+    no per-request description: such a batch runs through the plain kernel."""
+    if getattr(step, "req_start", None) is None or "counts" not in step.host:
+        return None
+    plan = step.plans.get("paged_attention")
+    if plan is None:
+        plan = step.plans["paged_attention"] = AttentionPlan(step)
+    return plan
+
+
+_tile_rows: dict = {}
+
+
+def tile_rows(which: int) -> int:
+    """Rows per tile of a prefill form, asked of the kernel library: 0 the `mma.sync` form, 1 the tcgen05 form."""
+    if which not in _tile_rows:
+        _tile_rows[which] = int(library.load().cuca_attention_tile_rows(which))
+    return _tile_rows[which]
+
+
 _attn_scratch: dict = {}
 _attn_scratch_retired: list = []  # superseded buffers: a captured graph may still hold their addresses
 USE_TC_ATTENTION = True  # prompt portions through the tcgen05 attention where the shape allows
@@ -190,12 +274,25 @@ def attention_mma_supported(n_heads, n_kv_heads, head_dim, q_stride, out_stride)
     return bool(lib.cuca_attention_mma_supported(n_heads, n_kv_heads, head_dim, q_stride, out_stride))
 
 
-def decode_chunking(n_rows: int, n_kv_heads: int, max_len: int, head_dim: int = 128, sms: int = 148):
+_sms: dict = {}
+
+
+def sm_count() -> int:
+    """SMs of the current device, asked of the kernel library once per device."""
+    dev = torch.cuda.current_device()
+    if dev not in _sms:
+        _sms[dev] = int(library.load().cuca_sm_count())
+    return _sms[dev]
+
+
+def decode_chunking(n_rows: int, n_kv_heads: int, max_len: int, head_dim: int = 128, sms: int | None = None):
     """(chunk, n_splits) of the decode attention. chunk 0: every row spreads its own keys evenly over the
     chunks it uses (the kernel repeats this choice per row from the row's own length, never above n_splits).
     n_splits minimises the time on the critical path in units of one 64-key tile: rounds of CTAs the GPU needs
     (a CTA holds three stages of a key and a value tile in shared memory) times (tiles per chunk + about three
     tiles' worth of fixed work per CTA); at most 32 and at most one chunk per tile of the longest row."""
+    if sms is None:
+        sms = sm_count()
     tiles = max(1, -(-max_len // 64))
     smem = 3 * 2 * 64 * (head_dim + 8) * 2 + 2048  # three stages of a key and a value tile
     slots = sms * max(1, min(8, (227 * 1024) // smem))
@@ -233,12 +330,11 @@ def attention_decode_fused(partial, bias, cos, sin, rotary_dim, has_kv, out, kpo
         _p(err), _stream()), "attention_decode_fused")
 
 
-def attention_decode_fused_supported(step, cache, out_dtype, n_rows, n_heads, n_kv_heads, head_dim) -> bool:
+def attention_decode_fused_supported(plan, cache, out_dtype, n_rows, n_heads, n_kv_heads, head_dim) -> bool:
     """True when every row of the step is a single token of its request and the tensor-core decode form takes
     the shape: then rotate-and-store and attention are one launch."""
-    plan = getattr(step, "attention_plan", None)
     bs = cache.block_size
-    return (out_dtype == torch.bfloat16 and plan is not None and plan.n_decode == n_rows and plan.n_tiles == 0
+    return (out_dtype == torch.bfloat16 and plan is not None and plan.identity and plan.n_decode == n_rows
             and n_rows > 0 and bs & (bs - 1) == 0 and head_dim % 16 == 0
             and attention_mma_supported(n_heads, n_kv_heads, head_dim, 2, n_heads * head_dim))
 
@@ -268,29 +364,28 @@ def attention_prefill_tc(q, out, kpool, vpool, positions, seq_of_row, tables, ti
         n_kv_heads, head_dim, float(scale), int(window or 0), _p(err), _stream()), "attention_prefill_tc")
 
 
-def attention(qkv, out, cache, step, n_heads, n_kv_heads, head_dim, scale, window, err) -> None:
+def attention(qkv, out, cache, step, plan, n_heads, n_kv_heads, head_dim, scale, window, err) -> None:
     """Paged causal attention of every row of the step; q is the head of each `qkv` row. bfloat16 with head
     sizes 16..128 in steps of 16 runs on tensor cores: single-token requests through the split-key decode form,
     portions of prompts through the prefill form; everything else (the 32-bit path, other head sizes) through
     the plain kernel."""
-    plan = getattr(step, "attention_plan", None)
     bs = cache.block_size
     if (out.dtype == torch.bfloat16 and plan is not None and bs & (bs - 1) == 0
             and attention_mma_supported(n_heads, n_kv_heads, head_dim, qkv.stride(0), out.stride(0))):
+        if plan.n_portions:
+            if USE_TC_ATTENTION and attention_tc_supported(qkv, out, cache.k, cache.v, n_heads, n_kv_heads, head_dim):
+                row0, nrows, n = plan.tiles(tile_rows(1))
+                attention_prefill_tc(qkv, out, cache.k, cache.v, step.positions, step.seq_of_row, cache.tables,
+                                     row0, nrows, n, n_heads, n_kv_heads, head_dim, scale, window, err)
+            else:
+                row0, nrows, n = plan.tiles(tile_rows(0))
+                attention_prefill(qkv, qkv.stride(0), out, cache.k, cache.v, step.positions, step.seq_of_row,
+                                  cache.tables, row0, nrows, n, n_heads, n_kv_heads, head_dim, scale, window, err)
         if plan.n_decode:
+            chunk, n_splits = plan.chunk(n_kv_heads, head_dim)
             attention_decode(qkv, qkv.stride(0), out, cache.k, cache.v, step.positions, step.seq_of_row,
                              cache.tables, plan.decode_rows, plan.n_decode, n_heads, n_kv_heads, head_dim, scale,
-                             window, plan.chunk(n_kv_heads, head_dim)[0], plan.chunk(n_kv_heads, head_dim)[1], err)
-        if plan.n_tiles:
-            if plan.n_tiles128 and USE_TC_ATTENTION and attention_tc_supported(qkv, out, cache.k, cache.v, n_heads,
-                                                                               n_kv_heads, head_dim):
-                attention_prefill_tc(qkv, out, cache.k, cache.v, step.positions, step.seq_of_row, cache.tables,
-                                     plan.tile128_row0, plan.tile128_nrows, plan.n_tiles128, n_heads, n_kv_heads,
-                                     head_dim, scale, window, err)
-            else:
-                attention_prefill(qkv, qkv.stride(0), out, cache.k, cache.v, step.positions, step.seq_of_row,
-                                  cache.tables, plan.tile_row0, plan.tile_nrows, plan.n_tiles, n_heads, n_kv_heads,
-                                  head_dim, scale, window, err)
+                             window, chunk, n_splits, err)
         return
     attention_generic(qkv, qkv.stride(0), out, cache.k, cache.v, step.positions, step.seq_of_row, cache.tables,
                       n_heads, n_kv_heads, head_dim, scale, window, err)

@@ -83,23 +83,28 @@ class PagedAttention(Mixer):
             self.position.prepare(context_length)
 
     # ------------------------------------------------------------ step
+    def plan(self, step):
+        """How this step's rows go to the attention kernels: made once per step from the per-request description
+        (`StepBatch.req_row0/req_count/req_start`) and shared by the attention layers of the step."""
+        return ops.attention_plan(step)
+
     def forward(self, h, stream, step, cache) -> None:
         stream = self.rt.stream(stream)
         nh, d = self.n_heads, self.head_dim
         nkv = 0 if self.shares_cache else self.n_kv_heads
         fused = self.position.fused_tables() if self.position is not None else None
         kpool, vpool = (None, None) if nkv == 0 else (cache.k, cache.v)
+        plan = self.plan(step)
         if fused is not None and self.rt.use_partials and ops.gemm_partial_supported(h, self.w_qkv):
             # few tokens: the projection leaves its K slices unadded; rotate-and-store adds them in 32-bit
             cos, sin, rot = fused
             parts = ops.gemm_partial(h, self.w_qkv, self.rt.err)
-            if ops.attention_decode_fused_supported(step, cache, h.dtype, h.shape[0], nh, self.n_kv_heads, d):
+            if ops.attention_decode_fused_supported(plan, cache, h.dtype, h.shape[0], nh, self.n_kv_heads, d):
                 # single tokens only: adding the slices, rotation, the page write and attention are one launch
                 attn = self.rt.empty(h.shape[0], nh * d)
-                plan = step.attention_plan
                 chunk, n_splits = plan.chunk(self.n_kv_heads, d)
                 ops.attention_decode_fused(parts, self.b_qkv, cos, sin, rot, nkv > 0, attn, cache.k, cache.v,
-                                           step.positions, step.seq_of_row, cache.tables, plan.decode_rows,
+                                           step.positions, step.seq_of_row, cache.tables, None,
                                            plan.n_decode, nh, self.n_kv_heads, d, self.scale, self.window, chunk,
                                            n_splits, self.rt.err)
                 stream.add_linear(attn, self.w_o, bias=self.b_o)
@@ -119,5 +124,5 @@ class PagedAttention(Mixer):
             ops.rope_store(q, step.positions, step.seq_of_row, cache.tables, cos, sin, rot, kpool, vpool,
                            cache.block_size, nh, nkv, d, self.rt.err)
         attn = self.rt.empty(h.shape[0], nh * d)
-        ops.attention(q, attn, cache, step, nh, self.n_kv_heads, d, self.scale, self.window, self.rt.err)
+        ops.attention(q, attn, cache, step, plan, nh, self.n_kv_heads, d, self.scale, self.window, self.rt.err)
         stream.add_linear(attn, self.w_o, bias=self.b_o)

@@ -587,3 +587,40 @@ def test_rmsnorm_many_rows_equals_few_rows_to_the_bit(dev):
         assert torch.equal(many[100:103], few)
         ref = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + 1e-5) * w
         assert torch.allclose(many, ref, atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("n_req,longest,tile", [(1, 1, 64), (3, 150, 64), (40, 300, 128), (1500, 3, 64),
+                                                (700, 700, 64), (9, 2048, 128)])
+def test_attention_plan_on_the_device(dev, n_req, longest, tile):
+    """The attention part's plan is made on the device from the step's per-request description: the rows of the
+    requests that bring one token, and the longer portions cut into tiles, heaviest (latest positions) first.
+    More requests than the kernel's block has threads, and more tiles than it ranks (then in request order)."""
+    import numpy as np
+    from cuca_b200.kernels import library, ops
+    rs = np.random.default_rng(n_req + longest)
+    counts = rs.integers(1, longest + 1, size=n_req)
+    counts[rs.random(n_req) < 0.4] = 1
+    starts = rs.integers(0, 5000, size=n_req)
+    row0 = np.concatenate([[0], np.cumsum(counts)[:-1]])
+    n_decode = int((counts == 1).sum())
+    n_tiles = int(sum(-(-c // tile) for c in counts if c > 1))
+    t = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device=dev)
+    rows = torch.full((max(1, n_decode),), -1, dtype=torch.int32, device=dev)
+    t0 = torch.full((max(1, n_tiles),), -1, dtype=torch.int32, device=dev)
+    tn = torch.full((max(1, n_tiles),), -1, dtype=torch.int32, device=dev)
+    lib = library.load()
+    d_row0, d_counts, d_starts = t(row0), t(counts), t(starts)
+    library.check(lib.cuca_attention_plan(d_row0.data_ptr(), d_counts.data_ptr(), d_starts.data_ptr(), n_req, tile,
+                                          rows.data_ptr(), n_decode, t0.data_ptr(), tn.data_ptr(), n_tiles,
+                                          torch.cuda.current_stream().cuda_stream), "attention_plan")
+    assert rows[:n_decode].tolist() == [int(r) for r, c in zip(row0, counts) if c == 1]
+    want = [(int(r + off), int(min(tile, c - off)), int(s + off))
+            for r, c, s in zip(row0, counts, starts) if c > 1 for off in range(0, c, tile)]
+    got = list(zip(t0[:n_tiles].tolist(), tn[:n_tiles].tolist()))
+    assert sorted(got) == sorted((a, b) for a, b, _ in want)          # every portion is covered exactly once
+    if n_tiles <= 2048:
+        ranked = sorted(range(len(want)), key=lambda i: (-want[i][2], i))
+        assert got == [(want[i][0], want[i][1]) for i in ranked]       # heaviest first, ties in request order
+    else:
+        assert got == [(a, b) for a, b, _ in want]
+    assert ops.tile_rows(0) == 64 and ops.tile_rows(1) == 128

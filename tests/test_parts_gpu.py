@@ -276,6 +276,41 @@ def test_toy_architecture_is_registered_built_and_stepped(dtype):
     assert all(p.free == p.n_blocks for p in core.pools.pools)
 
 
+def test_the_state_mixer_through_the_entry_point_and_the_prefix_cache_refusal():
+    """The toy architecture through `LocalModel.generate`: requests with state in their slots run under the
+    scheduler (graphs off by the parts' own declaration) and give the tokens of the plain reference. With
+    `prefix_cache` the engine refuses to load: cached pages do not bring a mixer's running state back, and a
+    request that started from them would compute with empty state (the reference snapshots such state,
+    src/provider/local/engine/scheduler.rs:813-830; this engine says no)."""
+    _register_toy_parts()
+    from cuca_b200 import BatchingConfig, LocalModel, LocalModelConfig, RandomWeights
+    from cuca_b200.cache.pages import StatefulCacheError
+    from cuca_b200.config.registry import build_spec
+    from cuca_b200.models.model import Model
+    from cuca_b200.weights.loader import RandomSource
+
+    def config(prefix_cache):
+        return LocalModelConfig(model_config=TOY, random_weights=RandomWeights(seed=11, std=0.08), dtype="float32",
+                                kv_block_size=8, batching=BatchingConfig(max_sequences=3, prefix_cache=prefix_cache,
+                                                                         max_step_tokens=32, prefill_chunk=16))
+
+    with pytest.raises(StatefulCacheError, match="prefix_cache"):
+        LocalModel.load(config(True))
+    m = LocalModel.load(config(False))
+    assert not m.backend.use_graphs
+    source = RandomSource(Model(build_spec(TOY)).tensor_needs(), seed=11, std=0.08, device="cpu", dtype=torch.bfloat16)
+    weights = {n: source.read(n) for n in source.shapes()}
+    prompts = [tiny.random_tokens(n, TOY["vocab"], seed=70 + n) for n in (5, 40, 23)]
+    outs = m.generate(prompts, max_tokens=10, temperature=0.0)
+    for prompt, out in zip(prompts, outs):
+        ref = _toy_reference(weights, prompt + out.tokens)
+        for i, tok in enumerate(out.tokens):
+            row = ref[len(prompt) - 1 + i]
+            assert float(row.max() - row[tok]) <= 2e-5 * float(row.abs().max()), f"token {i} is not the maximum"
+    with pytest.raises(StatefulCacheError, match="rolled back"):
+        m.core.pools.truncate(m.core.pools.new_seq(), 0)
+
+
 # ------------------------------------------------------------------------------------------ other arrangements
 def _register_parallel_parts():
     from cuca_b200.config.registry import register_architecture

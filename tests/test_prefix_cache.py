@@ -134,6 +134,68 @@ def test_random_orders_keep_the_books_straight():
     assert kv.pools[0].free == 24
 
 
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_hits_bring_the_right_tokens_through_heavy_eviction(seed):
+    """Hundreds of different prompts through a pool of 32 pages: names are taken out of the pool's name table all
+    the time (its probe runs are closed up on removal). The test remembers which tokens every page was last filled
+    with: a prefix hit must hand out pages that hold exactly the prompt's tokens, a prompt that was just finished
+    must be found whole, and a hit is never longer than what some finished prompt shares with it."""
+    rng = random.Random(seed)
+    bs, n_blocks = 4, 32
+    kv = pools(n_blocks=n_blocks, bs=bs)
+    content = {}                                 # page -> the tokens it was last filled with
+    finished = []
+    stems = [[rng.randrange(9) for _ in range(24)] for _ in range(6)]
+
+    def run(prompt, finish=True):
+        s = kv.new_seq_with_prefix(prompt)
+        shared = s.length // bs
+        assert s.length % bs == 0 and s.length <= len(prompt) - 1
+        for i in range(shared):
+            assert content[s.tables[0][i]] == tuple(prompt[i * bs:(i + 1) * bs]), "a hit handed out another prompt's page"
+        longest = max((next((k for k in range(min(len(f), len(prompt))) if f[k] != prompt[k]), min(len(f), len(prompt)))
+                       for f in finished), default=0)
+        assert s.length <= longest // bs * bs, "a hit is longer than any finished prompt shares"
+        try:
+            kv.reserve(s, len(prompt))
+        except PoolExhausted:
+            kv.release(s)
+            return None
+        s.length = len(prompt)
+        for i in range(shared, len(s.tables[0])):
+            content[s.tables[0][i]] = tuple(prompt[i * bs:(i + 1) * bs])
+        if finish:
+            kv.finish(s, prompt)
+            finished.append(list(prompt))
+            return None
+        return s
+
+    held = []
+    for step in range(1500):
+        stem = rng.choice(stems)
+        prompt = stem[:rng.randrange(1, 25)] + [rng.randrange(9) for _ in range(rng.randrange(0, 9))]
+        if rng.random() < 0.15 and len(held) < 3:
+            s = run(prompt, finish=False)
+            if s is not None:
+                held.append((s, prompt))
+        else:
+            run(prompt)
+            if rng.random() < 0.5 and len(prompt) > bs:   # just finished: found whole (below its last token)
+                again = kv.new_seq_with_prefix(prompt)
+                assert again.length == (len(prompt) - 1) // bs * bs
+                kv.release(again)
+        if held and rng.random() < 0.3:
+            s, prompt = held.pop(rng.randrange(len(held)))
+            kv.finish(s, prompt)
+            finished.append(list(prompt))
+        if step % 50 == 0:
+            kv.check()
+    for s, prompt in held:
+        kv.finish(s, prompt)
+    kv.check()
+    assert kv.pools[0].free == n_blocks
+
+
 # ------------------------------------------------------------------ the scheduler's use of it
 def make(n_blocks=16, prefix_cache=True):
     kv = KvPools([GroupLayout(2, 16, None, (0,), n_blocks)], 4)

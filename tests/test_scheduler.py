@@ -188,3 +188,16 @@ def test_seeded_requests_restart_their_generator():
     sch.run_until_done()
     states = {i: st for i, _, st in be.started}
     assert states[0] == states[1] == 123 and states[2] == 42
+
+
+def test_prefix_cache_is_refused_when_a_mixer_keeps_state():
+    """Pools whose model also keeps per-request state cannot serve requests from cached pages."""
+    from cuca_b200.cache.pages import GroupLayout, KvPools, StateSlots, StatefulCacheError
+    from cuca_b200.engine.scheduler import Scheduler, SchedulerConfig
+    pools = KvPools([GroupLayout(1, 16, None, (0,), 8)], 4)
+    pools.stateful = True
+    with pytest.raises(StatefulCacheError, match="prefix_cache"):
+        Scheduler(pools, StateSlots(2), None, SchedulerConfig(prefix_cache=True))
+    Scheduler(pools, StateSlots(2), None, SchedulerConfig(prefix_cache=False))
+    with pytest.raises(StatefulCacheError, match="rolled back"):
+        pools.truncate(pools.new_seq(), 0)
