@@ -2,6 +2,7 @@
 """Decode and prefill throughput of the engine on one B200, on the Llama-3.1-8B shape with random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl reference]
+                    [--shape llama-3.1-8b | llama-2-13b | llama-3.2-1b]
 
 One JSON line: `value` is decoded tokens per second at batch 8 (K captured decode steps back to back on the
 device, timed with CUDA events); `e2e` is the same through the public entry point (`LocalModel.generate`, host
@@ -9,6 +10,12 @@ token ids in and out every step); `prefill` is one 2,048-token prompt; `roofline
 step must read (weights once, the live requests' keys and values) with the measured copy bandwidth; `points`
 holds batch 1 and 64. A step reads 16 GB of weights, far more than the 126 MB L2, so no flush is needed between
 steps. For more than one GPU it prints one line saying so and exits with 2: this engine runs on one GPU.
+
+`--shape llama-2-13b` measures the same line on the Llama-2-13B shape (40 key/value heads, context 4,096,
+2,048-token prompts, an explicit page pool for batch 64). `--shape llama-3.2-1b` runs the mixed workload of that
+shape instead: 64 requests with prompts of 16 to 2,048 random ids and 128 tokens each under continuous batching
+through `LocalModel.generate`; `value` is then generated tokens per second from submission to the last token,
+and `points.decode_b64` / `roofline` describe the steady decode step of all 64 at head size 64.
 """
 from __future__ import annotations
 
@@ -33,10 +40,30 @@ LLAMA_31_8B = {
                      "original_max_position_embeddings": 8192},
     "tie_word_embeddings": False,
 }
-CONTEXT = 8192
-PROMPT = 1024
+LLAMA_2_13B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 40, "hidden_size": 5120, "num_attention_heads": 40, "num_key_value_heads": 40,
+    "head_dim": 128, "intermediate_size": 13824, "vocab_size": 32000, "max_position_embeddings": 4096,
+    "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "rope_scaling": None, "tie_word_embeddings": False,
+}
+LLAMA_32_1B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 16, "hidden_size": 2048, "num_attention_heads": 32, "num_key_value_heads": 8,
+    "head_dim": 64, "intermediate_size": 8192, "vocab_size": 128256, "max_position_embeddings": 131072,
+    "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "tie_word_embeddings": True,
+}
+# name -> (config.json, label, context, prompt tokens of the decode points, seed of the random weights, rope in words)
+SHAPES = {
+    "llama-3.1-8b": (LLAMA_31_8B, "Llama-3.1-8B shape", 8192, 1024, 5,
+                     "theta 5e5, llama3 factor 8 low 1 high 4 original 8192"),
+    "llama-2-13b": (LLAMA_2_13B, "Llama-2-13B shape", 4096, 2048, 7, "theta 1e4, no scaling"),
+    "llama-3.2-1b": (LLAMA_32_1B, "Llama-3.2-1B shape", 8192, 1024, 6,
+                     "theta 5e5, llama3 factor 32 low 1 high 4 original 8192"),
+}
 PREFILL_TOKENS = 2048
-SEED = 5
 
 
 def peaks() -> dict:
@@ -116,6 +143,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the model has (reported)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    ap.add_argument("--shape", default="llama-3.1-8b", choices=sorted(SHAPES))
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -139,15 +167,25 @@ def main() -> int:
     from cuca_b200.engine.scheduler import DECODE, Request
     from cuca_b200.kernels import library
 
-    cfg = dict(LLAMA_31_8B)
+    base_cfg, label, CONTEXT, PROMPT, SEED, rope_words = SHAPES[args.shape]
+    mixed = args.shape == "llama-3.2-1b"
+    cfg = dict(base_cfg)
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
     layers = cfg["num_hidden_layers"]
     pk = peaks()
-    max_batch = args.batch if args.no_points else max(64, args.batch)
-    per_request = PROMPT + 2 * (args.steps + args.warmup) + 64 + 2 * (-(-max(64, args.batch) * PROMPT // PREFILL_TOKENS))
-    kv_tokens = max(CONTEXT + 16, max_batch * (-(-per_request // 16) * 16) + PREFILL_TOKENS + 64)
+    max_batch = args.batch if args.no_points and not mixed else max(64, args.batch)
+    point_steps = min(args.steps, 64)  # steps of the batch-1 and batch-64 points
+
+    def pages_for(batch, steps):
+        """Positions the pool must hold for `batch` requests that decode `steps` timed steps after their prompt
+        (requests that finish their prompt early decode while the others are still being prefilled)."""
+        per_request = PROMPT + steps + args.warmup + 2 * (-(-batch * PROMPT // PREFILL_TOKENS)) + 48
+        return batch * (-(-per_request // 16) * 16)
+
+    kv_tokens = max(CONTEXT + 16, pages_for(args.batch, args.steps), 0 if args.no_points else pages_for(64, point_steps),
+                    64 * (2048 + 128 + 16) if mixed else 0) + PREFILL_TOKENS + 64
     t0 = time.perf_counter()
     model = LocalModel.load(LocalModelConfig(
         model_config=cfg, random_weights=RandomWeights(seed=SEED, std=0.02), dtype="bfloat16", context_length=CONTEXT,
@@ -199,7 +237,7 @@ def main() -> int:
         # requests that finish their prompt early decode while the others are still being prefilled: give every
         # request room for that, and never spin if the scheduler stops making progress
         turns_needed = -(-batch * PROMPT // sched.cfg.max_step_tokens) + 2
-        seqs = [sched.submit(Request(p, max_tokens=2 * (steps + warmup) + turns_needed + 8, temperature=0.0))
+        seqs = [sched.submit(Request(p, max_tokens=steps + warmup + 2 * turns_needed + 8, temperature=0.0))
                 for p in prompts(batch, PROMPT)]
         for _ in range(4 * turns_needed + 16):
             if all(s.phase == DECODE for s in seqs):
@@ -235,62 +273,102 @@ def main() -> int:
         mean_ctx = ctx0 + (steps - 1) / 2.0 + 1
         return ms / steps, mean_ctx, g
 
-    ms_step, mean_ctx, g8 = decode_device(args.batch, args.steps, args.warmup)
-    value = args.batch / (ms_step / 1e3)
-    step_bytes = model.core.model.weight_bytes() + args.batch * mean_ctx * core.cache.bytes_per_token()
-    achieved = step_bytes / (ms_step / 1e3) / 1e9
-    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(step_bytes),
-                "peaks": pk["source"]}
+    def roofline_of(batch, ms, ctx):
+        step_bytes = model.core.model.weight_bytes() + batch * ctx * core.cache.bytes_per_token()
+        achieved = step_bytes / (ms / 1e3) / 1e9
+        return {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(step_bytes), "peaks": pk["source"]}
+
+    points, fracs = {}, {}
+    if mixed:
+        # ---------------------------------------------------- 64 requests of mixed length, continuous batching
+        n_req, new_tokens = 64, 128
+        lengths = rng.integers(16, 2049, size=n_req).tolist()
+        ps = [rng.integers(0, vocab, size=n).tolist() for n in lengths]
+        model.generate(ps[:4], max_tokens=4, temperature=0.0)  # warm-up: kernels configured, first graphs captured
+        done_at = []
+        steps0 = core.stepper.steps
+        staging = core.stepper._staging
+        h2d0, d2h0 = staging.bytes_sent + backend.h2d_bytes, backend.d2h_bytes
+        torch.cuda.synchronize()
+        w = time.perf_counter()
+        outs = model.generate(ps, max_tokens=new_tokens, temperature=0.0,
+                              on_token=lambda seq, tok: done_at.append(time.perf_counter()))
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - w
+        windows.append((w, time.perf_counter()))
+        generated = sum(len(o.tokens) for o in outs)
+        assert generated == n_req * new_tokens and all(o.report.finish_reason == "length" for o in outs)
+        mixed_steps = core.stepper.steps - steps0
+        value = generated / wall
+        ms_step, mean_ctx, g8 = decode_device(64, point_steps, args.warmup)
+        roofline = roofline_of(64, ms_step, mean_ctx)
+        points["decode_b64"] = round(64 / (ms_step / 1e3), 1)
+        fracs["decode_b64"] = roofline["frac"]
+        e2e = {"value": round(value, 1), "unit": "tokens/s", "seconds": round(wall, 4), "steps": mixed_steps,
+               "prompt_tokens": int(sum(lengths)), "generated_tokens": generated,
+               "h2d_bytes_per_step": round((staging.bytes_sent + backend.h2d_bytes - h2d0) / max(1, mixed_steps)),
+               "d2h_bytes_per_step": round((backend.d2h_bytes - d2h0) / max(1, mixed_steps))}
+        metric = ("generated tokens/s, %s, bf16, 64 requests with prompts of 16..2048 ids and 128 tokens each, "
+                  "continuous batching, submission to last token" % label)
+        batch_of_value, steps_of_value = 64, mixed_steps
+        ms_per_step = wall / max(1, mixed_steps) * 1e3
+    else:
+        ms_step, mean_ctx, g8 = decode_device(args.batch, args.steps, args.warmup)
+        value = args.batch / (ms_step / 1e3)
+        roofline = roofline_of(args.batch, ms_step, mean_ctx)
+
+        # -------------------------------------------------------- decode, end to end through generate()
+        # Requests whose prompt is done decode while later prompts are still prefilled; the clock runs on the LAST
+        # request's tokens, which are all produced by steps that decode the whole batch, and every request gets
+        # enough tokens to still be running then.
+        stamps = []
+        turns = -(-args.batch * PROMPT // sched.cfg.max_step_tokens) + 2
+        last_id = sched._next_id + args.batch - 1
+
+        def on_token(seq, tok):
+            if seq.id == last_id:
+                stamps.append(time.perf_counter())
+
+        ps = prompts(args.batch, PROMPT)
+        w = time.perf_counter()
+        model.generate(ps, max_tokens=args.warmup + args.steps + 1 + turns, temperature=0.0, on_token=on_token)
+        windows.append((w, time.perf_counter()))
+        e2e_s = stamps[args.warmup + args.steps] - stamps[args.warmup]
+        bucket = g8.bucket
+        e2e = {"value": round(args.batch * args.steps / e2e_s, 1), "unit": "tokens/s",
+               "h2d_bytes_per_step": 3 * bucket * 4, "d2h_bytes_per_step": (bucket + 1) * 4,
+               "ms_per_step": round(e2e_s / args.steps * 1e3, 4)}
+        if not args.no_points:
+            for b in (1, 64):
+                ms_b, ctx_b, _ = decode_device(b, point_steps, args.warmup)
+                points[f"decode_b{b}"] = round(b / (ms_b / 1e3), 1)
+                fracs[f"decode_b{b}"] = roofline_of(b, ms_b, ctx_b)["frac"]
+        metric = "decode tokens/s, %s, bf16, batch %d, %d-token prompts" % (label, args.batch, PROMPT)
+        batch_of_value, steps_of_value = args.batch, args.steps
+        ms_per_step = ms_step
     launches_per_step = getattr(g8, "launches", 0)
-
-    # ------------------------------------------------------------ decode, end to end through generate()
-    # Requests whose prompt is done decode while later prompts are still prefilled; the clock runs on the LAST
-    # request's tokens, which are all produced by steps that decode the whole batch, and every request gets
-    # enough tokens to still be running then.
-    stamps = []
-    turns = -(-args.batch * PROMPT // sched.cfg.max_step_tokens) + 2
-    last_id = sched._next_id + args.batch - 1
-
-    def on_token(seq, tok):
-        if seq.id == last_id:
-            stamps.append(time.perf_counter())
-
-    ps = prompts(args.batch, PROMPT)
-    w = time.perf_counter()
-    model.generate(ps, max_tokens=args.warmup + args.steps + 1 + turns, temperature=0.0, on_token=on_token)
-    windows.append((w, time.perf_counter()))
-    e2e_s = stamps[args.warmup + args.steps] - stamps[args.warmup]
-    bucket = g8.bucket
-    e2e = {"value": round(args.batch * args.steps / e2e_s, 1), "unit": "tokens/s",
-           "h2d_bytes_per_step": 3 * bucket * 4, "d2h_bytes_per_step": bucket * 4,
-           "ms_per_step": round(e2e_s / args.steps * 1e3, 4)}
-
-    points = {}
-    if not args.no_points:
-        for b in (1, 64):
-            ms_b, _, _ = decode_device(b, min(args.steps, 64), args.warmup)
-            points[f"decode_b{b}"] = round(b / (ms_b / 1e3), 1)
+    step_bytes = roofline["bytes_per_step"]
     clocks.stop()
 
     line = {
-        "metric": "decode tokens/s, Llama-3.1-8B shape, bf16, batch %d, 1024-token prompts" % args.batch,
-        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic: seeded random token ids, random weights N(0, 0.02) seed 5",
+        "metric": metric,
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps_of_value, "warmup": args.warmup,
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random token ids, random weights N(0, 0.02) seed %d" % SEED,
         "config": {
-            "model": "Llama-3.1-8B shape", "layers": layers, "layers_of_model": full_layers,
+            "model": label, "layers": layers, "layers_of_model": full_layers,
             "hidden_size": E, "heads": nh, "kv_heads": nkv, "head_dim": d, "intermediate_size": ff,
-            "vocab_size": vocab, "rms_norm_eps": cfg["rms_norm_eps"],
-            "rope": "theta 5e5, llama3 factor 8 low 1 high 4 original 8192",
-            "global_batch": args.batch, "seq_len": CONTEXT, "prompt_tokens": PROMPT, "kv_block_size": 16,
-            "decode_context": round(mean_ctx, 1), "prefill_tokens": PREFILL_TOKENS,
+            "vocab_size": vocab, "rms_norm_eps": cfg["rms_norm_eps"], "rope": rope_words,
+            "global_batch": batch_of_value, "seq_len": CONTEXT, "prompt_tokens": "16..2048" if mixed else PROMPT,
+            "kv_block_size": 16, "decode_context": round(mean_ctx, 1), "prefill_tokens": PREFILL_TOKENS,
             "l2": "no flush: a step reads %.1f GB, far above the 126 MB L2" % (step_bytes / 1e9),
             "parallelism": "1 GPU",
         },
-        "e2e": e2e, "gpu_launches": int(launches_per_step * args.steps), "launches_per_step": launches_per_step,
+        "e2e": e2e, "gpu_launches": int(launches_per_step * (point_steps if mixed else args.steps)),
+        "launches_per_step": launches_per_step,
         "clocks": clocks.summary(windows), "prefill": prefill, "roofline": roofline, "points": points,
-        "load_seconds": round(load_s, 1), "impl": "ours",
+        "points_frac": fracs, "load_seconds": round(load_s, 1), "impl": "ours",
     }
     print(json.dumps(line))
     return 0

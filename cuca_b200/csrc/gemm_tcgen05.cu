@@ -881,3 +881,36 @@ CUCA_API int cuca_gemm_tc_partial(const void* A, const void* W, float* partial, 
   return gemm_tc_impl(A, W, nullptr, partial, CUCA_F32, M, N, K, lda, N, EPI_PARTIAL, nullptr, 0, nullptr, 0,
                       max_slices, n_slices, err, stream);
 }
+
+
+// ------------------------------------------------------------------ a wait that runs out (for the tests)
+namespace {
+__global__ void wait_probe_kernel(unsigned long long limit_ns, int* err, int* report) {
+  __shared__ __align__(8) uint64_t bars[2];
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bars[0], 1);
+    mbar_init(&bars[1], 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  // two roles, as in the contraction: each waits for a phase that nothing ever completes. The first to run out
+  // of time records the error and raises the CTA's abort flag; the other sees the flag and gives up too.
+  if (threadIdx.x == 0) report[0] = mbar_wait(&bars[0], 0, err, &abort_flag, limit_ns) ? 1 : 0;
+  if (threadIdx.x == 32) report[1] = mbar_wait(&bars[1], 0, err, &abort_flag, 1000ull * limit_ns) ? 1 : 0;
+  __syncthreads();
+  if (threadIdx.x == 0) report[2] = abort_flag;
+}
+}  // namespace
+
+// The kernels of this library never wait without a limit: a wait that runs out records CUCA_ERR_WAIT_TIMEOUT in
+// the error word, tells the CTA's other roles to give up, and the kernel returns. This entry shows that path on
+// its own: two threads wait (for `limit_ns`, and for a thousand times that) on barriers nobody arrives at.
+// report[0..1]: whether the waits succeeded (both 0), report[2]: the abort flag (1).
+CUCA_API int cuca_wait_probe(unsigned long long limit_ns, int* err, int* report, cudaStream_t stream) {
+  CUCA_REQUIRE(limit_ns > 0 && limit_ns <= 100000000ull, "wait_probe: a limit of %llu ns (at most 0.1 s)", limit_ns);
+  wait_probe_kernel<<<1, 64, 0, stream>>>(limit_ns, err, report);
+  CUCA_CHECK_LAUNCH("wait_probe");
+  return 0;
+}

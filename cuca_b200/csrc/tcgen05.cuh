@@ -38,16 +38,17 @@ __device__ __forceinline__ unsigned long long global_ns() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait: false if the phase did not complete in WAIT_LIMIT_NS (the error word is set) or if another
+// Bounded wait: false if the phase did not complete in `limit_ns` (the error word is set) or if another
 // role of this CTA gave up (`abort` is set).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, volatile int* abort) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, volatile int* abort,
+                                          unsigned long long limit_ns = WAIT_LIMIT_NS) {
   if (mbar_try_wait(bar, parity)) return true;
   unsigned long long t0 = global_ns();
   unsigned spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 63u) == 0) {
       if (*abort) return false;
-      if (global_ns() - t0 > WAIT_LIMIT_NS) {
+      if (global_ns() - t0 > limit_ns) {
         if (err) atomicExch(err, CUCA_ERR_WAIT_TIMEOUT);
         *abort = 1;
         return false;

@@ -69,6 +69,8 @@ class GpuBackend:
         self.graph_steps = 0
         self.eager_steps = 0
         self.last_graph = None  # the captured step that ran last
+        self.h2d_bytes = 0  # bytes of step inputs copied to the device (besides the step function's own uploads)
+        self.d2h_bytes = 0  # bytes of sampled tokens (and the error word) read back
 
     def start(self, seq: Sequence_) -> None:
         """A request takes its slot: clear its state, set its sampling constants and its generator."""
@@ -96,6 +98,8 @@ class GpuBackend:
         g.load_rows(tokens, starts, slots)
         g.replay()
         self.last_graph = g
+        self.h2d_bytes += 4 * g.meta.numel()
+        self.d2h_bytes += 4 * g.sampled.numel()
         out = g.sampled.tolist()  # the one synchronisation of a step; its last word is the device error word
         if out[g.bucket]:
             self.core.rt.raise_device_error(out[g.bucket])  # before anything is applied: the step is lost
@@ -157,6 +161,8 @@ class GpuBackend:
             ops.suppress_tokens(logits, self.suppress)
         ops.sample(logits, self.temperature, self.top_k, self.top_p, self.rng, slot_of_row, out, scratch)
         tokens = out.tolist()  # the one synchronisation of a step
+        self.h2d_bytes += 4 * len(rows)
+        self.d2h_bytes += 4 * len(rows) + 4
         self.core.rt.check_device_errors()
         return tokens
 

@@ -96,6 +96,7 @@ class _Staging:
         self.bufs = [torch.empty(ints, dtype=torch.int32).pin_memory() for _ in range(n)]
         self.events = [None] * n
         self.i = 0
+        self.bytes_sent = 0  # host-to-device bytes of every upload so far
 
     def take(self, ints: int = 0) -> torch.Tensor:
         """The next pinned buffer (at least `ints` long), free to be written."""
@@ -111,6 +112,7 @@ class _Staging:
         """Copy the first `n` integers of the buffer `take` returned to the device."""
         i = self.i
         self.i = (self.i + 1) % len(self.bufs)
+        self.bytes_sent += 4 * n
         dev = torch.empty(n, dtype=torch.int32, device=self.device)
         dev.copy_(self.bufs[i][:n], non_blocking=True)
         ev = torch.cuda.Event()

@@ -624,3 +624,32 @@ def test_attention_plan_on_the_device(dev, n_req, longest, tile):
     else:
         assert got == [(a, b) for a, b, _ in want]
     assert ops.tile_rows(0) == 64 and ops.tile_rows(1) == 128
+
+
+def test_a_bounded_wait_that_runs_out_returns_an_error_and_leaves_the_library_usable(dev):
+    """Every wait inside a kernel has a limit. Here two roles of one CTA wait for 1 ms and for 1 s on barriers that
+    nobody arrives at: the first runs out, records error 3 in the error word and raises the CTA's abort flag; the
+    second gives up on seeing the flag long before its own limit; the kernel returns, the host reads the error as
+    `DeviceFault`, and the next kernel runs as if nothing had happened."""
+    import time
+    from cuca_b200.kernels import library, ops
+    from cuca_b200.runtime import DeviceFault, Runtime
+    rt = Runtime("cuda:0", torch.bfloat16)
+    report = torch.full((3,), -1, dtype=torch.int32, device=dev)
+    lib = library.load()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    library.check(lib.cuca_wait_probe(1_000_000, rt.err.data_ptr(), report.data_ptr(),
+                                      torch.cuda.current_stream().cuda_stream), "wait_probe")
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 0.5, "the second role must give up on the flag, not wait out its own second"
+    assert report.tolist() == [0, 0, 1]
+    with pytest.raises(DeviceFault, match="bounded wait"):
+        rt.check_device_errors()
+    rt.check_device_errors()  # the word was cleared
+    a = torch.randn(8, 256, device=dev).bfloat16()
+    w = torch.randn(64, 256, device=dev).bfloat16()
+    out = rt.linear(a, w)
+    torch.cuda.synchronize()
+    assert torch.allclose(out.float(), a.float() @ w.float().T, atol=0.2, rtol=2e-2)
+    rt.check_device_errors()
