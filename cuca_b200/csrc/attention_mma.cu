@@ -127,7 +127,13 @@ attn_mma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tmK, con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int G = p.nh / p.nkv;
   pdl_trigger();
-  pdl_wait();
+  // The fused, TMA-fed decode form reads nothing the kernel before it (the q/k/v projection) writes until it adds
+  // that projection's slices: the rows' positions and slots were copied before the step's first kernel ran, the
+  // page tables were brought up to date before that, and every key it copies was written by an earlier step
+  // (the row's own key comes from registers). So its lookups and its first copies go out before the dependency
+  // wait and overlap the projection's tail. Every other form waits here.
+  constexpr bool EARLY = FUSED && TMA;
+  if (!EARLY) pdl_wait();
 
   // ---------------------------------------------------------------- what this CTA and warp own
   int seq, kvh, range_lo, range_hi;   // keys [range_lo, range_hi) of request `seq`
@@ -305,6 +311,7 @@ attn_mma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tmK, con
     }
   };
   float4 pre_a[4], pre_b[4], pre_c = make_float4(1.f, 1.f, 1.f, 1.f), pre_s = make_float4(0.f, 0.f, 0.f, 0.f);
+  auto preload = [&]() {
   if (FUSED && f_vec && (int)threadIdx.x < f_items) {
     int ca, hh, off;
     f_item(threadIdx.x, ca, hh, off);
@@ -321,6 +328,8 @@ attn_mma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tmK, con
       pre_s = *reinterpret_cast<const float4*>(p.sin_t + (size_t)P * f_half + off);
     }
   }
+  };
+  if (!EARLY) preload();
 
   if (TMA) {
     if (threadIdx.x == 0) w_abort = 0;
@@ -364,6 +373,10 @@ attn_mma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tmK, con
     }
   }
 
+  if (EARLY) {
+    pdl_wait();  // from here on the projection's slices are read
+    preload();
+  }
   // ---------------------------------------------------------------- fused form: q (and k, v) from the K slices
   __nv_bfloat16* q_s = TMA ? reinterpret_cast<__nv_bfloat16*>(ring_base + S::RING_BYTES)
                            : smem + (size_t)STAGES * 2 * S::TILE_ELEMS;  // [16][RS]: the group's rotated query heads
