@@ -144,6 +144,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--shape", default="llama-3.1-8b", choices=sorted(SHAPES))
+    ap.add_argument("--decode-only", action="store_true",
+                    help="with --shape llama-3.2-1b: the plain decode line at --batch instead of the mixed workload")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -168,7 +170,7 @@ def main() -> int:
     from cuca_b200.kernels import library
 
     base_cfg, label, CONTEXT, PROMPT, SEED, rope_words = SHAPES[args.shape]
-    mixed = args.shape == "llama-3.2-1b"
+    mixed = args.shape == "llama-3.2-1b" and not args.decode_only
     cfg = dict(base_cfg)
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
