@@ -36,7 +36,6 @@
 
 namespace {
 
-constexpr int NTHREADS = 224;  // warps 0 and 6 producers, warp 1 MMA, warps 2..5 epilogue
 constexpr int NPROD = 2;       // one thread requests about 16 KB per 0.45 us: too little for an SM's share of the memory's rate
 
 struct Params {
@@ -49,6 +48,7 @@ struct Params {
   int ldo;
   int epilogue;
   int out_f32;
+  int tile_rows; // rows of the 128-row operand one tile covers: 128, or 256 for the tall form (two row blocks)
   int tiles_a;   // tiles along the 128-row operand
   int tiles;     // all tiles
   int ksteps;    // K steps per tile
@@ -67,9 +67,16 @@ constexpr int STAGING_BUF = 32 * 128;  // 32 rows of 128 bytes
 
 // SWAP: weight rows on the 128 lanes, BN tokens as columns. Otherwise tokens on the lanes, 256 weight rows
 // (SwiGLU: 128 gate + 128 up) as columns.
-template <int BN, bool DUAL, bool SWAP>
+// TALL (many tokens only): a tile is 256 tokens x 256 weight rows, two row blocks that share every stage's weight
+// tile. A CTA then takes in 64 KB per K step for twice the arithmetic (32 KB per 128 x 256 block instead of 48):
+// the main loop of the 128-row form runs at the pace of its loads (64 bytes per clock from L2 into an SM), this
+// one at the pace of its MMAs. The two accumulators fill all 512 TMEM columns, so a tile's epilogue (eight warps,
+// one per 32 rows of either block) no longer runs under the next tile's main loop.
+template <int BN, bool DUAL, bool SWAP, bool TALL = false>
 struct Cfg {
-  static constexpr int A_BYTES = TILE_A * TILE_K * 2 * ((SWAP && DUAL) ? 2 : 1);
+  static_assert(!TALL || (!SWAP && BN == 256), "the tall form is for many tokens and 256 weight rows");
+  static constexpr int ROW_BLOCKS = TALL ? 2 : 1;
+  static constexpr int A_BYTES = TILE_A * TILE_K * 2 * ((SWAP && DUAL) || TALL ? 2 : 1);
   static constexpr int B_ROWS = BN;  // many tokens: 256 weight rows a stage, or 128 for launches of column pieces up to 128 wide
   static constexpr int B_BYTES = B_ROWS * TILE_K * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -81,11 +88,16 @@ struct Cfg {
   static constexpr int SMEM_BUDGET = (SWAP ? ((BN == 64 && DUAL && CUCA_SWAP_SMEM_KB < 124) ? 124 : CUCA_SWAP_SMEM_KB) : 192) * 1024;
   static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) > 12 ? 12 : (SMEM_BUDGET / STAGE_BYTES);
   static constexpr int MMA_N = BN;                                 // N of one tcgen05.mma
-  static constexpr int NCOLS = SWAP ? BN * (DUAL ? 2 : 1) : BN;    // accumulator columns of one tile
-  static constexpr int TMEM_COLS = 2 * NCOLS < 32 ? 32 : 2 * NCOLS;  // two accumulators
+  static constexpr int NCOLS = (SWAP ? BN * (DUAL ? 2 : 1) : BN) * ROW_BLOCKS;  // accumulator columns of one tile
+  static constexpr int ACC_BUFS = TALL ? 1 : 2;                      // tiles whose accumulators TMEM holds at once
+  static constexpr int TMEM_COLS = ACC_BUFS * NCOLS < 32 ? 32 : ACC_BUFS * NCOLS;
+  static constexpr int EPI_WARPS = 4 * ROW_BLOCKS;
+  static constexpr int PROD2_WARP = 2 + EPI_WARPS;                   // the second producer's warp
+  static constexpr int THREADS = 32 * (PROD2_WARP + 1);              // warp 0 producer, warp 1 MMA, epilogue warps, producer
+  static constexpr int STAGING_BUFS = TALL ? 1 : 2;                  // staging buffers per epilogue warp
   static constexpr int OUT_COLS = SWAP ? BN : (DUAL ? BN / 2 : BN);  // output columns of one tile
   // many tokens: each epilogue warp stages its 32 rows x 128 bytes of output twice over for the copy engine
-  static constexpr int STAGING = SWAP ? 0 : 4 * 2 * STAGING_BUF;
+  static constexpr int STAGING = SWAP ? 0 : EPI_WARPS * STAGING_BUFS * STAGING_BUF;
   static constexpr int SMEM = STAGES * STAGE_BYTES + STAGING + 1024 /*alignment*/ + 512 /*barriers*/;
 };
 
@@ -108,7 +120,7 @@ struct SegmentWalk {
     tile_cursor = blockIdx.x;
   }
   __device__ void origin(Segment& s) const {
-    s.a0 = (s.tile % p.tiles_a) * TILE_A;
+    s.a0 = (s.tile % p.tiles_a) * p.tile_rows;
     s.b0 = (s.tile / p.tiles_a) * out_cols;
     s.w = out_cols;
   }
@@ -252,7 +264,7 @@ __device__ __forceinline__ void store16(const Params& p, int a0, int b0, int lan
 // map (no bank conflicts), and the copy engine stores the 32 x 128-byte box, or adds it into the 32-bit stream,
 // clipped at the matrix's edges. A thread writing its own row straight to global memory instead touches one line
 // per lane and instruction: measured, 13 us per tile of the output projection against 26 us of main loop.
-template <bool DUAL>
+template <bool DUAL, int BUFS = 2>
 __device__ __forceinline__ void tma_epilogue(const Params& p, const CUtensorMap* tmO, uint32_t acc, int a0, int b0,
                                              int width, bool with_bias, int quarter, int lane, uint8_t* staging,
                                              int& chunk_no) {
@@ -262,8 +274,8 @@ __device__ __forceinline__ void tma_epilogue(const Params& p, const CUtensorMap*
   const int sw = lane & 7;
 #pragma unroll 1
   for (int c = 0; c < width; c += ch) {
-    uint8_t* row = my_row + (chunk_no & 1) * STAGING_BUF;
-    if (lane == 0) bulk_wait_read<1>();  // the copy that last used this buffer has read it
+    uint8_t* row = my_row + (chunk_no % BUFS) * STAGING_BUF;
+    if (lane == 0) bulk_wait_read<BUFS - 1>();  // the copy that last used this buffer has read it
     __syncwarp();
 #pragma unroll 1
     for (int h = 0; h < ch; h += 16) {
@@ -301,7 +313,7 @@ __device__ __forceinline__ void tma_epilogue(const Params& p, const CUtensorMap*
     __syncwarp();
     if (lane == 0) {
       if (y0 < p.M && b0 + c < p.N) {
-        const void* src = staging + (chunk_no & 1) * STAGING_BUF;
+        const void* src = staging + (chunk_no % BUFS) * STAGING_BUF;
         if (p.epilogue == EPI_RESIDUAL) tma_reduce_add_2d(tmO, src, b0 + c, y0);
         else tma_store_2d(tmO, src, b0 + c, y0);
       }
@@ -311,11 +323,15 @@ __device__ __forceinline__ void tma_epilogue(const Params& p, const CUtensorMap*
   }
 }
 
-template <int BN, bool DUAL, bool SWAP>
-__global__ void __launch_bounds__(NTHREADS, 1)
+template <int N_THREADS>
+__device__ __forceinline__ void epilogue_sync_n() { asm volatile("bar.sync 1, %0;" ::"n"(N_THREADS) : "memory"); }
+
+template <int BN, bool DUAL, bool SWAP, bool TALL = false>
+__global__ void __launch_bounds__((Cfg<BN, DUAL, SWAP, TALL>::THREADS), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmO, const Params p) {
-  using C = Cfg<BN, DUAL, SWAP>;
+  using C = Cfg<BN, DUAL, SWAP, TALL>;
+  auto epilogue_sync = [] { epilogue_sync_n<32 * C::EPI_WARPS>(); };
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* staging = smem + C::STAGES * C::STAGE_BYTES;  // 1024-byte aligned: the stages are multiples of 1024 bytes
@@ -337,7 +353,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full[b], 1);
-      mbar_init(&tmem_empty[b], 4);  // one arrival per epilogue warp
+      mbar_init(&tmem_empty[b], C::EPI_WARPS);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     *last_flag = 0;
@@ -371,10 +387,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   };
   auto load_activations = [&](uint8_t* st, uint64_t* bar, const Segment& s, int kc) {
     if (SWAP) tma_load_2d(st + C::A_BYTES, &tmB, bar, kc, s.b0);
-    else tma_load_2d(st, &tmA, bar, kc, s.a0);
+    else {
+      tma_load_2d(st, &tmA, bar, kc, s.a0);
+      if (TALL) tma_load_2d(st + TILE_A * TILE_K * 2, &tmA, bar, kc, s.a0 + TILE_A);  // rows past M read as zeros
+    }
   };
 
-  if ((warp == 0 || warp == 6) && lane == 0) {
+  if ((warp == 0 || warp == C::PROD2_WARP) && lane == 0) {
     // ------------------------------------------------ producers: stages in turn (it mod NPROD)
     const int mine = warp == 0 ? 0 : 1;
     // the first ring of weight tiles is requested before waiting for the predecessor kernel
@@ -417,10 +436,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     int it = 0, seg = 0;
     bool ok = true;
     while (ok && walk.next(s)) {
-      const int buf = seg & 1;
+      const int buf = seg % C::ACC_BUFS;
       // a column piece is narrower than a tile (never with SwiGLU, whose tile is 128 gate and 128 up columns)
       const uint32_t idesc = instr_desc((SWAP || DUAL) ? C::MMA_N : s.w);
-      if (!mbar_wait(&tmem_empty[buf], ((seg >> 1) & 1) ^ 1, p.err, abort_flag)) break;
+      if (!mbar_wait(&tmem_empty[buf], ((seg / C::ACC_BUFS) & 1) ^ 1, p.err, abort_flag)) break;
       tc_fence_after();
       const uint32_t acc = tmem_base + buf * C::NCOLS;
       for (int ks = s.ks0; ks < s.ks1; ++ks, ++it) {
@@ -437,30 +456,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const uint64_t koff = (uint64_t)(k * UMMA_K * 2 >> 4);
           umma_bf16(acc, adesc + koff, bdesc + koff, idesc, accumulate);
           if (SWAP && DUAL) umma_bf16(acc + BN, adesc2 + koff, bdesc + koff, idesc, accumulate);
+          if (TALL) umma_bf16(acc + BN, adesc2 + koff, bdesc + koff, idesc, accumulate);  // the second row block
         }
         umma_commit(&empty[st]);
       }
       if (ok) umma_commit(&tmem_full[buf]);
       ++seg;
     }
-  } else if (warp >= 2 && warp <= 5) {
-    // ------------------------------------------------ epilogue: four warps, one TMEM lane per thread
+  } else if (warp >= 2 && warp < 2 + C::EPI_WARPS) {
+    // ------------------------------------------------ epilogue: four warps per row block, one TMEM lane per thread
     pdl_wait();
     const int quarter = warp & 3;               // the TMEM lanes this warp may read
-    const int lane_row = quarter * 32 + lane;   // row of the 128-row operand
-    const int eidx = (warp - 2) * 32 + lane;    // 0..127 among the epilogue threads
+    const int block = TALL ? (warp - 2) >> 2 : 0;  // which 128-row block of a tall tile
+    const int lane_row = quarter * 32 + lane;   // row within the block
+    const int eidx = (warp - 2) * 32 + lane;    // 0.. among the epilogue threads
     SegmentWalk walk(p, C::OUT_COLS);
     Segment s;
     int seg = 0, chunk_no = 0;
     while (walk.next(s)) {
-      const int buf = seg & 1;
-      // one thread waits and tells the others, so all 128 leave the loop together (they share named barriers)
-      if (eidx == 0) seg_ok[buf] = mbar_wait(&tmem_full[buf], (seg >> 1) & 1, p.err, abort_flag) ? 1 : 0;
+      const int buf = seg % C::ACC_BUFS;
+      // one thread waits and tells the others, so all leave the loop together (they share named barriers)
+      if (eidx == 0) seg_ok[buf] = mbar_wait(&tmem_full[buf], (seg / C::ACC_BUFS) & 1, p.err, abort_flag) ? 1 : 0;
       epilogue_sync();
       if (!seg_ok[buf]) break;
       tc_fence_after();
-      const int a0 = s.a0, b0 = s.b0;
-      const uint32_t acc = tmem_base + buf * C::NCOLS + ((uint32_t)(quarter * 32) << 16);
+      const int a0 = s.a0 + block * TILE_A, b0 = s.b0;
+      const uint32_t acc = tmem_base + buf * C::NCOLS + block * BN + ((uint32_t)(quarter * 32) << 16);
       if (SWAP && !DUAL && p.epilogue == EPI_PARTIAL) {
         // this K slice's partial sums go out as they are, [slice][token][feature]; whoever reads them adds them up
         float* dst = (float*)p.out + (size_t)s.part * p.M * p.ldo;
@@ -479,7 +500,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         __syncwarp();
         if (lane == 0) mbar_arrive(&tmem_empty[buf]);
       } else if (!SWAP && s.nparts == 1 && p.tma_out) {
-        tma_epilogue<DUAL>(p, &tmO, acc, a0, b0, s.w, true, quarter, lane, staging + (warp - 2) * (2 * STAGING_BUF), chunk_no);
+        tma_epilogue<DUAL, C::STAGING_BUFS>(p, &tmO, acc, a0, b0, s.w, true, quarter, lane,
+                                            staging + (warp - 2) * (C::STAGING_BUFS * STAGING_BUF), chunk_no);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tmem_empty[buf]);
@@ -509,8 +531,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         epilogue_sync();  // everyone has read the flag before it is written again
         if (!mine) break;
         __threadfence();  // the slices before this one have added their sums
-        tma_epilogue<false>(p, &tmO, acc, a0, b0, s.w, s.part == 0, quarter, lane, staging + (warp - 2) * (2 * STAGING_BUF),
-                            chunk_no);
+        tma_epilogue<false, C::STAGING_BUFS>(p, &tmO, acc, a0, b0, s.w, s.part == 0, quarter, lane,
+                                             staging + (warp - 2) * (C::STAGING_BUFS * STAGING_BUF), chunk_no);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) {
@@ -692,13 +714,13 @@ bool cuca_tensor_map_2d(const void* ptr, int elem_bytes, uint64_t rows, uint64_t
 }
 
 namespace {
-template <int BN, bool DUAL, bool SWAP>
+template <int BN, bool DUAL, bool SWAP, bool TALL = false>
 int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmO, const Params& p, int grid,
               cudaStream_t stream) {
-  using C = Cfg<BN, DUAL, SWAP>;
+  using C = Cfg<BN, DUAL, SWAP, TALL>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, DUAL, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, DUAL, SWAP, TALL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          C::SMEM);
     if (e != cudaSuccess) {
       cuca_set_error("gemm_tc: cannot reserve %d bytes of shared memory: %s", C::SMEM, cudaGetErrorString(e));
@@ -706,7 +728,7 @@ int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap&
     }
     configured = true;
   }
-  cuca_launch(gemm_tc_kernel<BN, DUAL, SWAP>, dim3(grid), dim3(NTHREADS), C::SMEM, stream, true, tmA, tmB, tmO, p);
+  cuca_launch(gemm_tc_kernel<BN, DUAL, SWAP, TALL>, dim3(grid), dim3(C::THREADS), C::SMEM, stream, true, tmA, tmB, tmO, p);
   CUCA_CHECK_LAUNCH("gemm_tc");
   return 0;
 }
@@ -754,11 +776,27 @@ static int gemm_tc_impl(const void* A, const void* W, const void* bias, void* ou
   p.err = err; p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.epilogue = epilogue; p.out_f32 = out_dtype == CUCA_F32;
   const int out_cols = swap ? bn : (dual ? 128 : 256);
   const int ncols = swap ? bn * (dual ? 2 : 1) : 256;
-  p.tiles_a = swap ? (N + TILE_A - 1) / TILE_A : (M + TILE_A - 1) / TILE_A;
+  const int sms = cuca_device_sms();
   const int tiles_b = swap ? (M + bn - 1) / bn : (N + out_cols - 1) / out_cols;
+  // Many tokens, whole tiles through the copy engine: tiles of 256 tokens (the tall form, see Cfg) where they fill
+  // the SMs in fewer rounds. Measured at 2,048 tokens on the Llama-3.1-8B widths, a tall tile takes 1.84 to 1.9
+  // times a 128-row tile (three 64 KB stages hold less of a round trip than four of 48 KB, and the epilogue is
+  // not hidden), so it pays only where it halves the rounds: output projection 58.3 -> 53.7 us (256 tiles in
+  // two rounds -> 128 in one), down 193 -> 171 us; q/k/v (384 -> 192 tiles) and gate/up (1,792 -> 896) stay.
+  // CUCA_GEMM_TALL=0 keeps the 128-row form everywhere, =2 takes the tall form wherever it is allowed.
+  bool tall = false;
+  if (!swap && tma_out && epilogue != EPI_PARTIAL && M >= 512) {
+    static int allow = -1;
+    if (allow < 0) { const char* e = getenv("CUCA_GEMM_TALL"); allow = e ? atoi(e) : 1; }
+    const long long t128 = (long long)((M + TILE_A - 1) / TILE_A) * tiles_b;
+    const long long t256 = (long long)((M + 2 * TILE_A - 1) / (2 * TILE_A)) * tiles_b;
+    const long long rounds128 = (t128 + sms - 1) / sms, rounds256 = (t256 + sms - 1) / sms;
+    tall = allow == 2 || (allow == 1 && rounds256 * 19 < rounds128 * 10);
+  }
+  p.tile_rows = tall ? 2 * TILE_A : TILE_A;
+  p.tiles_a = swap ? (N + TILE_A - 1) / TILE_A : (M + p.tile_rows - 1) / p.tile_rows;
   p.tiles = p.tiles_a * tiles_b;
   p.ksteps = (K + TILE_K - 1) / TILE_K;
-  const int sms = cuca_device_sms();
   const long long units = (long long)p.tiles * p.ksteps;
   int grid = p.tiles < sms ? p.tiles : sms;
   p.tma_out = tma_out;
@@ -774,7 +812,9 @@ static int gemm_tc_impl(const void* A, const void* W, const void* bias, void* ou
   // of its MMAs, so a piece takes as long as a whole tile: cutting the last round of many tiles this way gains
   // nothing and is not done.)
   bool pieced = false;
-  if (!swap && !dual && p.tiles < sms && p.ksteps <= 128) {
+  if (tall) {
+    // whole tiles in turn, nothing split
+  } else if (!swap && !dual && p.tiles < sms && p.ksteps <= 128) {
     const int unit = out_dtype == CUCA_F32 ? 32 : 64;  // whole 128-byte runs of the epilogue
     for (int w = unit; w < out_cols && !pieced; w += unit) {
       const int pieces = p.tiles_a * ((N + w - 1) / w);
@@ -786,7 +826,7 @@ static int gemm_tc_impl(const void* A, const void* W, const void* bias, void* ou
       grid = pieces;
     }
   }
-  if (pieced) {
+  if (pieced || tall) {
   } else if (epilogue == EPI_PARTIAL) {
     CUCA_REQUIRE(swap && out_dtype == CUCA_F32 && bias == nullptr && n_slices_out != nullptr,
                  "gemm_tc: partial sums are for up to 64 tokens, 32-bit, without bias");
@@ -848,6 +888,9 @@ static int gemm_tc_impl(const void* A, const void* W, const void* bias, void* ou
   // column pieces up to 128 wide: stages of 128 weight rows, so that six instead of four fit (a piece's main loop
   // runs at the pace of its loads)
   if (pieced && p.piece_w <= 128) return launch_tc<128, false, false>(tmA, tmB, tmO, p, grid, stream);
+  if (tall)
+    return dual ? launch_tc<256, true, false, true>(tmA, tmB, tmO, p, grid, stream)
+                : launch_tc<256, false, false, true>(tmA, tmB, tmO, p, grid, stream);
   return dual ? launch_tc<256, true, false>(tmA, tmB, tmO, p, grid, stream)
               : launch_tc<256, false, false>(tmA, tmB, tmO, p, grid, stream);
 }
