@@ -131,3 +131,28 @@ def test_burst_feeds_tokens_back_on_the_device(folder):
     got = [[first[i]] + [row[i] for row in hist] for i in range(3)]
     assert got == want
     m.core.pools.check()
+
+
+def test_a_fault_inside_a_replayed_step_fails_that_step_and_the_engine_goes_on(folder):
+    """The device error word rides along with a captured step's sampled tokens. A page-table entry outside the
+    pool (planted here; the kernels check every page id, record the error and skip the access) makes the step's
+    tokens worthless: the step must raise before anything is applied, the running requests fail, pools and slots
+    are reset, and the next request is served as if nothing had happened."""
+    from cuca_b200 import BatchingConfig, LocalModel, LocalModelConfig
+    from cuca_b200.engine.scheduler import DECODE, Request
+    from cuca_b200.runtime import DeviceFault
+    m = LocalModel.load(LocalModelConfig(source=str(folder), dtype="bfloat16", batching=BatchingConfig(max_sequences=2)))
+    prompt = tiny.random_tokens(40, 512, seed=3)
+    want = m.generate(prompt, max_tokens=6, temperature=0.0).tokens
+    seq = m.scheduler.submit(Request(prompt, max_tokens=20, temperature=0.0))
+    while seq.phase != DECODE:
+        m.scheduler.turn()
+    m.scheduler.turn()                                     # one good captured step
+    assert m.backend.graph_steps >= 1 and len(seq.completion) == 2
+    m.core.cache.tables[0][seq.slot, 0] = 1_000_000       # the first page of the request: no such page
+    with pytest.raises(DeviceFault, match="page id"):
+        m.scheduler.turn()
+    assert seq.done and seq.finish_reason == "error" and len(seq.completion) == 2   # the lost step gave no token
+    m.core.pools.check()
+    assert m.core.pools.stats()["live_requests"] == 0
+    assert m.generate(prompt, max_tokens=6, temperature=0.0).tokens == want
