@@ -6,6 +6,8 @@ back to torch operators.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import library
@@ -294,6 +296,10 @@ def decode_chunking(n_rows: int, n_kv_heads: int, max_len: int, head_dim: int = 
     if sms is None:
         sms = sm_count()
     tiles = max(1, -(-max_len // 64))
+    forced = os.environ.get("CUCA_DECODE_SPLITS")  # a measuring aid: this many equal chunks for every row
+    if forced:
+        n = max(1, min(32, tiles, int(forced)))
+        return -(-tiles // n) * 64, n
     smem = 3 * 2 * 64 * (head_dim + 8) * 2 + 2048  # three stages of a key and a value tile
     slots = sms * max(1, min(8, (227 * 1024) // smem))
     pairs = max(1, n_rows * n_kv_heads)
