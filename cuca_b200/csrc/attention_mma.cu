@@ -50,6 +50,8 @@ struct AttnParams {
   int slots;             // decode, chunk 0: CTAs the GPU holds at once (for the choice of chunks per row)
   float* part;           // decode: [rows][nh][splits][D + 2] partial (acc, m, l)
   int* counters;         // decode: [rows][nkv], zero before and after
+  int cluster;           // decode: 1: the chunk CTAs of a (row, key head) pair are one thread-block cluster and merge
+                         // their partial results through distributed shared memory (no scratch, no counters)
   int* err;
   // decode with the projection's K slices as input: the kernel adds them, rotates q and k and stores k and v itself
   const float* partial;  // [slices][rows][(nh + 2 nkv) D] 32-bit; row layout q heads, k heads, v heads
@@ -67,6 +69,26 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool v
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Thread-block clusters: a barrier over every thread of every CTA of the cluster (release / acquire), the address
+// of a shared-memory location in another CTA of the cluster, and a load from there.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float dsmem_ld(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
 template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
@@ -166,7 +188,15 @@ attn_mma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tmK, con
       n_used = best;
       chunk = ((tiles + best - 1) / best) * TILE;
     }
-    if ((int)blockIdx.x >= n_used) return;
+    if ((int)blockIdx.x >= n_used) {
+      // a chunk this row does not use: in a cluster it still meets the others at their two barriers (it has
+      // nothing to hand over and nobody reads its shared memory)
+      if (p.cluster && n_used > 1) {
+        cluster_sync_all();
+        cluster_sync_all();
+      }
+      return;
+    }
     range_lo = max(lo, (int)blockIdx.x * chunk);
     range_hi = min(P + 1, ((int)blockIdx.x + 1) * chunk);
 #pragma unroll
@@ -706,8 +736,10 @@ attn_mma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tmK, con
   }
   __syncthreads();
   const int n_splits = gridDim.x;  // layout of the scratch; the row uses the first n_used of them
+  const bool by_cluster = p.cluster && n_used > 1;
   // scratch and counters are indexed by the ordinal of the decode row in this launch
-  float* part_row = p.part + ((size_t)blockIdx.z * p.nh + (size_t)kvh * G) * n_splits * FR;
+  float* part_row = by_cluster ? nullptr : p.part + ((size_t)blockIdx.z * p.nh + (size_t)kvh * G) * n_splits * FR;
+  float* cpart = fs + (size_t)4 * 16 * FR;  // cluster form: this CTA's [G][D + 2] (acc, m, l), read by the cluster's first CTA
   for (int idx = threadIdx.x; idx < G * D; idx += NTHREADS) {
     int item = idx / D, dim = idx % D;
     float M = -INFINITY;
@@ -725,12 +757,61 @@ attn_mma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tmK, con
       p.out[(size_t)dec_row * p.out_stride + (size_t)(kvh * G + item) * D + dim] =
           __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
     } else {
-      float* dst = part_row + ((size_t)item * n_splits + blockIdx.x) * FR;
+      float* dst = by_cluster ? cpart + (size_t)item * FR : part_row + ((size_t)item * n_splits + blockIdx.x) * FR;
       dst[dim] = O;
       if (dim == 0) { dst[D] = M; dst[D + 1] = L; }
     }
   }
   if (n_used == 1) return;
+  constexpr int MAXS = 32;
+  __shared__ float s_m[16][MAXS], s_f[16][MAXS], s_inv[16];
+  if (by_cluster) {
+    // Every chunk CTA of the row has its partial result in its own shared memory; after the cluster's barrier the
+    // first CTA reads them from there and merges in chunk order, and a second barrier keeps the others' shared
+    // memory alive until it has. No trip through global memory, no counter, no last arriver.
+    cluster_sync_all();
+    if (cluster_rank() == 0) {
+      const uint32_t mine = smem_u32(cpart);
+      for (int qd = threadIdx.x; qd < G * MAXS; qd += NTHREADS) {
+        const int item = qd / MAXS, sidx = qd % MAXS;
+        float ms = -INFINITY, ls = 0.f;
+        if (sidx < n_used) {
+          const uint32_t src = dsmem_addr(mine + (uint32_t)((item * FR + D) * sizeof(float)), (uint32_t)sidx);
+          ms = dsmem_ld(src);
+          ls = dsmem_ld(src + 4);
+        }
+        s_m[item][sidx] = ms;
+        s_f[item][sidx] = ls;
+      }
+      __syncthreads();
+      if (threadIdx.x < G) {
+        const int item = threadIdx.x;
+        float M = -INFINITY;
+        for (int sidx = 0; sidx < n_used; ++sidx) M = fmaxf(M, s_m[item][sidx]);
+        float L = 0.f;
+        for (int sidx = 0; sidx < n_used; ++sidx) {
+          const float f = (s_m[item][sidx] == -INFINITY) ? 0.f : exp2f(s_m[item][sidx] - M);
+          L += s_f[item][sidx] * f;
+          s_f[item][sidx] = f;
+        }
+        s_inv[item] = L > 0.f ? 1.f / L : 0.f;
+      }
+      __syncthreads();
+      for (int idx = threadIdx.x; idx < G * D; idx += NTHREADS) {
+        const int item = idx / D, dim = idx % D;
+        const uint32_t at = mine + (uint32_t)((item * FR + dim) * sizeof(float));
+        float v[8];
+#pragma unroll
+        for (int sidx = 0; sidx < 8; ++sidx) v[sidx] = sidx < n_used ? dsmem_ld(dsmem_addr(at, (uint32_t)sidx)) : 0.f;
+        float O = 0.f;
+#pragma unroll
+        for (int sidx = 0; sidx < 8; ++sidx) O += v[sidx] * (sidx < n_used ? s_f[item][sidx] : 0.f);
+        p.out[(size_t)dec_row * p.out_stride + (size_t)(kvh * G + item) * D + dim] = __float2bfloat16_rn(O * s_inv[item]);
+      }
+    }
+    cluster_sync_all();
+    return;
+  }
   __threadfence();
   __syncthreads();
   __shared__ int last;
@@ -743,8 +824,6 @@ attn_mma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tmK, con
   __threadfence();
   // Merge the chunks in chunk order. All loads of a phase are independent and issued together, so the merge
   // costs a few memory round trips, not one per chunk.
-  constexpr int MAXS = 32;
-  __shared__ float s_m[16][MAXS], s_f[16][MAXS], s_inv[16];
   // Up to four output elements per thread and eight chunks (the common case): their partial sums are asked for
   // now, together with the maxima and sums below, so that the merge pays one trip to memory, not two.
   constexpr int PE = 4, PS = 8;
@@ -814,7 +893,7 @@ template <int D, bool DECODE, bool FUSED, bool TMA>
 int launch(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, dim3 grid, cudaStream_t stream) {
   int smem = TMA ? Smem<D>::TMA_BYTES : FUSED ? Smem<D>::FUSED_BYTES : Smem<D>::BYTES;
   if (DECODE) {
-    int need = 4 * 16 * (D + 2) * (int)sizeof(float) + (TMA ? 1024 : 0);
+    int need = 5 * 16 * (D + 2) * (int)sizeof(float) + (TMA ? 1024 : 0);  // four warps' results, then the CTA's
     if (need > smem) smem = need;
   }
   static bool configured = false;
@@ -826,7 +905,10 @@ int launch(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, 
     }
     configured = true;
   }
-  cuca_launch(attn_mma_kernel<D, DECODE, FUSED, TMA>, grid, dim3(NTHREADS), smem, stream, true, p, tmK, tmV);
+  if (DECODE && p.cluster)
+    cuca_launch_cluster(attn_mma_kernel<D, DECODE, FUSED, TMA>, grid, dim3(NTHREADS), smem, stream, true, grid.x, p, tmK, tmV);
+  else
+    cuca_launch(attn_mma_kernel<D, DECODE, FUSED, TMA>, grid, dim3(NTHREADS), smem, stream, true, p, tmK, tmV);
   CUCA_CHECK_LAUNCH("attention_mma");
   return 0;
 }
@@ -904,7 +986,10 @@ int attention_decode_impl(const void* q, int q_stride, const FusedInput* fused, 
                "(heads %d/%d, head size %d)", nh, nkv, d);
   CUCA_REQUIRE(chunk >= 0 && chunk % TILE == 0 && n_splits >= 1 && n_splits <= 32, "attention_decode: bad chunking (at most 32 chunks)");
   CUCA_REQUIRE(bs > 0 && (bs & (bs - 1)) == 0, "attention_decode: %d positions per page is no power of two", bs);
-  CUCA_REQUIRE(n_splits == 1 || (part && counters), "attention_decode: split keys need scratch");
+  // Without scratch the chunk CTAs of a row form a thread-block cluster (up to eight, the portable size) and merge
+  // through distributed shared memory.
+  const bool by_cluster = n_splits > 1 && !(part && counters);
+  CUCA_REQUIRE(!by_cluster || n_splits <= 8, "attention_decode: %d key chunks need scratch (a cluster merges up to 8)", n_splits);
   CUCA_REQUIRE(n_rows <= 65535, "attention_decode: too many rows");
   AttnParams p;
   p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride; p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
@@ -913,6 +998,7 @@ int attention_decode_impl(const void* q, int q_stride, const FusedInput* fused, 
   p.rows = rows; p.tile_row0 = nullptr; p.tile_nrows = nullptr; p.nh = nh; p.nkv = nkv;
   p.scale_log2e = scale * 1.4426950408889634f; p.window = window; p.chunk = chunk; p.part = part;
   p.counters = counters; p.err = err; p.slots = sms * per_sm;
+  p.cluster = by_cluster ? 1 : 0;
   p.partial = nullptr; p.n_slices = 0; p.slice_stride = 0; p.bias = nullptr; p.cos_t = p.sin_t = nullptr;
   p.table_rows = 0; p.rot = 0; p.has_kv = 0;
   static int env_tma = -1;
@@ -981,7 +1067,7 @@ CUCA_API int cuca_attention_prefill(const void* q, int q_stride, void* out, int 
   p.tables = tables; p.table_stride = table_stride; p.positions = positions; p.seq_of_row = seq_of_row;
   p.rows = nullptr; p.tile_row0 = tile_row0; p.tile_nrows = tile_nrows; p.nh = nh; p.nkv = nkv;
   p.scale_log2e = scale * 1.4426950408889634f; p.window = window; p.chunk = 0; p.part = nullptr;
-  p.counters = nullptr; p.err = err; p.slots = 1;
+  p.counters = nullptr; p.err = err; p.slots = 1; p.cluster = 0;
   p.partial = nullptr; p.n_slices = 0; p.slice_stride = 0; p.bias = nullptr; p.cos_t = p.sin_t = nullptr;
   p.table_rows = 0; p.rot = 0; p.has_kv = 0;
   return dispatch<false, false>(d, p, dim3(n_tiles, nh), stream);

@@ -306,16 +306,31 @@ def decode_chunking(n_rows: int, n_kv_heads: int, max_len: int, head_dim: int = 
     best, best_cost = 1, None
     for n in range(1, min(32, tiles) + 1):
         rounds = -(-pairs * n // slots)
-        cost = rounds * (-(-tiles // n) + 3) * 8 + (2 if n > 1 else 0)
+        # the merge: none for one chunk, through distributed shared memory up to a cluster's eight chunks, through
+        # global memory and a last arriver beyond (measured: about a tile's time more, and growing with the chunks)
+        merge = 0 if n == 1 else 2 if (CLUSTER_MERGE and n <= MAX_CLUSTER) else 10 + n // 2
+        cost = rounds * (-(-tiles // n) + 3) * 8 + merge
         if best_cost is None or cost < best_cost:
             best, best_cost = n, cost
     return 0, best
 
 
+CLUSTER_MERGE = os.environ.get("CUCA_ATTN_CLUSTER", "1") != "0"
+MAX_CLUSTER = 8  # the portable cluster size
+
+
+def _decode_scratch(device, n_rows, n_heads, n_kv_heads, head_dim, n_splits):
+    """Scratch of a split-key decode launch, or (None, None) when the row's chunk CTAs merge as a thread-block
+    cluster through distributed shared memory (up to eight chunks): nothing then goes through global memory."""
+    if n_splits == 1 or (CLUSTER_MERGE and n_splits <= MAX_CLUSTER):
+        return None, None
+    return attention_scratch(device, n_rows * n_heads * n_splits * (head_dim + 2), n_rows * n_kv_heads)
+
+
 def attention_decode(q, q_stride, out, kpool, vpool, positions, seq_of_row, tables, rows, n_rows, n_heads,
                      n_kv_heads, head_dim, scale, window, chunk, n_splits, err) -> None:
     lib = library.load()
-    part, cnt = attention_scratch(out.device, n_rows * n_heads * n_splits * (head_dim + 2), n_rows * n_kv_heads)
+    part, cnt = _decode_scratch(out.device, n_rows, n_heads, n_kv_heads, head_dim, n_splits)
     library.check(lib.cuca_attention_decode(
         _p(q), int(q_stride), _p(out), out.stride(0), _p(kpool), _p(vpool), kpool.shape[0], kpool.shape[2],
         _p(positions), _p(seq_of_row), _p(tables), tables.shape[1], _p(rows), n_rows, n_heads, n_kv_heads, head_dim,
@@ -327,7 +342,7 @@ def attention_decode_fused(partial, bias, cos, sin, rotary_dim, has_kv, out, kpo
     """The decode form fed by the stacked q/k/v projection's unadded K slices (`PartialSums`): adds them, rotates
     q and k, stores k and v in the pages and attends, in one launch. Every row of the step is a single token."""
     lib = library.load()
-    part, cnt = attention_scratch(out.device, n_rows * n_heads * n_splits * (head_dim + 2), n_rows * n_kv_heads)
+    part, cnt = _decode_scratch(out.device, n_rows, n_heads, n_kv_heads, head_dim, n_splits)
     library.check(lib.cuca_attention_decode_fused(
         _p(partial.data), partial.slices, partial.slice_stride, _p(bias), _p(cos), _p(sin),
         cos.shape[0] if cos is not None else 0, int(rotary_dim), int(bool(has_kv)), _p(out), out.stride(0), _p(kpool),
