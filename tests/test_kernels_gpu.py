@@ -653,3 +653,59 @@ def test_a_bounded_wait_that_runs_out_returns_an_error_and_leaves_the_library_us
     torch.cuda.synchronize()
     assert torch.allclose(out.float(), a.float() @ w.float().T, atol=0.2, rtol=2e-2)
     rt.check_device_errors()
+
+
+@pytest.mark.parametrize("d,nh,nkv", [(128, 4, 2), (64, 6, 2)])
+def test_attention_over_tens_of_thousands_of_keys(dev, d, nh, nkv):
+    """Forty thousand keys of one request: the key/value rings of both tensor-core kernels wrap more than a hundred
+    times and the page table is read in seventy-eight batches. Decode: the last position, with its keys in one
+    chunk per row's own choice, in a cluster of eight chunks and in thirty-two chunks through scratch. Prefill: the
+    last 300 rows as a portion that starts deep inside the request. One query is pointed at the key of position 7,
+    another at a key in the middle, so that a lost page shows."""
+    from cuca_b200.kernels import ops
+    dtype, bs = torch.bfloat16, 16
+    lens = [40_000, 33_333]
+    k, v, kpool, vpool, tables = _paged_setup(dev, dtype, lens, nh, nkv, d, bs,
+                                              n_blocks=sum(-(-l // bs) for l in lens) + 7, seed=12)
+    g = torch.Generator(device=dev).manual_seed(13)
+    scale = 1.0 / math.sqrt(d)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    kf = [x.to(dtype).float() for x in k]
+    vf = [x.to(dtype).float() for x in v]
+    # ---- decode: one row per request at its last position
+    q = torch.randn(2, nh * d, device=dev, generator=g)
+    q[0, :d] = k[0][7, 0] * 3.0            # head 0 of request 0 looks at position 7
+    q[1, :d] = k[1][17_001, 0] * 3.0       # head 0 of request 1 at a key in the middle
+    qb = q.to(dtype).contiguous()
+    positions = torch.tensor([lens[0] - 1, lens[1] - 1], dtype=torch.int32, device=dev)
+    seq = torch.tensor([0, 1], dtype=torch.int32, device=dev)
+    want = [_ref_attention(qb[r].float().view(nh, d), kf[r], vf[r], lens[r] - 1, scale, None) for r in range(2)]
+    for chunk, n_splits in ((0, 5), (0, 8), (-(-lens[0] // 32 // 64) * 64, 32)):
+        out = torch.zeros(2, nh * d, device=dev, dtype=dtype)
+        ops.attention_decode(qb, nh * d, out, kpool, vpool, positions, seq, tables, None, 2, nh, nkv, d, scale, None,
+                             chunk, n_splits, err)
+        assert int(err.item()) == 0
+        for r in range(2):
+            got = out[r].float().view(nh, d)
+            assert torch.allclose(got, want[r], atol=2e-2, rtol=2e-2), (n_splits, r, float((got - want[r]).abs().max()))
+    # ---- prefill on tcgen05: the last 300 rows of request 0
+    n = 300
+    start = lens[0] - n
+    width = (nh + 2 * nkv) * d
+    qkv = torch.randn(n, width, device=dev, generator=g)
+    qkv[-1, :d] = k[0][7, 0] * 3.0
+    qkv[5, d:2 * d] = k[0][20_000, 0] * 3.0
+    qkv = qkv.to(dtype)
+    pos = torch.arange(start, lens[0], dtype=torch.int32, device=dev)
+    seq_p = torch.zeros(n, dtype=torch.int32, device=dev)
+    out = torch.zeros(n, nh * d, device=dev, dtype=dtype)
+    assert ops.attention_tc_supported(qkv, out, kpool, vpool, nh, nkv, d)
+    row0 = torch.tensor([0, 128, 256], dtype=torch.int32, device=dev)
+    nrows = torch.tensor([128, 128, 44], dtype=torch.int32, device=dev)
+    ops.attention_prefill_tc(qkv, out, kpool, vpool, pos, seq_p, tables, row0, nrows, 3, nh, nkv, d, scale, None, err)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    for r in (0, 5, 127, 128, 200, 299):
+        ref = _ref_attention(qkv[r, :nh * d].float().view(nh, d), kf[0], vf[0], start + r, scale, None)
+        got = out[r].float().view(nh, d)
+        assert torch.allclose(got, ref, atol=2e-2, rtol=2e-2), (r, float((got - ref).abs().max()))
