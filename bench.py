@@ -144,6 +144,10 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--shape", default="llama-3.1-8b", choices=sorted(SHAPES))
+    ap.add_argument("--prompt-tokens", type=int, default=None, help="prompt length of the decode points (the shape's default else)")
+    ap.add_argument("--prefill-tokens", type=int, default=None,
+                    help="length of the timed prefill prompt (2,048 else; longer prompts run in portions of 2,048)")
+    ap.add_argument("--context", type=int, default=None, help="context length (the shape's default else)")
     ap.add_argument("--decode-only", action="store_true",
                     help="with --shape llama-3.2-1b: the plain decode line at --batch instead of the mixed workload")
     args = ap.parse_args()
@@ -171,6 +175,10 @@ def main() -> int:
 
     base_cfg, label, CONTEXT, PROMPT, SEED, rope_words = SHAPES[args.shape]
     mixed = args.shape == "llama-3.2-1b" and not args.decode_only
+    PREFILL_TOKENS = args.prefill_tokens or globals()["PREFILL_TOKENS"]
+    STEP_TOKENS = 2048  # rows of one step: longer prompts are prefilled in portions of this many
+    PROMPT = args.prompt_tokens or PROMPT
+    CONTEXT = args.context or max(CONTEXT, PROMPT + args.steps + args.warmup + 256, PREFILL_TOKENS + 16)
     cfg = dict(base_cfg)
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
@@ -183,17 +191,17 @@ def main() -> int:
     def pages_for(batch, steps):
         """Positions the pool must hold for `batch` requests that decode `steps` timed steps after their prompt
         (requests that finish their prompt early decode while the others are still being prefilled)."""
-        per_request = PROMPT + steps + args.warmup + 2 * (-(-batch * PROMPT // PREFILL_TOKENS)) + 48
+        per_request = PROMPT + steps + args.warmup + 2 * (-(-batch * PROMPT // STEP_TOKENS)) + 48
         return batch * (-(-per_request // 16) * 16)
 
     kv_tokens = max(CONTEXT + 16, pages_for(args.batch, args.steps), 0 if args.no_points else pages_for(64, point_steps),
-                    64 * (2048 + 128 + 16) if mixed else 0) + PREFILL_TOKENS + 64
+                    64 * (2048 + 128 + 16) if mixed else 0, PREFILL_TOKENS + 64) + STEP_TOKENS + 64
     t0 = time.perf_counter()
     model = LocalModel.load(LocalModelConfig(
         model_config=cfg, random_weights=RandomWeights(seed=SEED, std=0.02), dtype="bfloat16", context_length=CONTEXT,
         kv_block_size=16, batching=BatchingConfig(max_sequences=max_batch, kv_tokens=kv_tokens,
-                                                  max_step_tokens=max(PREFILL_TOKENS, max_batch),
-                                                  prefill_chunk=PREFILL_TOKENS)))
+                                                  max_step_tokens=max(STEP_TOKENS, max_batch),
+                                                  prefill_chunk=STEP_TOKENS)))
     load_s = time.perf_counter() - t0
     core, sched, backend = model.core, model.scheduler, model.backend
     vocab = cfg["vocab_size"]
