@@ -15,7 +15,6 @@ from ..config.engine_config import LocalModelConfig, SamplingConfig
 from ..config.model_config import read_config_json
 from ..config.registry import build_spec
 from ..kernels import ops
-from ..native import host
 from ..weights.loader import FolderSource
 from .core import EngineCore
 from .graphs import MAX_HISTORY, DecodeGraphs
