@@ -782,10 +782,12 @@ static int gemm_tc_impl(const void* A, const void* W, const void* bias, void* ou
   // the SMs in fewer rounds. Measured at 2,048 tokens on the Llama-3.1-8B widths, a tall tile takes 1.84 to 1.9
   // times a 128-row tile (three 64 KB stages hold less of a round trip than four of 48 KB, and the epilogue is
   // not hidden), so it pays only where it halves the rounds: output projection 58.3 -> 53.7 us (256 tiles in
-  // two rounds -> 128 in one), down 193 -> 171 us; q/k/v (384 -> 192 tiles) and gate/up (1,792 -> 896) stay.
+  // two rounds -> 128 in one), down 193 -> 171 us; q/k/v (384 -> 192 tiles) and gate/up (1,792 -> 896) stay. From
+  // 129 tokens on the same rule holds: gate/up at 256 tokens 70.0 -> 64.0 us, at 192 tokens 85.1 -> 74.8 (224 tiles
+  // in two rounds -> 112 in one).
   // CUCA_GEMM_TALL=0 keeps the 128-row form everywhere, =2 takes the tall form wherever it is allowed.
   bool tall = false;
-  if (!swap && tma_out && epilogue != EPI_PARTIAL && M >= 512) {
+  if (!swap && tma_out && epilogue != EPI_PARTIAL && M > TILE_A) {
     static int allow = -1;
     if (allow < 0) { const char* e = getenv("CUCA_GEMM_TALL"); allow = e ? atoi(e) : 1; }
     const long long t128 = (long long)((M + TILE_A - 1) / TILE_A) * tiles_b;
