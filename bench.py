@@ -134,6 +134,62 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(mhz)}
 
 
+def contraction_table(args, token_counts) -> int:
+    """The four contractions of one layer (q/k/v with store, output projection into the 32-bit stream, gate/up
+    with SwiGLU, down into the stream) at the shape's widths: this library's kernels beside cuBLAS through
+    torch.matmul (the plain product only; its epilogues would be further launches). Six sets of weights take
+    turns, so weights always come from memory; CUDA events around six launches, best of five."""
+    import math
+
+    import torch
+
+    from cuca_b200.kernels import ops
+
+    cfg = SHAPES[args.shape][0]
+    E, ff = cfg["hidden_size"], cfg["intermediate_size"]
+    qkv = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * cfg["head_dim"]
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(1)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    shapes = [("qkv", qkv, E, ops.EPI_STORE, torch.bfloat16), ("o", E, cfg["num_attention_heads"] * cfg["head_dim"],
+                                                                  ops.EPI_RESIDUAL, torch.float32),
+              ("gate_up", ff, E, ops.EPI_SWIGLU, torch.bfloat16), ("down", E, ff, ops.EPI_RESIDUAL, torch.float32)]
+    sets = 6
+
+    def best_us(fn):
+        fn()
+        torch.cuda.synchronize()
+        out = []
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            out.append(a.elapsed_time(b) * 1e3 / sets)
+        return min(out)
+
+    for M in token_counts:
+        line = {"tokens": M, "shape": SHAPES[args.shape][1], "unit": "us per launch, cold weights"}
+        for name, N, K, epi, odt in shapes:
+            a = torch.randn(M, K, device=dev, generator=g).bfloat16()
+            rows = (2 if epi == ops.EPI_SWIGLU else 1) * N
+            ws = [(torch.randn(rows, K, device=dev, generator=g) / math.sqrt(K)).bfloat16() for _ in range(sets)]
+            out = torch.zeros(M, N, device=dev, dtype=odt)
+            ref = torch.empty(M, rows, device=dev, dtype=torch.bfloat16)
+            if epi != ops.EPI_SWIGLU and ops.gemm_partial_supported(a, ws[0]):
+                # as the engine runs it over few tokens: K slices left unadded for the kernel that reads them next
+                ours = best_us(lambda: [ops.gemm_partial(a, w, err) for w in ws])
+                line.setdefault("unadded_slices", []).append(name)
+            else:
+                ours = best_us(lambda: [ops.gemm_tc(a, w, out, epi, None, err) for w in ws])
+            cublas = best_us(lambda: [torch.matmul(a, w.T, out=ref) for w in ws])
+            line[name] = {"ours": round(ours, 1), "cublas": round(cublas, 1), "ratio": round(ours / cublas, 2)}
+        assert int(err.item()) == 0
+        print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -148,6 +204,9 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=None,
                     help="length of the timed prefill prompt (2,048 else; longer prompts run in portions of 2,048)")
     ap.add_argument("--context", type=int, default=None, help="context length (the shape's default else)")
+    ap.add_argument("--contractions", default=None, metavar="M,M,...",
+                    help="instead of the bench: time the four contractions of a layer at these token counts, this "
+                         "library's kernels beside cuBLAS (torch.matmul), cold weights; one JSON line per count")
     ap.add_argument("--decode-only", action="store_true",
                     help="with --shape llama-3.2-1b: the plain decode line at --batch instead of the mixed workload")
     args = ap.parse_args()
@@ -168,6 +227,9 @@ def main() -> int:
 
     import numpy as np
     import torch
+
+    if args.contractions:
+        return contraction_table(args, [int(m) for m in args.contractions.split(",")])
 
     from cuca_b200 import BatchingConfig, LocalModel, LocalModelConfig, RandomWeights
     from cuca_b200.engine.scheduler import DECODE, Request

@@ -8,8 +8,8 @@
 // add into the 32-bit residual stream, or SwiGLU), so the epilogue of one tile overlaps the main loop of the
 // next. tcgen05.commit hands stages back to the producer and accumulators to the epilogue.
 //
-// Two orientations share the code. Up to 64 tokens (decode), the weight is the 128-row MMA operand and the
-// tokens are the N dimension (16..64): D[feature, token], one TMEM lane per output feature. Above, the tokens
+// Two orientations share the code. Up to 256 tokens (decode, short portions; SwiGLU up to 64), the weight is the 128-row
+// MMA operand and the tokens are the N dimension (16..256): D[feature, token], one TMEM lane per output feature. Above, the tokens
 // are the 128-row operand and 256 weight rows the N dimension: D[token, feature], so a thread owns a run of
 // consecutive features of one token and stores vectors. For SwiGLU the gate and up tiles accumulate side by
 // side in TMEM, so one thread holds both values of a feature.
@@ -36,6 +36,11 @@
 
 namespace {
 
+constexpr int SWAP_MAX_TOKENS = 256;  // up to here the weights are the 128-row operand and the tokens the columns
+// SwiGLU: up to here. Beyond, its two accumulators leave no room in the tensor memory for a second tile's, and the
+// token-row forms are as fast or faster (measured on the Llama-3.1-8B widths, us: 65..128 tokens 46.0-46.5 against
+// 46.4-49.4 this way; 129..256 tokens 55.4-59.3 in the tall form against 56.7-65.7).
+constexpr int SWAP_MAX_TOKENS_SWIGLU = 64;
 constexpr int NPROD = 2;       // one thread requests about 16 KB per 0.45 us: too little for an SM's share of the memory's rate
 
 struct Params {
@@ -89,7 +94,9 @@ struct Cfg {
   static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) > 12 ? 12 : (SMEM_BUDGET / STAGE_BYTES);
   static constexpr int MMA_N = BN;                                 // N of one tcgen05.mma
   static constexpr int NCOLS = (SWAP ? BN * (DUAL ? 2 : 1) : BN) * ROW_BLOCKS;  // accumulator columns of one tile
-  static constexpr int ACC_BUFS = TALL ? 1 : 2;                      // tiles whose accumulators TMEM holds at once
+  // tiles whose accumulators TMEM holds at once: two, so that one tile's epilogue runs under the next one's main
+  // loop; one in the tall form, whose accumulators fill all 512 columns
+  static constexpr int ACC_BUFS = TALL ? 1 : 2;
   static constexpr int TMEM_COLS = ACC_BUFS * NCOLS < 32 ? 32 : ACC_BUFS * NCOLS;
   static constexpr int EPI_WARPS = 4 * ROW_BLOCKS;
   static constexpr int PROD2_WARP = 2 + EPI_WARPS;                   // the second producer's warp
@@ -180,7 +187,10 @@ struct SegmentWalk {
   }
 };
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + __expf(-g)) * u; }
+// The quotient is the approximate one (2 ulp, rounded to bf16 right after): the IEEE division leaves its fast path
+// for a numerator of zero, which is what every padded row or column of a tile holds, and a warp then pays the slow
+// path for all its lanes (measured: SwiGLU over 255 tokens took 76.7 us, over 256 tokens 63.1).
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
 
 // ---- epilogue of 16 accumulator columns held by one thread (TMEM lane `lane_row` of tile rows a0.., columns c..)
 template <int BN, bool DUAL, bool SWAP>
@@ -637,6 +647,9 @@ int cuca_device_sms() {
   return sms;
 }
 
+// Most tokens for which a contraction can leave its K slices unadded (cuca_gemm_tc_partial).
+CUCA_API int cuca_gemm_tc_partial_max_tokens() { return SWAP_MAX_TOKENS; }
+
 // How many SMs the current device has (the Python side sizes its split choices by it too).
 CUCA_API int cuca_sm_count() { return cuca_device_sms(); }
 
@@ -753,9 +766,9 @@ static int gemm_tc_impl(const void* A, const void* W, const void* bias, void* ou
   CUCA_REQUIRE(epilogue != EPI_RESIDUAL || out_dtype == CUCA_F32, "gemm_tc: the residual stream is 32-bit");
   CUCA_REQUIRE(epilogue != EPI_SWIGLU || (bias == nullptr && out_dtype == CUCA_BF16), "gemm_tc: SwiGLU writes bf16, no bias");
   const bool dual = epilogue == EPI_SWIGLU;
-  const bool swap = M <= 64;
+  const bool swap = M <= (epilogue == EPI_SWIGLU ? SWAP_MAX_TOKENS_SWIGLU : SWAP_MAX_TOKENS);
   CUCA_REQUIRE(epilogue >= 0 && epilogue <= EPI_PARTIAL, "gemm_tc: unknown epilogue %d", epilogue);
-  const int bn = M <= 16 ? 16 : M <= 32 ? 32 : 64;
+  const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
   const uint64_t w_rows = (uint64_t)N * (dual ? 2 : 1);
   CUtensorMap tmA, tmB, tmO;
   int tma_out = 0;
@@ -831,7 +844,7 @@ static int gemm_tc_impl(const void* A, const void* W, const void* bias, void* ou
   if (pieced || tall) {
   } else if (epilogue == EPI_PARTIAL) {
     CUCA_REQUIRE(swap && out_dtype == CUCA_F32 && bias == nullptr && n_slices_out != nullptr,
-                 "gemm_tc: partial sums are for up to 64 tokens, 32-bit, without bias");
+                 "gemm_tc: partial sums are for up to %d tokens, 32-bit, without bias", SWAP_MAX_TOKENS);
     int per_tile = sms / p.tiles;
     if (per_tile > max_splits) per_tile = max_splits;
     if (per_tile > p.ksteps / 2) per_tile = p.ksteps / 2;
@@ -885,6 +898,8 @@ static int gemm_tc_impl(const void* A, const void* W, const void* bias, void* ou
                 : launch_tc<BN_, false, true>(tmA, tmB, tmO, p, grid, stream);
   if (swap) {
     switch (bn) { GO(16) GO(32) GO(64) }
+    return bn == 128 ? launch_tc<128, false, true>(tmA, tmB, tmO, p, grid, stream)  // 65..256 tokens, never SwiGLU
+                     : launch_tc<256, false, true>(tmA, tmB, tmO, p, grid, stream);
   }
 #undef GO
   // column pieces up to 128 wide: stages of 128 weight rows, so that six instead of four fit (a piece's main loop
@@ -907,7 +922,7 @@ CUCA_API int cuca_gemm_tc(const void* A, const void* W, const void* bias, void* 
 
 // How many K slices cuca_gemm_tc_partial will write for this shape (the first dimension of its output).
 CUCA_API int cuca_gemm_tc_partial_slices(int M, int N, int K, int max_slices) {
-  if (M > 64 || M <= 0 || N <= 0 || K <= 0) return 0;
+  if (M > SWAP_MAX_TOKENS || M <= 0 || N <= 0 || K <= 0) return 0;
   const int sms = cuca_device_sms();
   const int tiles = (N + TILE_A - 1) / TILE_A, ksteps = (K + TILE_K - 1) / TILE_K;
   int per_tile = sms / tiles;
@@ -917,7 +932,7 @@ CUCA_API int cuca_gemm_tc_partial_slices(int M, int N, int K, int max_slices) {
   return per_tile;
 }
 
-// partial[slice][M][N] (32-bit) = A[M, K slice] W[N, K slice]^T for up to 64 tokens: the K slices of a tile are
+// partial[slice][M][N] (32-bit) = A[M, K slice] W[N, K slice]^T for up to 256 tokens: the K slices of a tile are
 // not added up here (no workspace, no counters, no second pass); the kernel that reads the result adds them in
 // slice order. *n_slices gets the number of slices written (cuca_gemm_tc_partial_slices of the same shape).
 CUCA_API int cuca_gemm_tc_partial(const void* A, const void* W, float* partial, int M, int N, int K, int lda,

@@ -470,13 +470,23 @@ class PartialSums:
         return self.data.stride(0)
 
 
+_partial_max: list = []
+
+
+def partial_max_tokens() -> int:
+    """Most tokens for which a contraction may leave its K slices unadded (asked of the kernel library)."""
+    if not _partial_max:
+        _partial_max.append(int(library.load().cuca_gemm_tc_partial_max_tokens()))
+    return _partial_max[0]
+
+
 def gemm_partial_supported(a, w) -> bool:
-    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[0] <= 64
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[0] <= partial_max_tokens()
             and gemm_tc_supported(a, w))
 
 
 def gemm_partial(a, w, err=None, max_slices=16) -> PartialSums:
-    """a @ w.T for up to 64 rows, as partial sums over K slices (see `PartialSums`)."""
+    """a @ w.T for few rows (`partial_max_tokens`), as partial sums over K slices (see `PartialSums`)."""
     _cuda(a, w)
     lib = library.load()
     M, K = a.shape

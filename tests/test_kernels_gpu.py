@@ -30,7 +30,8 @@ def _ref_gemm(a, w, epilogue, bias, prior):
 GEMM_SHAPES = [(1, 64, 64), (3, 96, 96), (8, 176, 64), (16, 128, 200), (17, 331, 120), (33, 1000, 320),
                (64, 512, 1024), (100, 264, 4096), (130, 640, 256), (300, 384, 136), (8, 4096, 4096),
                (65, 176, 96), (256, 1000, 320), (640, 128, 64), (40, 2304, 512),
-               (2048, 4096, 512), (1300, 5000, 1160)]  # more tiles than SMs: the last round's K steps are dealt out
+               (2048, 4096, 512), (1300, 5000, 1160),  # more tiles than SMs: the last round's K steps are dealt out
+               (160, 20000, 512), (192, 1000, 4096), (200, 5000, 320)]  # 129..256 tokens, more tiles than SMs
 
 
 @pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
@@ -462,7 +463,8 @@ def test_attention_prefill_mma(dev, nh, nkv, d, bs, window):
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 64, 64), (8, 4096, 4096), (8, 6144, 4096), (3, 96, 96), (17, 331, 120),
-                                   (64, 512, 1024), (40, 2304, 512), (5, 128256 // 8, 256)])
+                                   (64, 512, 1024), (40, 2304, 512), (5, 128256 // 8, 256),
+                                   (100, 2304, 512), (130, 4096, 1024), (256, 6144, 4096), (200, 331, 120)])
 def test_gemm_partial_sums_and_their_readers(dev, M, N, K):
     """The decode contraction that leaves its K slices unadded, and the kernels that add them while reading:
     RMSNorm over the residual stream and rotate-and-store of the q/k/v projection."""
