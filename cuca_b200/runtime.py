@@ -68,8 +68,8 @@ class Runtime:
 class ResidualStream:
     """The 32-bit residual stream of a step, `[rows, width]`, as blocks and parts get it.
 
-    Over few tokens a contraction into the stream is cut along K over the SMs and leaves its slices unadded
-    (`add_linear`); whoever reads the stream next adds them. That hand-over is this object's business, not the
+    Over few tokens (up to a few hundred: the kernel library says how many) a contraction into the stream is cut
+    along K over the SMs and leaves its slices unadded (`add_linear`); whoever reads the stream next adds them. That hand-over is this object's business, not the
     parts': `data` adds pending slices before it returns the tensor, so a part written against `data` (read it,
     update it in place) is always right. A reader that can add the slices while it reads, in the same pass over
     memory (the RMSNorm kernel), asks for `take()` instead and gets the tensor and the slices."""
