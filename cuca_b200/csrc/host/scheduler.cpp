@@ -118,20 +118,37 @@ void Scheduler::plan(std::vector<PlanItem>& out) {
     const int room = budget - used;
     if (room <= 0) break;
     const int n = std::min(std::min((int)s.prompt.size() - s.pos, cfg_.prefill_chunk), room);
-    if (pools_.reserve(s.blocks, s.pos + n) != OK) {
-      // a prompt portion that cannot get its pages fails that request
-      // (src/provider/local/engine/scheduler.rs:1260-1263)
-      release(id, false);
-      finish(id, FIN_ERROR, "the K/V page pool is exhausted");
-      continue;
-    }
+    if (!ensure_portion(id, s.pos + n)) continue;
     const int last = s.pos + n == (int)s.prompt.size() ? 1 : 0;
     out.push_back(PlanItem{id, s.pos, n, last, s.slot, s.blocks, 0, -1});
     used += n;
   }
+  // a portion that found no page may have sent younger requests, planned ones among them, back to the queue
+  out.erase(std::remove_if(out.begin(), out.end(), [&](const PlanItem& p) { return !is_running(p.seq); }), out.end());
   for (PlanItem& p : out) {
     SeqBlocks* b = pools_.seq(p.blocks);
     p.start = b ? b->length : 0;
+  }
+}
+
+// Pages for a prompt portion up to position `upto`. When the pool is exhausted the youngest running request gives
+// way: it goes back to the head of the queue and starts again when pages are free. If that is this request, it
+// waits there itself. Only a request that runs alone and still finds no page fails: the pool is too small for it.
+// (The reference fails the request at once, src/provider/local/engine/scheduler.rs:1260-1263; admission only counts
+// the prompts being prefilled, so there a request could fail because others had grown while it was cut into
+// portions, although it would have fitted a moment later.)
+bool Scheduler::ensure_portion(int id, int upto) {
+  while (true) {
+    Sequence& s = seqs_[id];
+    if (pools_.reserve(s.blocks, upto) == OK) return true;
+    if (running_.size() == 1) {
+      release(id, false);
+      finish(id, FIN_ERROR, "the K/V page pool is exhausted");
+      return false;
+    }
+    const int victim = running_.back();  // youngest
+    preempt(victim);
+    if (victim == id) return false;
   }
 }
 

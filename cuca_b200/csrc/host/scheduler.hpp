@@ -73,6 +73,7 @@ class Scheduler {
  private:
   void committed(std::vector<int>& total);
   bool ensure_block(int id);
+  bool ensure_portion(int id, int upto);
   void preempt(int id);
   void take_token(int id, int tok);
   void release(int id, bool share);  // share: with the prefix cache on, its full pages stay findable

@@ -9,6 +9,7 @@ back to back without the host (`burst`), which is how the device-only decode rat
 """
 from __future__ import annotations
 
+import gc
 from typing import Sequence
 
 import torch
@@ -76,8 +77,17 @@ class DecodeGraph:
         from ..kernels import library
         before = library.launches
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
-            self._body()
+        # No collection of dead Python cycles while the stream captures: a cycle that holds a CUDA graph or device
+        # tensors (an engine the caller dropped a moment ago) would be torn down in the middle of the capture, and
+        # resetting a graph or recording an event then invalidates it.
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph):
+                self._body()
+        finally:
+            if collecting:
+                gc.enable()
         self.launches = library.launches - before  # kernels one replay runs
         torch.cuda.synchronize()
         self.counter.zero_()

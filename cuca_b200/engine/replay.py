@@ -40,6 +40,10 @@ class Replayer:
         for ent in record.get("entries", []):
             rid = ent["id"]
             tokens = [int(t) for t in ent["tokens"]]
+            if not tokens:  # nothing to run for this request in this step
+                if ent.get("want"):
+                    raise ValueError(f"request `{rid}`, step {record['step']}: logits wanted of no tokens")
+                continue
             if rid not in self.live:
                 slot = core.slots.alloc()
                 if slot is None:

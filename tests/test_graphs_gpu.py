@@ -115,6 +115,45 @@ def test_sampled_decode_through_graphs_keeps_each_requests_generator(folder):
     assert [o.tokens for o in together] == [o.tokens for o in alone]
 
 
+def test_a_capture_is_not_disturbed_by_the_collection_of_a_dropped_engine(folder):
+    """A dropped engine lives on in dead reference cycles with its CUDA graphs and tensors until Python collects
+    them. If that happened while another engine's step is being captured, resetting the old graphs would
+    invalidate the capture: no automatic collection runs during a capture."""
+    import gc
+    import torch
+    from cuca_b200 import BatchingConfig, LocalModel, LocalModelConfig
+    from cuca_b200.engine import graphs
+    cfg = LocalModelConfig(source=str(folder), dtype="float32", batching=BatchingConfig(max_sequences=4))
+    prompt = np.random.default_rng(31).integers(0, 512, size=9).tolist()
+    seen = []
+    body = graphs.DecodeGraph._body
+
+    def watched(self):
+        if torch.cuda.is_current_stream_capturing():
+            seen.append(gc.isenabled())
+            [[] for _ in range(5000)]  # enough container allocations for several automatic collections
+        return body(self)
+
+    old_threshold = gc.get_threshold()
+    gc.collect()
+    gc.disable()
+    try:
+        first = LocalModel.load(cfg)
+        want = first.generate(prompt, max_tokens=8, temperature=0.0).tokens
+        del first                      # dead cycles now hold its captured graphs
+        second = LocalModel.load(cfg)
+        graphs.DecodeGraph._body = watched
+        gc.set_threshold(50, 1, 1)     # collect all generations at every opportunity
+        gc.enable()
+        got = second.generate(prompt, max_tokens=8, temperature=0.0).tokens
+    finally:
+        graphs.DecodeGraph._body = body
+        gc.set_threshold(*old_threshold)
+        gc.enable()
+    assert seen and not any(seen), "the collector was switched on during a capture"
+    assert gc.isenabled() and got == want
+
+
 def test_burst_feeds_tokens_back_on_the_device(folder):
     from cuca_b200 import BatchingConfig, LocalModel, LocalModelConfig
     from cuca_b200.engine.scheduler import DECODE, Request

@@ -149,6 +149,24 @@ def test_pages_run_out_the_youngest_is_preempted_and_resumes():
     pools.check()
 
 
+def test_a_prompt_portion_that_finds_no_page_waits_instead_of_failing():
+    """Admission counts the prompts being prefilled, not what decoding requests will grow by: a prompt cut into
+    portions can find the pool empty half-way. It goes back to the queue (it is the youngest) and finishes later."""
+    sch, be, pools, slots = make(n_blocks=4, max_step_tokens=9, prefill_chunk=8, ctx=256)
+    a = sch.submit(Request(list(range(30)), max_tokens=20))            # two pages, a third from position 32 on
+    while a.phase != DECODE:
+        sch.turn()
+    b = sch.submit(Request(list(range(100, 130)), max_tokens=3))       # admitted: two pages are free
+    sch.run_until_done()
+    assert a.finish_reason == b.finish_reason == "length" and a.error is None and b.error is None
+    assert len(a.completion) == 20 and b.completion == [1100, 1101, 1102]
+    assert b.preemptions >= 1 and a.preemptions == 0
+    starts_of_b = [st for st in be.started if st[0] == 1]
+    assert len(starts_of_b) >= 2  # admitted, sent back while still in its prompt, admitted again
+    assert all(p.free == p.n_blocks for p in pools.pools) and slots.free == 4
+    pools.check()
+
+
 def test_a_single_request_that_exhausts_the_pool_fails_cleanly():
     sch, be, pools, slots = make(n_blocks=2, max_step_tokens=64, prefill_chunk=64)
     a = sch.submit(Request(list(range(20)), max_tokens=100))
