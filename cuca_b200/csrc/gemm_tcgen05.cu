@@ -634,6 +634,227 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
 }
 
+// ------------------------------------------------------------------ many tokens: two SMs on one tile
+// A pair of CTAs (a cluster of two, on neighbouring SMs) takes a tile of 256 tokens x 256 weight rows. Each CTA
+// stages its own 128 token rows and HALF of the tile's weight rows (16 KB + 16 KB per K step instead of 16 + 32), and
+// one thread of the first CTA issues `tcgen05.mma.cta_group::2` with M = 256: the tensor cores of both SMs read
+// both halves of the weight tile, each SM accumulates its own 128 rows x 256 columns in its own tensor memory.
+// Per SM and K step that is 32 KB from L2 for 278 ns of MMAs (the one-SM form needs 48 KB and runs at the pace of
+// those loads), in six stages of 32 KB, with two accumulators as before so that a tile's epilogue runs under the
+// next tile's main loop. Who signals whom: both CTAs' copies complete on the first CTA's `full` barrier (its
+// producer expects the bytes of both); the MMA thread's commits arrive on the `empty` and `tmem_full` barriers of
+// both CTAs (`tcgen05.commit ... multicast::cluster`, an arrival, not a load); the epilogue warps of both CTAs
+// arrive on the first CTA's `tmem_empty`. No copy is multicast: each CTA fetches what it stages.
+struct PairCfg {
+  static constexpr int A_BYTES = TILE_A * TILE_K * 2;   // this CTA's 128 token rows of a K step
+  static constexpr int B_BYTES = 128 * TILE_K * 2;      // this CTA's half of the 256 weight rows
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = 6;
+  static constexpr int NCOLS = 256;
+  static constexpr int EPI_WARPS = 4;
+  static constexpr int PROD2_WARP = 2 + EPI_WARPS;
+  static constexpr int THREADS = 32 * (PROD2_WARP + 1);
+  static constexpr int STAGING = EPI_WARPS * 2 * STAGING_BUF;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + STAGING + 1024 + 512;
+};
+
+__device__ __forceinline__ uint32_t pair_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// The shared::cluster address of the first CTA's copy of a shared-memory object of this CTA.
+__device__ __forceinline__ uint32_t in_first_cta(const void* p) {
+  uint32_t a;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(a) : "r"(smem_u32(p)));
+  return a;
+}
+__device__ __forceinline__ void pair_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void pair_tma_load_2d(void* dst, const CUtensorMap* map, uint32_t bar_first, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(bar_first), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void pair_mbar_arrive_first(uint32_t bar_first) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_first) : "memory");
+}
+__device__ __forceinline__ void pair_tmem_alloc(uint32_t* dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void pair_tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void pair_tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void pair_umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// An arrival on the barrier at this offset in both CTAs of the pair, once the MMAs issued so far are done.
+__device__ __forceinline__ void pair_umma_commit(uint64_t* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(smem_u32(bar)), "h"((uint16_t)3)
+      : "memory");
+}
+// M = 256 over the pair (128 rows per CTA), N = 256.
+__host__ __device__ constexpr uint32_t pair_instr_desc() {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+
+template <bool DUAL>
+__global__ void __launch_bounds__(PairCfg::THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmO, const Params p) {
+  using C = PairCfg;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* staging = smem + C::STAGES * C::STAGE_BYTES;
+  uint64_t* full = (uint64_t*)(staging + C::STAGING);
+  uint64_t* empty = full + C::STAGES;
+  uint64_t* tmem_full = empty + C::STAGES;   // [2]
+  uint64_t* tmem_empty = tmem_full + 2;      // [2]
+  uint32_t* tmem_slot = (uint32_t*)(tmem_empty + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  volatile int* seg_ok = (volatile int*)(tmem_slot + 2);  // [2]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = pair_rank();
+  const bool first = rank == 0;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  pdl_trigger();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&full[s], 1);   // the first CTA's producer, with the bytes of both CTAs' copies
+      mbar_init(&empty[s], 1);  // the MMA thread's commit
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], 2 * C::EPI_WARPS);  // one arrival per epilogue warp of either CTA
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    pair_tmem_alloc(tmem_slot, 512);
+    pair_tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  pair_sync();  // the other CTA's barriers exist before anything of this CTA signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // tile t: 256 token rows from a0, 256 weight rows (SwiGLU: 128 gate and 128 up) for the output columns from b0
+  auto tile_a0 = [&](int t) { return (t % p.tiles_a) * 256; };
+  auto tile_b0 = [&](int t) { return (t / p.tiles_a) * (DUAL ? 128 : 256); };
+  // this CTA's half of the weight rows: the first CTA's rows become accumulator columns 0..127, the second's 128..255
+  auto weight_row = [&](int b0) { return DUAL ? (first ? b0 : p.N + b0) : b0 + (int)rank * 128; };
+
+  if ((warp == 0 || warp == C::PROD2_WARP) && lane == 0) {
+    // ------------------------------------------------ producers of this CTA: stages in turn
+    const int mine = warp == 0 ? 0 : 1;
+    uint32_t full_first[C::STAGES];
+#pragma unroll
+    for (int s = 0; s < C::STAGES; ++s) full_first[s] = in_first_cta(&full[s]);
+    // the first ring of weight tiles is requested before waiting for the predecessor kernel
+    {
+      int it = 0;
+      for (int t = pair; t < p.tiles && it < C::STAGES; t += n_pairs)
+        for (int ks = 0; ks < p.ksteps && it < C::STAGES; ++ks, ++it) {
+          if (it % NPROD != mine) continue;
+          if (first) mbar_expect_tx(&full[it], 2 * C::STAGE_BYTES);
+          pair_tma_load_2d(smem + it * C::STAGE_BYTES + C::A_BYTES, &tmB, full_first[it], ks * TILE_K, weight_row(tile_b0(t)));
+        }
+    }
+    pdl_wait();
+    int it = 0;
+    bool ok = true;
+    for (int t = pair; ok && t < p.tiles; t += n_pairs) {
+      const int a0 = tile_a0(t) + (int)rank * TILE_A, wr = weight_row(tile_b0(t));
+      for (int ks = 0; ks < p.ksteps; ++ks, ++it) {
+        if (it % NPROD != mine) continue;
+        const int st = it % C::STAGES;
+        uint8_t* sp = smem + st * C::STAGE_BYTES;
+        if (it >= C::STAGES) {
+          if (!mbar_wait(&empty[st], ((it / C::STAGES) & 1) ^ 1, p.err, abort_flag)) { ok = false; break; }
+          if (first) mbar_expect_tx(&full[st], 2 * C::STAGE_BYTES);
+          pair_tma_load_2d(sp + C::A_BYTES, &tmB, full_first[st], ks * TILE_K, wr);
+        }
+        pair_tma_load_2d(sp, &tmA, full_first[st], ks * TILE_K, a0);  // rows past M read as zeros
+      }
+    }
+  } else if (warp == 1 && lane == 0 && first) {
+    // ------------------------------------------------ MMA issuer of the pair
+    pdl_wait();
+    constexpr uint32_t idesc = pair_instr_desc();
+    int it = 0, seg = 0;
+    bool ok = true;
+    for (int t = pair; ok && t < p.tiles; t += n_pairs, ++seg) {
+      const int buf = seg & 1;
+      if (!mbar_wait(&tmem_empty[buf], ((seg >> 1) & 1) ^ 1, p.err, abort_flag)) break;
+      tc_fence_after();
+      const uint32_t acc = tmem_base + buf * C::NCOLS;
+      for (int ks = 0; ks < p.ksteps; ++ks, ++it) {
+        const int st = it % C::STAGES;
+        if (!mbar_wait(&full[st], (it / C::STAGES) & 1, p.err, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + st * C::STAGE_BYTES);
+        const uint64_t adesc = smem_desc(sa), bdesc = smem_desc(sa + C::A_BYTES);
+#pragma unroll
+        for (int k = 0; k < TILE_K / UMMA_K; ++k) {
+          const uint64_t koff = (uint64_t)(k * UMMA_K * 2 >> 4);
+          pair_umma_bf16(acc, adesc + koff, bdesc + koff, idesc, (ks > 0 || k > 0) ? 1u : 0u);
+        }
+        pair_umma_commit(&empty[st]);
+      }
+      if (ok) pair_umma_commit(&tmem_full[buf]);
+    }
+  } else if (warp >= 2 && warp < 2 + C::EPI_WARPS) {
+    // ------------------------------------------------ epilogue of this CTA's 128 rows
+    pdl_wait();
+    const int quarter = warp & 3;
+    const int eidx = (warp - 2) * 32 + lane;
+    uint32_t empty_first[2] = {in_first_cta(&tmem_empty[0]), in_first_cta(&tmem_empty[1])};
+    int seg = 0, chunk_no = 0;
+    for (int t = pair; t < p.tiles; t += n_pairs, ++seg) {
+      const int buf = seg & 1;
+      if (eidx == 0) seg_ok[buf] = mbar_wait(&tmem_full[buf], (seg >> 1) & 1, p.err, abort_flag) ? 1 : 0;
+      epilogue_sync_n<32 * C::EPI_WARPS>();
+      if (!seg_ok[buf]) break;
+      tc_fence_after();
+      const uint32_t acc = tmem_base + buf * C::NCOLS + ((uint32_t)(quarter * 32) << 16);
+      tma_epilogue<DUAL, 2>(p, &tmO, acc, tile_a0(t) + (int)rank * TILE_A, tile_b0(t), DUAL ? 128 : 256, true, quarter,
+                            lane, staging + (warp - 2) * (2 * STAGING_BUF), chunk_no);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) pair_mbar_arrive_first(empty_first[buf]);
+    }
+    if (lane == 0) bulk_wait_all();  // this thread's stores have left shared memory and landed
+  }
+  __syncwarp();
+  if (*abort_flag) {
+    // let copies in flight land before the shared memory is handed to another CTA
+    unsigned long long t0 = global_ns();
+    while (global_ns() - t0 < 2000000ull) { }
+  }
+  tc_fence_before();
+  __syncthreads();
+  pair_sync();  // neither CTA leaves (or frees tensor memory) while the other may still signal it or read its stages
+  if (warp == 1) pair_tmem_dealloc(tmem_base, 512);
+}
+
 // ------------------------------------------------------------------ host side
 }  // namespace
 int cuca_device_sms() {
@@ -746,6 +967,49 @@ int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap&
   return 0;
 }
 
+template <bool DUAL>
+int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmO, const Params& p, int grid,
+                cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::SMEM);
+    if (e != cudaSuccess) {
+      cuca_set_error("gemm_tc: cannot reserve %d bytes of shared memory: %s", PairCfg::SMEM, cudaGetErrorString(e));
+      return 2;
+    }
+    configured = true;
+  }
+  // as many pairs as are resident together (a cluster lies within one GPC, so an odd SM there stays idle)
+  static int resident_pairs = 0;
+  if (!resident_pairs) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (cuca_device_sms() / 2));
+    cfg.blockDim = dim3(PairCfg::THREADS);
+    cfg.dynamicSmemBytes = PairCfg::SMEM;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<DUAL>, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = cuca_device_sms() / 2;
+    }
+    resident_pairs = n;
+  }
+  if (grid > 2 * resident_pairs) grid = 2 * resident_pairs;
+  cudaError_t e = cuca_launch_cluster(gemm_pair_kernel<DUAL>, dim3(grid), dim3(PairCfg::THREADS), PairCfg::SMEM, stream, true, 2,
+                                      tmA, tmB, tmO, p);
+  if (e != cudaSuccess) {
+    cuca_set_error("gemm_tc: launch of a pair kernel failed: %s", cudaGetErrorString(e));
+    return 2;
+  }
+  CUCA_CHECK_LAUNCH("gemm_tc pair");
+  return 0;
+}
+
 }  // namespace
 
 // 1 when the tensor-core kernel takes this problem, else 0 with the reason in cuca_last_error().
@@ -755,6 +1019,11 @@ CUCA_API int cuca_gemm_tc_supported(const void* A, const void* W, int M, int N, 
   if (M <= 0 || N <= 0) { cuca_set_error("gemm_tc: empty problem"); return 0; }
   return 1;
 }
+
+// When the two-SM form runs: 1 by the rule in gemm_tc_impl, 0 never, 2 wherever it can (tests and measurements),
+// -1 as the environment variable CUCA_GEMM_PAIR says (1 without it).
+static int allow_pair = -1;
+CUCA_API void cuca_gemm_pair_mode(int mode) { allow_pair = mode; }
 
 // out = epilogue(A[M,K] W[N,K]^T), bf16 operands. workspace/counters: scratch for tiles split along K
 // (ws_bytes of 32-bit partials; n_counters zeroed ints, left zeroed). max_splits <= 1: whole tiles only.
@@ -807,6 +1076,32 @@ static int gemm_tc_impl(const void* A, const void* W, const void* bias, void* ou
     const long long t256 = (long long)((M + 2 * TILE_A - 1) / (2 * TILE_A)) * tiles_b;
     const long long rounds128 = (t128 + sms - 1) / sms, rounds256 = (t256 + sms - 1) / sms;
     tall = allow == 2 || (allow == 1 && rounds256 * 19 < rounds128 * 10);
+  }
+  // The two-SM form (gemm_pair_kernel): CUCA_GEMM_PAIR=0 never, =2 wherever it is allowed.
+  bool pair = false;
+  if (!swap && tma_out && epilogue != EPI_PARTIAL && M > TILE_A && sms >= 2) {
+    if (allow_pair < 0) { const char* e = getenv("CUCA_GEMM_PAIR"); allow_pair = e ? atoi(e) : 1; }
+    // Rounds of tiles times what a round costs in each form, in units of a 128 x 256 tile's time (measured on the
+    // Llama-3.1-8B widths at 1,024 to 4,096 tokens: a tall tile 1.9 to 2.1, a pair's tile 0.93 to 0.97; with K above
+    // 8,192 the pair lost to the tall form by 5 to 7 %, so it counts as 1.02 there).
+    const long long t128 = (long long)((M + TILE_A - 1) / TILE_A) * tiles_b;
+    const long long t256 = (long long)((M + 2 * TILE_A - 1) / (2 * TILE_A)) * tiles_b;
+    const int pairs = sms / 2;
+    const double cost128 = (double)((t128 + sms - 1) / sms);
+    const double cost_tall = (double)((t256 + sms - 1) / sms) * 1.95;
+    const double cost_pair = (double)((t256 + pairs - 1) / pairs) * (K > 8192 ? 1.02 : 0.96);
+    pair = allow_pair == 2 || (allow_pair == 1 && t256 >= pairs && cost_pair < cost128 && cost_pair < (tall ? cost_tall : 1e30));
+  }
+  if (pair) {
+    p.tile_rows = 2 * TILE_A;
+    p.tiles_a = (M + p.tile_rows - 1) / p.tile_rows;
+    p.tiles = p.tiles_a * tiles_b;
+    p.ksteps = (K + TILE_K - 1) / TILE_K;
+    p.tma_out = 1;
+    p.ordered_add = p.skew = p.stream_k = p.pieces = p.piece_w = 0;
+    p.per_tile = p.max_parts = 1;
+    const int pairs = p.tiles < sms / 2 ? p.tiles : sms / 2;
+    return dual ? launch_pair<true>(tmA, tmB, tmO, p, 2 * pairs, stream) : launch_pair<false>(tmA, tmB, tmO, p, 2 * pairs, stream);
   }
   p.tile_rows = tall ? 2 * TILE_A : TILE_A;
   p.tiles_a = swap ? (N + TILE_A - 1) / TILE_A : (M + p.tile_rows - 1) / p.tile_rows;
@@ -880,6 +1175,11 @@ static int gemm_tc_impl(const void* A, const void* W, const void* bias, void* ou
         p.max_parts = per_tile;
         grid = per_tile * p.tiles;
       }
+    } else if (!swap && 2 * p.tiles >= sms) {
+      // many tokens, tiles for more than half of the SMs: one whole tile per CTA. Dealing the K steps out over all
+      // SMs costs more in the last-arriver reduction than the idle SMs do (768 tokens, down projection of the
+      // Llama-3.1-8B widths, 96 tiles: 127.6 us dealt out).
+      grid = p.tiles;
     } else {
       long long g = units / 2 < sms ? units / 2 : sms;
       long long per = units / g;  // smallest share

@@ -151,6 +151,13 @@ def gemm_tc(a, w, out, epilogue=EPI_STORE, bias=None, err=None, max_splits=16) -
                                    int(max_splits), _p(err), _stream()), "gemm_tc")
 
 
+def gemm_pair_mode(mode: int) -> None:
+    """When contractions over many tokens run as pairs of CTAs on one tile (`tcgen05.mma.cta_group::2`): 1 where
+    the library's rule expects them to be faster, 0 never, 2 wherever they can (tests and measurements), -1 as the
+    environment variable CUCA_GEMM_PAIR says."""
+    library.load().cuca_gemm_pair_mode(int(mode))
+
+
 def gemm(a, w, out, epilogue=EPI_STORE, bias=None, err=None) -> None:
     """out = epilogue(a @ w.T), on the kernel that fits dtype and shape: tensor cores for bfloat16
     (rows of 16-byte multiples), CUDA cores for the 32-bit path and for shapes the former refuses."""

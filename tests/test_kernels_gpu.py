@@ -77,6 +77,33 @@ def test_gemm_tcgen05(dev, M, N, K, epilogue, max_splits):
     assert int(ops.gemm_scratch(dev)[1].abs().sum().item()) == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(129, 256, 64), (256, 256, 512), (300, 384, 136), (512, 1000, 320), (2048, 4096, 512),
+                                   (1300, 5000, 1160), (700, 20000, 264)])
+@pytest.mark.parametrize("epilogue", [0, 1, 2])
+def test_gemm_tcgen05_pairs_of_ctas(dev, M, N, K, epilogue):
+    """The two-SM form (a cluster of two CTAs on a tile of 256 tokens x 256 weight rows, `cta_group::2`), forced for
+    every shape it takes: ragged rows and columns, K no multiple of the stage, more tiles than pairs."""
+    from cuca_b200.kernels import ops
+    g = torch.Generator(device=dev).manual_seed(M * 7 + N + K + epilogue)
+    a = torch.randn(M, K, device=dev, generator=g).bfloat16()
+    rows = N * (2 if epilogue == ops.EPI_SWIGLU else 1)
+    w = (torch.randn(rows, K, device=dev, generator=g) / math.sqrt(K)).bfloat16()
+    bias = torch.randn(N, device=dev, generator=g).bfloat16() if epilogue == ops.EPI_STORE else None
+    out = torch.randn(M, N, device=dev, generator=g).to(torch.float32 if epilogue == ops.EPI_RESIDUAL else torch.bfloat16)
+    prior = out.float().clone()
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    ops.gemm_pair_mode(2)
+    try:
+        ops.gemm_tc(a, w, out, epilogue, bias, err)
+        torch.cuda.synchronize()
+    finally:
+        ops.gemm_pair_mode(-1)
+    assert int(err.item()) == 0
+    want = _ref_gemm(a, w, epilogue, bias, prior)
+    tol = 2e-3 if epilogue == ops.EPI_RESIDUAL else 2e-2
+    assert torch.allclose(out.float(), want, atol=tol, rtol=tol), float((out.float() - want).abs().max())
+
+
 @pytest.mark.parametrize("M,N,K,out_dtype,epilogue", [
     (256, 4096, 512, torch.float32, 1), (200, 3072, 192, torch.bfloat16, 0), (130, 4000, 1024, torch.float32, 0),
     (300, 2001, 320, torch.bfloat16, 0), (65, 6144, 256, torch.bfloat16, 0)])
