@@ -188,6 +188,8 @@ class LocalModel:
         self.config = config
         self.sizes = sizes
         self.backend = GpuBackend(core)
+        if self.backend.use_graphs:
+            self.backend.graphs.prime(config.batching.max_sequences)
         self.scheduler = Scheduler(core.pools, core.slots, self.backend, SchedulerConfig(
             max_sequences=config.batching.max_sequences, max_step_tokens=sizes["max_step_tokens"],
             prefill_chunk=sizes["prefill_chunk"], context_length=sizes["context_length"],

@@ -57,8 +57,18 @@ def test_logits_inside_captured_graphs_match_plain(tmp_path_factory, which):
     cfgj, weights = plain_llama.load_model_dir(d)
     vocab = cfgj["vocab_size"]
     prompts = [tiny.random_tokens(n, vocab, seed=500 + n) for n in (2, 61, 200, 500)]
-    m = LocalModel.load(LocalModelConfig(source=str(d), dtype="bfloat16", batching=BatchingConfig(max_sequences=4)))
-    be, seen = m.backend, []
+    from cuca_b200.engine.graphs import DecodeGraphs
+    DecodeGraphs.keep_logits = True  # the graphs of this engine keep the logits of their last replay
+    try:
+        m = LocalModel.load(LocalModelConfig(source=str(d), dtype="bfloat16", batching=BatchingConfig(max_sequences=4)))
+        be, seen = m.backend, []
+        _logits_of_graph_steps(m, be, seen, prompts, cfgj, weights)
+    finally:
+        DecodeGraphs.keep_logits = False
+
+
+def _logits_of_graph_steps(m, be, seen, prompts, cfgj, weights):
+    import torch
     run_graph = be._run_decode_graph
 
     def spy(plans):
