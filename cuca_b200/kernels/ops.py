@@ -307,15 +307,14 @@ def decode_chunking(n_rows: int, n_kv_heads: int, max_len: int, head_dim: int = 
     if forced:
         n = max(1, min(32, tiles, int(forced)))
         return -(-tiles // n) * 64, n
-    smem = 3 * 2 * 64 * (head_dim + 8) * 2 + 2048  # three stages of a key and a value tile
-    slots = sms * max(1, min(8, (227 * 1024) // smem))
+    slots = _decode_slots(head_dim, sms)
     pairs = max(1, n_rows * n_kv_heads)
     best, best_cost = 1, None
     for n in range(1, min(32, tiles) + 1):
         rounds = -(-pairs * n // slots)
-        # the merge: none for one chunk, through distributed shared memory up to a cluster's eight chunks, through
-        # global memory and a last arriver beyond (measured: about a tile's time more, and growing with the chunks)
-        merge = 0 if n == 1 else 2 if (CLUSTER_MERGE and n <= MAX_CLUSTER) else 10 + n // 2
+        # the merge: none for one chunk, through distributed shared memory where a row's chunks run as a cluster,
+        # through global memory and a last arriver else (measured: about a tile's time more, growing with the chunks)
+        merge = 0 if n == 1 else 2 if _merge_as_cluster(pairs, n, slots) else 10 + n // 2
         cost = rounds * (-(-tiles // n) + 3) * 8 + merge
         if best_cost is None or cost < best_cost:
             best, best_cost = n, cost
@@ -326,10 +325,26 @@ CLUSTER_MERGE = os.environ.get("CUCA_ATTN_CLUSTER", "1") != "0"
 MAX_CLUSTER = 8  # the portable cluster size
 
 
+def _decode_slots(head_dim: int, sms: int | None = None) -> int:
+    """CTAs of the decode attention that are resident at once."""
+    smem = 3 * 2 * 64 * (head_dim + 8) * 2 + 2048  # three stages of a key and a value tile
+    return (sms or sm_count()) * max(1, min(8, (227 * 1024) // smem))
+
+
+def _merge_as_cluster(pairs: int, n_splits: int, slots: int) -> bool:
+    """Whether a row's chunk CTAs run as a thread-block cluster and merge through distributed shared memory. Only
+    where all CTAs of the launch are resident together: a cluster's CTAs keep their places until its slowest one
+    has finished, which costs nothing in a single round and a lot in several (Llama-2-13B shape, batch 8, 320
+    (row, head) pairs in four chunks each, five rounds: 8.88 ms a step as clusters, 8.00 ms merged through global
+    memory). And only for 2, 4 or 8 chunks: clusters of other sizes fill a GPC's SMs badly (same shape, batch 1, seven
+    chunks: 6.01 ms as clusters, 5.61 ms through global memory; four or eight chunks: no difference)."""
+    return CLUSTER_MERGE and n_splits in (2, 4, 8) and pairs * n_splits <= slots
+
+
 def _decode_scratch(device, n_rows, n_heads, n_kv_heads, head_dim, n_splits):
     """Scratch of a split-key decode launch, or (None, None) when the row's chunk CTAs merge as a thread-block
-    cluster through distributed shared memory (up to eight chunks): nothing then goes through global memory."""
-    if n_splits == 1 or (CLUSTER_MERGE and n_splits <= MAX_CLUSTER):
+    cluster through distributed shared memory: nothing then goes through global memory."""
+    if n_splits == 1 or _merge_as_cluster(n_rows * n_kv_heads, n_splits, _decode_slots(head_dim)):
         return None, None
     return attention_scratch(device, n_rows * n_heads * n_splits * (head_dim + 2), n_rows * n_kv_heads)
 
