@@ -332,13 +332,14 @@ def _decode_slots(head_dim: int, sms: int | None = None) -> int:
 
 
 def _merge_as_cluster(pairs: int, n_splits: int, slots: int) -> bool:
-    """Whether a row's chunk CTAs run as a thread-block cluster and merge through distributed shared memory. Only
-    where all CTAs of the launch are resident together: a cluster's CTAs keep their places until its slowest one
-    has finished, which costs nothing in a single round and a lot in several (Llama-2-13B shape, batch 8, 320
-    (row, head) pairs in four chunks each, five rounds: 8.88 ms a step as clusters, 8.00 ms merged through global
-    memory). And only for 2, 4 or 8 chunks: clusters of other sizes fill a GPC's SMs badly (same shape, batch 1, seven
-    chunks: 6.01 ms as clusters, 5.61 ms through global memory; four or eight chunks: no difference)."""
-    return CLUSTER_MERGE and n_splits in (2, 4, 8) and pairs * n_splits <= slots
+    """Whether a row's chunk CTAs run as a thread-block cluster and merge through distributed shared memory. A
+    cluster's CTAs keep their places until its slowest one has finished, a cluster lies within one GPC, and sizes
+    that do not divide a GPC's places leave some empty: so only where every cluster is resident at once (clusters of
+    two or four: the launch fits the GPU's places; of eight: half of them, since eight pack a GPC's places badly),
+    and only for 2, 4 or 8 chunks. Measured: Llama-3.1-8B shape, batch 1, eight chunks: +1.3 % tokens/s as clusters;
+    batch 8, 64 clusters of four (256 of 296 places): +0.5 %; batch 4, 32 clusters of eight (256 places): -9 %;
+    Llama-2-13B shape, batch 8, 1,280 CTAs in five rounds: -11 %; batch 1, clusters of seven: -7 %."""
+    return CLUSTER_MERGE and n_splits in (2, 4, 8) and pairs * n_splits * (2 if n_splits == 8 else 1) <= slots
 
 
 def _decode_scratch(device, n_rows, n_heads, n_kv_heads, head_dim, n_splits):
