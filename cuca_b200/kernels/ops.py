@@ -6,6 +6,7 @@ back to torch operators.
 """
 from __future__ import annotations
 
+import ctypes
 import os
 
 import torch
@@ -24,7 +25,15 @@ def dtype_code(dtype: torch.dtype) -> int:
         raise library.KernelError(f"kernels take float32 or bfloat16, not {dtype}") from None
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current stream's handle. Asked of torch's C entry where there is one: `torch.cuda.current_stream()` builds
+    a Python object per call, 2.5 us of the 19 us of host time that a launch cost (a prompt step of a few tokens is
+    230 launches whose kernels take 16 us each: the host set its pace)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -134,9 +143,19 @@ def gemm_scratch(device):
     return _scratch[key]
 
 
+_tc_supported: dict = {}
+
+
 def gemm_tc_supported(a, w) -> bool:
-    lib = library.load()
-    return bool(lib.cuca_gemm_tc_supported(_p(a), _p(w), a.shape[0], w.shape[0], a.shape[1], a.stride(0)))
+    """Whether the tensor-core kernel takes this problem (the library's answer, remembered by what it depends on:
+    K, the row stride, the operands' alignment and whether the problem is empty)."""
+    pa, pw = a.data_ptr(), w.data_ptr()
+    key = (a.shape[1], a.stride(0), pa & 15, pw & 15, a.shape[0] > 0, w.shape[0] > 0)
+    ok = _tc_supported.get(key)
+    if ok is None:
+        lib = library.load()
+        ok = _tc_supported[key] = bool(lib.cuca_gemm_tc_supported(pa, pw, a.shape[0], w.shape[0], a.shape[1], a.stride(0)))
+    return ok
 
 
 def gemm_tc(a, w, out, epilogue=EPI_STORE, bias=None, err=None, max_splits=16) -> None:
@@ -508,22 +527,28 @@ def gemm_partial_supported(a, w) -> bool:
             and gemm_tc_supported(a, w))
 
 
+_partial_slices: dict = {}  # (rows, features, K, most slices) -> slices the kernel writes
+_slices_written = ctypes.c_int(0)  # where a launch reports how many it wrote
+_SLICES_WRITTEN_AT = ctypes.addressof(_slices_written)
+
+
 def gemm_partial(a, w, err=None, max_slices=16) -> PartialSums:
     """a @ w.T for few rows (`partial_max_tokens`), as partial sums over K slices (see `PartialSums`)."""
     _cuda(a, w)
     lib = library.load()
     M, K = a.shape
     N = w.shape[0]
-    slices = lib.cuca_gemm_tc_partial_slices(M, N, K, max_slices)
+    key = (M, N, K, max_slices)
+    slices = _partial_slices.get(key)
+    if slices is None:
+        slices = _partial_slices[key] = int(lib.cuca_gemm_tc_partial_slices(M, N, K, max_slices))
     if slices <= 0:
         raise library.KernelError("gemm_partial: unsupported shape")
     data = torch.empty(slices, M, N, dtype=torch.float32, device=a.device)
-    import ctypes
-    got = ctypes.c_int(0)
     library.check(lib.cuca_gemm_tc_partial(_p(a), _p(w), _p(data), M, N, K, a.stride(0), max_slices,
-                                           ctypes.addressof(got), _p(err), _stream()), "gemm_partial")
-    if got.value != slices:
-        raise library.KernelError(f"gemm_partial: {got.value} slices written, {slices} expected")
+                                           _SLICES_WRITTEN_AT, _p(err), _stream()), "gemm_partial")
+    if _slices_written.value != slices:
+        raise library.KernelError(f"gemm_partial: {_slices_written.value} slices written, {slices} expected")
     return PartialSums(data, slices)
 
 
