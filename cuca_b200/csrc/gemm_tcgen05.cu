@@ -66,6 +66,7 @@ struct Params {
   int tma_out;   // many tokens: whole tiles leave through shared memory and the copy engine (tensor map of `out`)
   int ordered_add;  // mode 2 into the 32-bit stream over many tokens: the K slices of a tile add themselves in turn
   int skew;         // ... and slice k + 1 has `skew` K steps more than slice k, so that it finishes when slice k has added
+  int slab_rows;    // pairs of CTAs leaving K slices unadded: rows of one slice's slab in `out` (a multiple of 32, >= M)
 };
 
 constexpr int STAGING_BUF = 32 * 128;  // 32 rows of 128 bytes
@@ -277,7 +278,7 @@ __device__ __forceinline__ void store16(const Params& p, int a0, int b0, int lan
 template <bool DUAL, int BUFS = 2>
 __device__ __forceinline__ void tma_epilogue(const Params& p, const CUtensorMap* tmO, uint32_t acc, int a0, int b0,
                                              int width, bool with_bias, int quarter, int lane, uint8_t* staging,
-                                             int& chunk_no) {
+                                             int& chunk_no, int row_offset = 0) {
   const int y0 = a0 + quarter * 32;
   const int ch = p.out_f32 ? 32 : 64;  // the host cuts column pieces in whole runs
   uint8_t* const my_row = staging + lane * 128;
@@ -325,7 +326,7 @@ __device__ __forceinline__ void tma_epilogue(const Params& p, const CUtensorMap*
       if (y0 < p.M && b0 + c < p.N) {
         const void* src = staging + (chunk_no % BUFS) * STAGING_BUF;
         if (p.epilogue == EPI_RESIDUAL) tma_reduce_add_2d(tmO, src, b0 + c, y0);
-        else tma_store_2d(tmO, src, b0 + c, y0);
+        else tma_store_2d(tmO, src, b0 + c, y0 + row_offset);  // row_offset: the slab of a K slice left unadded
       }
       bulk_commit();
     }
@@ -756,9 +757,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // tile t: 256 token rows from a0, 256 weight rows (SwiGLU: 128 gate and 128 up) for the output columns from b0
+  // unit u: K slice (u % per_tile) of tile (u / per_tile); a tile is 256 token rows from a0 and 256 weight rows
+  // (SwiGLU: 128 gate and 128 up) for the output columns from b0. With more than one slice per tile the slices stay
+  // unadded: slice k goes to slab k of `out` (EPI_PARTIAL) for the kernel that reads them next.
+  const int units = p.tiles * p.per_tile;
   auto tile_a0 = [&](int t) { return (t % p.tiles_a) * 256; };
   auto tile_b0 = [&](int t) { return (t / p.tiles_a) * (DUAL ? 128 : 256); };
+  auto ks_first = [&](int u) { return (int)((long long)(u % p.per_tile) * p.ksteps / p.per_tile); };
+  auto ks_end = [&](int u) { return (int)((long long)(u % p.per_tile + 1) * p.ksteps / p.per_tile); };
   // this CTA's half of the weight rows: the first CTA's rows become accumulator columns 0..127, the second's 128..255
   auto weight_row = [&](int b0) { return DUAL ? (first ? b0 : p.N + b0) : b0 + (int)rank * 128; };
 
@@ -771,19 +777,21 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // the first ring of weight tiles is requested before waiting for the predecessor kernel
     {
       int it = 0;
-      for (int t = pair; t < p.tiles && it < C::STAGES; t += n_pairs)
-        for (int ks = 0; ks < p.ksteps && it < C::STAGES; ++ks, ++it) {
+      for (int u = pair; u < units && it < C::STAGES; u += n_pairs)
+        for (int ks = ks_first(u); ks < ks_end(u) && it < C::STAGES; ++ks, ++it) {
           if (it % NPROD != mine) continue;
           if (first) mbar_expect_tx(&full[it], 2 * C::STAGE_BYTES);
-          pair_tma_load_2d(smem + it * C::STAGE_BYTES + C::A_BYTES, &tmB, full_first[it], ks * TILE_K, weight_row(tile_b0(t)));
+          pair_tma_load_2d(smem + it * C::STAGE_BYTES + C::A_BYTES, &tmB, full_first[it], ks * TILE_K,
+                           weight_row(tile_b0(u / p.per_tile)));
         }
     }
     pdl_wait();
     int it = 0;
     bool ok = true;
-    for (int t = pair; ok && t < p.tiles; t += n_pairs) {
+    for (int u = pair; ok && u < units; u += n_pairs) {
+      const int t = u / p.per_tile;
       const int a0 = tile_a0(t) + (int)rank * TILE_A, wr = weight_row(tile_b0(t));
-      for (int ks = 0; ks < p.ksteps; ++ks, ++it) {
+      for (int ks = ks_first(u); ks < ks_end(u); ++ks, ++it) {
         if (it % NPROD != mine) continue;
         const int st = it % C::STAGES;
         uint8_t* sp = smem + st * C::STAGE_BYTES;
@@ -801,12 +809,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     constexpr uint32_t idesc = pair_instr_desc();
     int it = 0, seg = 0;
     bool ok = true;
-    for (int t = pair; ok && t < p.tiles; t += n_pairs, ++seg) {
+    for (int u = pair; ok && u < units; u += n_pairs, ++seg) {
       const int buf = seg & 1;
       if (!mbar_wait(&tmem_empty[buf], ((seg >> 1) & 1) ^ 1, p.err, abort_flag)) break;
       tc_fence_after();
       const uint32_t acc = tmem_base + buf * C::NCOLS;
-      for (int ks = 0; ks < p.ksteps; ++ks, ++it) {
+      const int ks0 = ks_first(u);
+      for (int ks = ks0; ks < ks_end(u); ++ks, ++it) {
         const int st = it % C::STAGES;
         if (!mbar_wait(&full[st], (it / C::STAGES) & 1, p.err, abort_flag)) { ok = false; break; }
         tc_fence_after();
@@ -815,7 +824,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
         for (int k = 0; k < TILE_K / UMMA_K; ++k) {
           const uint64_t koff = (uint64_t)(k * UMMA_K * 2 >> 4);
-          pair_umma_bf16(acc, adesc + koff, bdesc + koff, idesc, (ks > 0 || k > 0) ? 1u : 0u);
+          pair_umma_bf16(acc, adesc + koff, bdesc + koff, idesc, (ks > ks0 || k > 0) ? 1u : 0u);
         }
         pair_umma_commit(&empty[st]);
       }
@@ -828,15 +837,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int eidx = (warp - 2) * 32 + lane;
     uint32_t empty_first[2] = {in_first_cta(&tmem_empty[0]), in_first_cta(&tmem_empty[1])};
     int seg = 0, chunk_no = 0;
-    for (int t = pair; t < p.tiles; t += n_pairs, ++seg) {
-      const int buf = seg & 1;
+    for (int u = pair; u < units; u += n_pairs, ++seg) {
+      const int buf = seg & 1, t = u / p.per_tile;
       if (eidx == 0) seg_ok[buf] = mbar_wait(&tmem_full[buf], (seg >> 1) & 1, p.err, abort_flag) ? 1 : 0;
       epilogue_sync_n<32 * C::EPI_WARPS>();
       if (!seg_ok[buf]) break;
       tc_fence_after();
       const uint32_t acc = tmem_base + buf * C::NCOLS + ((uint32_t)(quarter * 32) << 16);
       tma_epilogue<DUAL, 2>(p, &tmO, acc, tile_a0(t) + (int)rank * TILE_A, tile_b0(t), DUAL ? 128 : 256, true, quarter,
-                            lane, staging + (warp - 2) * (2 * STAGING_BUF), chunk_no);
+                            lane, staging + (warp - 2) * (2 * STAGING_BUF), chunk_no, (u % p.per_tile) * p.slab_rows);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) pair_mbar_arrive_first(empty_first[buf]);
@@ -869,7 +878,7 @@ int cuca_device_sms() {
 }
 
 // Most tokens for which a contraction can leave its K slices unadded (cuca_gemm_tc_partial).
-CUCA_API int cuca_gemm_tc_partial_max_tokens() { return SWAP_MAX_TOKENS; }
+CUCA_API int cuca_gemm_tc_partial_max_tokens();
 
 // How many SMs the current device has (the Python side sizes its split choices by it too).
 CUCA_API int cuca_sm_count() { return cuca_device_sms(); }
@@ -1020,9 +1029,36 @@ CUCA_API int cuca_gemm_tc_supported(const void* A, const void* W, int M, int N, 
   return 1;
 }
 
+// K slices left unadded (cuca_gemm_tc_partial) over more than 128 tokens come from pairs of CTAs: a tile of 256
+// tokens x 256 weight rows stages 32 KB per SM and K step where the one-SM forms stage 48 (and every CTA of the
+// weights-as-rows form re-reads all tokens), and whole 32-row boxes of a slice leave through the copy engine.
+constexpr int PAIR_PARTIAL_MAX_TOKENS = 512;
+// Slices per tile of that form: the count that makes the rounds of (tile, slice) units over the pairs, times a
+// unit's K steps plus about eight steps' worth of start and epilogue, the shortest; a step's worth per slice for
+// what writing and re-reading it costs. (q/k/v at 512 tokens: 48 tiles as three slices each in two rounds of 22
+// K steps, rather than one round of 64 on 48 of the 74 pairs.)
+static int pair_partial_slices(int M, int N, int K, int max_slices) {
+  const int pairs = cuca_device_sms() / 2;
+  const int tiles = ((M + 255) / 256) * ((N + 255) / 256), ksteps = (K + TILE_K - 1) / TILE_K;
+  int best = 1;
+  long long best_cost = -1;
+  for (int n = 1; n <= max_slices && (n == 1 || 2 * n <= ksteps); ++n) {
+    const long long rounds = ((long long)tiles * n + pairs - 1) / pairs;
+    const long long cost = rounds * ((ksteps + n - 1) / n + 8) + n;
+    if (best_cost < 0 || cost < best_cost) { best = n; best_cost = cost; }
+  }
+  return best;
+}
+static int sms_pairs() { return cuca_device_sms() / 2; }
+static int allow_pair = -1;
+static bool pair_partial_takes(int M, int N) {
+  if (allow_pair < 0) { const char* e = getenv("CUCA_GEMM_PAIR"); allow_pair = e ? atoi(e) : 1; }
+  // rows of the 32-bit output are 16-byte multiples (the copy engine stores them)
+  return allow_pair != 0 && M > TILE_A && M <= PAIR_PARTIAL_MAX_TOKENS && N % 4 == 0 && cuca_device_sms() >= 2;
+}
+
 // When the two-SM form runs: 1 by the rule in gemm_tc_impl, 0 never, 2 wherever it can (tests and measurements),
 // -1 as the environment variable CUCA_GEMM_PAIR says (1 without it).
-static int allow_pair = -1;
 CUCA_API void cuca_gemm_pair_mode(int mode) { allow_pair = mode; }
 
 // out = epilogue(A[M,K] W[N,K]^T), bf16 operands. workspace/counters: scratch for tiles split along K
@@ -1035,8 +1071,31 @@ static int gemm_tc_impl(const void* A, const void* W, const void* bias, void* ou
   CUCA_REQUIRE(epilogue != EPI_RESIDUAL || out_dtype == CUCA_F32, "gemm_tc: the residual stream is 32-bit");
   CUCA_REQUIRE(epilogue != EPI_SWIGLU || (bias == nullptr && out_dtype == CUCA_BF16), "gemm_tc: SwiGLU writes bf16, no bias");
   const bool dual = epilogue == EPI_SWIGLU;
-  const bool swap = M <= (epilogue == EPI_SWIGLU ? SWAP_MAX_TOKENS_SWIGLU : SWAP_MAX_TOKENS);
   CUCA_REQUIRE(epilogue >= 0 && epilogue <= EPI_PARTIAL, "gemm_tc: unknown epilogue %d", epilogue);
+  if (epilogue == EPI_PARTIAL && pair_partial_takes(M, N)) {
+    CUCA_REQUIRE(out_dtype == CUCA_F32 && bias == nullptr && n_slices_out != nullptr && ((uintptr_t)out & 15) == 0, "gemm_tc: partial sums are 32-bit, without bias, in rows of 16-byte multiples");
+    const int per_tile = pair_partial_slices(M, N, K, max_splits);
+    const int slab_rows = (M + 31) / 32 * 32;
+    CUtensorMap tmA, tmB, tmO;
+    CUCA_REQUIRE(cuca_tensor_map_bf16(A, M, K, lda, TILE_A, &tmA), "gemm_tc: activation tensor map failed");
+    CUCA_REQUIRE(cuca_tensor_map_bf16(W, N, K, K, 128, &tmB), "gemm_tc: weight tensor map failed");
+    CUCA_REQUIRE(cuca_tensor_map_2d(out, 4, (uint64_t)per_tile * slab_rows, N, N, 32, &tmO), "gemm_tc: output tensor map failed");
+    Params p;
+    p.out = out; p.bias = nullptr; p.workspace = nullptr; p.counters = nullptr; p.err = err;
+    p.M = M; p.N = N; p.K = K; p.ldo = N; p.epilogue = EPI_PARTIAL; p.out_f32 = 1;
+    p.tile_rows = 2 * TILE_A;
+    p.tiles_a = (M + 255) / 256;
+    p.tiles = p.tiles_a * ((N + 255) / 256);
+    p.ksteps = (K + TILE_K - 1) / TILE_K;
+    p.tma_out = 1;
+    p.ordered_add = p.skew = p.stream_k = p.pieces = p.piece_w = 0;
+    p.per_tile = per_tile; p.max_parts = 1; p.slab_rows = slab_rows;
+    *n_slices_out = per_tile;
+    const long long units = (long long)p.tiles * per_tile;
+    const int pairs = units < sms_pairs() ? (int)units : sms_pairs();
+    return launch_pair<false>(tmA, tmB, tmO, p, 2 * pairs, stream);
+  }
+  const bool swap = M <= (epilogue == EPI_SWIGLU ? SWAP_MAX_TOKENS_SWIGLU : SWAP_MAX_TOKENS);
   const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
   const uint64_t w_rows = (uint64_t)N * (dual ? 2 : 1);
   CUtensorMap tmA, tmB, tmO;
@@ -1100,6 +1159,7 @@ static int gemm_tc_impl(const void* A, const void* W, const void* bias, void* ou
     p.tma_out = 1;
     p.ordered_add = p.skew = p.stream_k = p.pieces = p.piece_w = 0;
     p.per_tile = p.max_parts = 1;
+    p.slab_rows = 0;
     const int pairs = p.tiles < sms / 2 ? p.tiles : sms / 2;
     return dual ? launch_pair<true>(tmA, tmB, tmO, p, 2 * pairs, stream) : launch_pair<false>(tmA, tmB, tmO, p, 2 * pairs, stream);
   }
@@ -1220,9 +1280,17 @@ CUCA_API int cuca_gemm_tc(const void* A, const void* W, const void* bias, void* 
                       n_counters, max_splits, nullptr, err, stream);
 }
 
+CUCA_API int cuca_gemm_tc_partial_max_tokens() { return pair_partial_takes(PAIR_PARTIAL_MAX_TOKENS, 4) ? PAIR_PARTIAL_MAX_TOKENS : SWAP_MAX_TOKENS; }
+
+// Rows of one slice's slab in the output of cuca_gemm_tc_partial for this many tokens (at least M; the two-SM form
+// stores whole boxes of 32 rows, so its slabs are padded to a multiple of 32) and N features.
+CUCA_API int cuca_gemm_tc_partial_rows(int M, int N) { return pair_partial_takes(M, N) ? (M + 31) / 32 * 32 : M; }
+
 // How many K slices cuca_gemm_tc_partial will write for this shape (the first dimension of its output).
 CUCA_API int cuca_gemm_tc_partial_slices(int M, int N, int K, int max_slices) {
-  if (M > SWAP_MAX_TOKENS || M <= 0 || N <= 0 || K <= 0) return 0;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (pair_partial_takes(M, N)) return pair_partial_slices(M, N, K, max_slices);
+  if (M > SWAP_MAX_TOKENS) return 0;
   const int sms = cuca_device_sms();
   const int tiles = (N + TILE_A - 1) / TILE_A, ksteps = (K + TILE_K - 1) / TILE_K;
   int per_tile = sms / tiles;
@@ -1232,9 +1300,10 @@ CUCA_API int cuca_gemm_tc_partial_slices(int M, int N, int K, int max_slices) {
   return per_tile;
 }
 
-// partial[slice][M][N] (32-bit) = A[M, K slice] W[N, K slice]^T for up to 256 tokens: the K slices of a tile are
-// not added up here (no workspace, no counters, no second pass); the kernel that reads the result adds them in
-// slice order. *n_slices gets the number of slices written (cuca_gemm_tc_partial_slices of the same shape).
+// partial[slice][rows][N] (32-bit) = A[M, K slice] W[N, K slice]^T for up to cuca_gemm_tc_partial_max_tokens()
+// tokens, rows = cuca_gemm_tc_partial_rows(M): the K slices of a tile are not added up here (no workspace, no
+// counters, no second pass); the kernel that reads the result adds them in slice order. *n_slices gets the number
+// of slices written (cuca_gemm_tc_partial_slices of the same shape).
 CUCA_API int cuca_gemm_tc_partial(const void* A, const void* W, float* partial, int M, int N, int K, int lda,
                                   int max_slices, int* n_slices, int* err, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;

@@ -175,6 +175,8 @@ def gemm_pair_mode(mode: int) -> None:
     the library's rule expects them to be faster, 0 never, 2 wherever they can (tests and measurements), -1 as the
     environment variable CUCA_GEMM_PAIR says."""
     library.load().cuca_gemm_pair_mode(int(mode))
+    _partial_slices.clear()  # what was remembered of the library's choices depended on the mode
+    _partial_max.clear()
 
 
 def gemm(a, w, out, epilogue=EPI_STORE, bias=None, err=None) -> None:
@@ -522,12 +524,23 @@ def partial_max_tokens() -> int:
     return _partial_max[0]
 
 
+def _partial_plan(M: int, N: int, K: int, max_slices: int):
+    """(slices, rows of a slice's slab) the library will use for this shape; slices 0: it does not take it."""
+    key = (M, N, K, max_slices)
+    plan = _partial_slices.get(key)
+    if plan is None:
+        lib = library.load()
+        plan = _partial_slices[key] = (int(lib.cuca_gemm_tc_partial_slices(M, N, K, max_slices)),
+                                       int(lib.cuca_gemm_tc_partial_rows(M, N)))
+    return plan
+
+
 def gemm_partial_supported(a, w) -> bool:
     return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[0] <= partial_max_tokens()
-            and gemm_tc_supported(a, w))
+            and gemm_tc_supported(a, w) and _partial_plan(a.shape[0], w.shape[0], a.shape[1], 16)[0] > 0)
 
 
-_partial_slices: dict = {}  # (rows, features, K, most slices) -> slices the kernel writes
+_partial_slices: dict = {}  # (rows, features, K, most slices) -> (slices the kernel writes, rows of a slice's slab)
 _slices_written = ctypes.c_int(0)  # where a launch reports how many it wrote
 _SLICES_WRITTEN_AT = ctypes.addressof(_slices_written)
 
@@ -538,13 +551,12 @@ def gemm_partial(a, w, err=None, max_slices=16) -> PartialSums:
     lib = library.load()
     M, K = a.shape
     N = w.shape[0]
-    key = (M, N, K, max_slices)
-    slices = _partial_slices.get(key)
-    if slices is None:
-        slices = _partial_slices[key] = int(lib.cuca_gemm_tc_partial_slices(M, N, K, max_slices))
+    plan = _partial_plan(M, N, K, max_slices)
+    slices, slab_rows = plan
     if slices <= 0:
         raise library.KernelError("gemm_partial: unsupported shape")
-    data = torch.empty(slices, M, N, dtype=torch.float32, device=a.device)
+    # a slice's slab may be padded to the rows its kernel stores at once; the readers see [slices, M, N] of it
+    data = torch.empty(slices, slab_rows, N, dtype=torch.float32, device=a.device)[:, :M]
     library.check(lib.cuca_gemm_tc_partial(_p(a), _p(w), _p(data), M, N, K, a.stride(0), max_slices,
                                            _SLICES_WRITTEN_AT, _p(err), _stream()), "gemm_partial")
     if _slices_written.value != slices:
@@ -565,6 +577,12 @@ def add_partials(x, partial: PartialSums) -> None:
     lib = library.load()
     library.check(lib.cuca_add_partials(_p(x), _p(partial.data), partial.slices, partial.slice_stride, x.numel(),
                                         _stream()), "add_partials")
+
+
+# Most rows for which q/k/v are made from unadded slices: beyond, the rotate-and-store kernel that adds them (one
+# block per row, every slice read again) costs more than the slices save (first token of a 300-token prompt on the
+# Llama-3.1-8B shape: 7.9 ms that way, 7.4 ms with the projection written out and rotated in place).
+ROPE_PARTIAL_MAX_ROWS = 256
 
 
 def rope_store_partial(partial: PartialSums, bias, q_out, positions, seq_of_row, tables, cos, sin, rotary_dim, kpool,

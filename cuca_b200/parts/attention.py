@@ -95,7 +95,8 @@ class PagedAttention(Mixer):
         fused = self.position.fused_tables() if self.position is not None else None
         kpool, vpool = (None, None) if nkv == 0 else (cache.k, cache.v)
         plan = self.plan(step)
-        if fused is not None and self.rt.use_partials and ops.gemm_partial_supported(h, self.w_qkv):
+        if (fused is not None and self.rt.use_partials and h.shape[0] <= ops.ROPE_PARTIAL_MAX_ROWS
+                and ops.gemm_partial_supported(h, self.w_qkv)):
             # few tokens: the projection leaves its K slices unadded; rotate-and-store adds them in 32-bit
             cos, sin, rot = fused
             parts = ops.gemm_partial(h, self.w_qkv, self.rt.err)
