@@ -177,7 +177,8 @@ def contraction_table(args, token_counts) -> int:
             ws = [(torch.randn(rows, K, device=dev, generator=g) / math.sqrt(K)).bfloat16() for _ in range(sets)]
             out = torch.zeros(M, N, device=dev, dtype=odt)
             ref = torch.empty(M, rows, device=dev, dtype=torch.bfloat16)
-            if epi != ops.EPI_SWIGLU and ops.gemm_partial_supported(a, ws[0]):
+            if epi != ops.EPI_SWIGLU and ops.gemm_partial_supported(a, ws[0]) and \
+                    (name != "qkv" or M <= ops.ROPE_PARTIAL_MAX_ROWS):
                 # as the engine runs it over few tokens: K slices left unadded for the kernel that reads them next
                 ours = best_us(lambda: [ops.gemm_partial(a, w, err) for w in ws])
                 line.setdefault("unadded_slices", []).append(name)
