@@ -556,7 +556,9 @@ def gemm_partial(a, w, err=None, max_slices=16) -> PartialSums:
     if slices <= 0:
         raise library.KernelError("gemm_partial: unsupported shape")
     # a slice's slab may be padded to the rows its kernel stores at once; the readers see [slices, M, N] of it
-    data = torch.empty(slices, slab_rows, N, dtype=torch.float32, device=a.device)[:, :M]
+    data = torch.empty(slices, slab_rows, N, dtype=torch.float32, device=a.device)
+    if slab_rows != M:
+        data = data[:, :M]
     library.check(lib.cuca_gemm_tc_partial(_p(a), _p(w), _p(data), M, N, K, a.stride(0), max_slices,
                                            _SLICES_WRITTEN_AT, _p(err), _stream()), "gemm_partial")
     if _slices_written.value != slices:
