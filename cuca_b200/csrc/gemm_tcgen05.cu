@@ -18,7 +18,9 @@
 // turn. With few tiles (decode: 32 to 1002 tiles of 64 K steps on 148 SMs) the units are dealt out evenly
 // ("stream-K"): a CTA's share may start and end inside a tile; partial tiles go to a workspace and the last CTA
 // to arrive adds the parts in K order (the result does not depend on arrival order) and runs the epilogue.
-// With many tokens and a last round of tiles that would leave SMs idle, only that round's tiles are dealt out so.
+// Over many tokens there are two more forms of a tile: the tall one (256 tokens x 256 weight rows in one CTA, see
+// Cfg) and the two-SM one (a cluster of two CTAs on such a tile, tcgen05.mma.cta_group::2, see gemm_pair_kernel),
+// which also produces the K slices left unadded (EPI_PARTIAL) from 129 to 512 tokens.
 //
 // The kernel is a programmatic dependent: it requests its first ring of weight tiles before waiting for its
 // predecessor, since weights are never written. Every wait on an mbarrier is bounded; on a timeout the kernel
@@ -58,7 +60,7 @@ struct Params {
   int tiles;     // all tiles
   int ksteps;    // K steps per tile
   int stream_k;  // 0: whole tiles in turn; 1: units dealt out evenly; 2: per_tile even K slices of every tile
-  // more than 64 tokens but fewer tiles than SMs (mode 0): instead of whole tiles, `pieces` column pieces of
+  // tokens as rows but fewer tiles than SMs (mode 0): instead of whole tiles, `pieces` column pieces of
   // `piece_w` output columns over all of K, one per CTA
   int pieces, piece_w;
   int per_tile;  // mode 2: CTAs per tile
@@ -1176,7 +1178,7 @@ static int gemm_tc_impl(const void* A, const void* W, const void* bias, void* ou
   p.pieces = p.piece_w = 0;
   p.per_tile = 1;
   p.max_parts = 1;
-  // More than 64 tokens, fewer tiles than SMs, K not long: column pieces as narrow as it takes for about one per SM,
+  // Tokens as rows (more than 256 of them), fewer tiles than SMs, K not long: column pieces as narrow as it takes for about one per SM,
   // each over all of K, so nothing is added up afterwards. (Measured at 256 tokens, K = 4096: 31 us against 57 us
   // with K slices; with K = 14336 no gain. A piece's main loop runs at the pace of its loads, 4 stages deep, not
   // of its MMAs, so a piece takes as long as a whole tile: cutting the last round of many tiles this way gains
