@@ -64,6 +64,7 @@ SHAPES = {
                      "theta 5e5, llama3 factor 32 low 1 high 4 original 8192"),
 }
 PREFILL_TOKENS = 2048
+SETTLE_S = 0.3  # idle time between the prompts' prefill and a decode measurement's warm-up steps
 
 
 def peaks() -> dict:
@@ -321,6 +322,12 @@ def main() -> int:
             raise RuntimeError("bench: the prompts did not all reach the decode phase: "
                                + ", ".join(sorted({s.phase for s in seqs})))
         tokens = [s.pending for s in seqs]
+        # The prompts' prefill leaves the SM clock where the power cap held it, and it comes back in stages over
+        # the next 70 ms: the first ten decode steps after it take 4.2 ms, the next ten 3.7, then 3.57. A short
+        # idle pause lets the clock recover before the warm-up steps, so that K = 20 timed steps show the steady
+        # decode rate that K = 128 shows without it (named in `config.settle`).
+        torch.cuda.synchronize()
+        time.sleep(SETTLE_S)
         hist = backend.burst(seqs, tokens, warmup)
         tokens = hist[-1].tolist()
         ctx0 = seqs[0].blocks.length
@@ -442,6 +449,7 @@ def main() -> int:
             "kv_block_size": 16, "decode_context": round(mean_ctx, 1), "prefill_tokens": PREFILL_TOKENS,
             "l2": "no flush: a step reads %.1f GB, far above the 126 MB L2" % (step_bytes / 1e9),
             "parallelism": "1 GPU",
+            "settle": "%.1f s idle between the prompts and a decode measurement's warm-up steps" % SETTLE_S,
         },
         "e2e": e2e, "gpu_launches": int(launches_per_step * (point_steps if mixed else args.steps)),
         "launches_per_step": launches_per_step,
