@@ -57,6 +57,8 @@ struct Params {
   const int* tile_nrows;
   int n_blocks, bs, nh, nkv;
   int heads_per_cta;     // 2: a CTA takes two query heads of one key/value head (even group size); else 1
+  int n_tiles;           // tiles of the launch (heaviest first)
+  int pair_tiles;        // 1: CTA b takes tile b and then tile n_tiles - 1 - b (a heavy and a light one)
   float scale_log2e;
   int window;
   int* err;
@@ -184,21 +186,37 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     return;
   }
   // This CTA's query tiles: the same rows for `nq` consecutive query heads, which share their key/value head.
-  const int tile = blockIdx.x;
   const int nq = p.heads_per_cta;             // 1 or NQ
   const int head0 = blockIdx.y * nq;
+  const int kvh = head0 / (p.nh / p.nkv);
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  // One tile, or two in turn: with a causal mask the tiles of a prompt differ in their keys by up to the prompt's
+  // length, and the host's list has the heaviest first, so CTA b takes tile b and then tile n - 1 - b: equal work
+  // for every CTA and one round of CTAs where the tiles alone would need two (a 2,048-token prompt of the
+  // Llama-3.1-8B shape: 256 tiles x head pairs on 148 SMs). Between the two the barriers are set up anew.
+  const int second = p.n_tiles - 1 - (int)blockIdx.x;
+  const int n_items = (p.pair_tiles && second != (int)blockIdx.x) ? 2 : 1;
+  uint32_t tmem_base = 0;
+  for (int item = 0; item < n_items; ++item) {
+  const int tile = item == 0 ? (int)blockIdx.x : second;
   const int row0 = p.tile_row0[tile], n_rows = p.tile_nrows[tile];
   const int seq = p.seq_of_row[row0];
-  if (seq < 0) return;
   const int pos0 = p.positions[row0];
-  const int kvh = head0 / (p.nh / p.nkv);
   const int lo_min = (p.window > 0 && pos0 - (p.window - 1) > 0) ? pos0 - (p.window - 1) : 0;
   const int hi = pos0 + n_rows;                       // keys [lo_min, hi) matter
   const int first_tile = lo_min / KEYS;
   const int n_tiles = (hi - 1) / KEYS - first_tile + 1;
-  const int* table = p.tables + (size_t)seq * p.table_stride;
+  const int* table = p.tables + (size_t)(seq < 0 ? 0 : seq) * p.table_stride;
 
   if (threadIdx.x == 0) {
+    if (item > 0) {
+      // every thread has left the first tile (the barrier below it): its barriers are dead and set up again
+      for (uint64_t* b = bars; b < (uint64_t*)tmem_slot; ++b)
+        asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(b)) : "memory");
+    }
     mbar_init(q_full, 1);
     for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], nq); }  // one commit per query tile
     for (int x = 0; x < NQ; ++x) {
@@ -207,21 +225,20 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       mbar_init(&p_full[x], 128);
       mbar_init(&pv_done[x], 1);
     }
-    *abort_flag = 0;
+    if (item == 0) *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 1) {
-    tmem_alloc(tmem_slot, TMEM_COLS);
-    tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  tmem_base = *tmem_slot;
   // query tile x: scores of key tile t in columns [64 (2 x + t % 2), + 64), output in [256 + 128 x, + 128)
   auto tmem_s = [&](int x, int t) { return tmem_base + (uint32_t)((2 * x + (t & 1)) * KEYS); };
   auto tmem_o = [&](int x) { return tmem_base + (uint32_t)(2 * NQ * KEYS + x * D); };
 
+  if (seq < 0) {
+    // a tile of padding rows: nothing to do
+  } else
   if (warp == 0) {
     // ------------------------------------------------ producer: the Q tiles once, then K and V tiles page by page.
     // Lane 0 issues the copies; the warp reads the block table 32 entries at a time (one coalesced load for
@@ -464,6 +481,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
   }
   __syncwarp();
+  tc_fence_before();
+  __syncthreads();  // every role is done with this tile: its barriers may be set up anew, tensor memory reused
+  if (*abort_flag) break;
+  }
   if (*abort_flag) {
     unsigned long long t0 = global_ns();
     while (global_ns() - t0 < 2000000ull) { }
@@ -485,7 +506,8 @@ int launch_attn_tc(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtenso
                  cudaGetErrorString(e));
     configured = true;
   }
-  cuca_launch(attn_tc_kernel<D>, dim3(n_tiles, p.nh / p.heads_per_cta), dim3(NTHREADS), smem, stream, true, tmQ, tmK, tmV, p);
+  const int grid_x = p.pair_tiles ? (n_tiles + 1) / 2 : n_tiles;
+  cuca_launch(attn_tc_kernel<D>, dim3(grid_x, p.nh / p.heads_per_cta), dim3(NTHREADS), smem, stream, true, tmQ, tmK, tmV, p);
   CUCA_CHECK_LAUNCH("attention_prefill_tc");
   return 0;
 }
@@ -526,5 +548,13 @@ CUCA_API int cuca_attention_prefill_tc(const void* q, int q_stride, int n_rows_t
   p.n_blocks = n_blocks; p.bs = bs; p.nh = nh; p.nkv = nkv; p.scale_log2e = scale * 1.4426950408889634f;
   p.window = window; p.err = err;
   p.heads_per_cta = ((nh / nkv) % NQ == 0) ? NQ : 1;
+  p.n_tiles = n_tiles;
+  // Two tiles per CTA, a heavy and a light one, where that makes one round of CTAs out of more than one
+  // (CUCA_ATTN_PAIR_TILES=0 never, =2 whenever there are two tiles).
+  static int pair_mode = -1;
+  if (pair_mode < 0) { const char* e = getenv("CUCA_ATTN_PAIR_TILES"); pair_mode = e ? atoi(e) : 1; }
+  const int head_ctas = nh / p.heads_per_cta, sms = cuca_device_sms();
+  p.pair_tiles = n_tiles >= 2 && (pair_mode == 2 || (pair_mode == 1 && n_tiles * head_ctas > sms &&
+                                                     ((n_tiles + 1) / 2) * head_ctas <= sms)) ? 1 : 0;
   return d == 128 ? launch_attn_tc<128>(tmQ, tmK, tmV, p, n_tiles, stream) : launch_attn_tc<64>(tmQ, tmK, tmV, p, n_tiles, stream);
 }
