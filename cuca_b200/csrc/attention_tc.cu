@@ -525,6 +525,11 @@ CUCA_API int cuca_attention_tc_supported(int nh, int nkv, int d, int bs, int q_s
   return 1;
 }
 
+// Two tiles per CTA in the tcgen05 prefill attention: 1 where it makes one round of CTAs out of more, 0 never, 2
+// whenever a launch has two tiles (tests), -1 as the environment variable CUCA_ATTN_PAIR_TILES says (1 without it).
+static int pair_mode = -1;
+CUCA_API void cuca_attention_pair_tiles_mode(int mode) { pair_mode = mode; }
+
 // Prefill form on tcgen05: tile i covers rows tile_row0[i] .. +tile_nrows[i]-1 (at most 128 consecutive rows of
 // one request). q: [n_rows_total][q_stride] with the rotated query heads first; out: [..][out_stride].
 CUCA_API int cuca_attention_prefill_tc(const void* q, int q_stride, int n_rows_total, void* out, int out_stride,
@@ -551,7 +556,6 @@ CUCA_API int cuca_attention_prefill_tc(const void* q, int q_stride, int n_rows_t
   p.n_tiles = n_tiles;
   // Two tiles per CTA, a heavy and a light one, where that makes one round of CTAs out of more than one
   // (CUCA_ATTN_PAIR_TILES=0 never, =2 whenever there are two tiles).
-  static int pair_mode = -1;
   if (pair_mode < 0) { const char* e = getenv("CUCA_ATTN_PAIR_TILES"); pair_mode = e ? atoi(e) : 1; }
   const int head_ctas = nh / p.heads_per_cta, sms = cuca_device_sms();
   p.pair_tiles = n_tiles >= 2 && (pair_mode == 2 || (pair_mode == 1 && n_tiles * head_ctas > sms &&

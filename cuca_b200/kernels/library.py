@@ -58,6 +58,7 @@ _SIGNATURES = {
     "cuca_sm_count": [],
     "cuca_gemm_tc_partial_max_tokens": [],
     "cuca_gemm_pair_mode": [_I],
+    "cuca_attention_pair_tiles_mode": [_I],
     "cuca_gemm_tc_partial_rows": [_I, _I],
     "cuca_wait_probe": [ctypes.c_ulonglong, _P, _P, _P],
     "cuca_attention_tile_rows": [_I],

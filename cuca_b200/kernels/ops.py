@@ -419,6 +419,13 @@ def attention_tc_supported(q, out, kpool, vpool, n_heads, n_kv_heads, head_dim) 
                                                 out.stride(0), _p(q), _p(kpool), _p(vpool)))
 
 
+def attention_pair_tiles_mode(mode: int) -> None:
+    """When a CTA of the tcgen05 prefill attention takes two tiles in turn (a heavy and a light one): 1 where that
+    makes one round of CTAs out of more, 0 never, 2 whenever a launch has two tiles (tests), -1 as the environment
+    variable CUCA_ATTN_PAIR_TILES says."""
+    library.load().cuca_attention_pair_tiles_mode(int(mode))
+
+
 def attention_prefill_tc(q, out, kpool, vpool, positions, seq_of_row, tables, tile_row0, tile_nrows, n_tiles,
                          n_heads, n_kv_heads, head_dim, scale, window, err) -> None:
     """Prefill attention on tcgen05; tiles of up to 128 consecutive rows of one request."""

@@ -564,13 +564,15 @@ def test_rope_store_from_partial_sums(dev):
 @pytest.mark.parametrize("nh,nkv,bs,window", [(4, 2, 16, None), (8, 8, 32, None), (8, 2, 16, 150), (2, 1, 8, None),
                                               (3, 1, 64, 40)])
 @pytest.mark.parametrize("d", [128, 64])
-def test_attention_prefill_tcgen05(dev, nh, nkv, bs, window, d):
+@pytest.mark.parametrize("two_tiles_per_cta", [False, True])
+def test_attention_prefill_tcgen05(dev, nh, nkv, bs, window, d, two_tiles_per_cta):
     """Prefill attention on tcgen05 (head size 128 or 64): portions that start at position 0 and in the middle of a
-    request, tiles of 128 rows and ragged tails, several key tiles, against 32-bit attention."""
+    request, tiles of 128 rows and ragged tails, several key tiles, against 32-bit attention; with one tile per CTA
+    and with two in turn (an odd number of tiles, so that the middle one stays alone)."""
     from cuca_b200.kernels import ops
     dtype = torch.bfloat16
-    lens = [5, 128, 200, 390, 131]
-    starts = [0, 0, 33, 129, 129]
+    lens = [5, 128, 200, 390, 131, 60]
+    starts = [0, 0, 33, 129, 129, 0]   # nine tiles
     k, v, kpool, vpool, tables = _paged_setup(dev, dtype, lens, nh, nkv, d, bs,
                                               n_blocks=sum(-(-l // bs) for l in lens) + 3, seed=6)
     g = torch.Generator(device=dev).manual_seed(8)
@@ -591,11 +593,15 @@ def test_attention_prefill_tcgen05(dev, nh, nkv, bs, window, d):
     out = torch.zeros(T, nh * d, device=dev, dtype=dtype)
     err = torch.zeros(1, dtype=torch.int32, device=dev)
     assert ops.attention_tc_supported(qkv, out, kpool, vpool, nh, nkv, d)
-    ops.attention_prefill_tc(qkv, out, kpool, vpool, positions, seq, tables,
-                             torch.tensor(tile_row0, dtype=torch.int32, device=dev),
-                             torch.tensor(tile_nrows, dtype=torch.int32, device=dev), len(tile_row0), nh, nkv, d,
-                             1.0 / math.sqrt(d), window, err)
-    torch.cuda.synchronize()
+    ops.attention_pair_tiles_mode(2 if two_tiles_per_cta else 0)
+    try:
+        ops.attention_prefill_tc(qkv, out, kpool, vpool, positions, seq, tables,
+                                 torch.tensor(tile_row0, dtype=torch.int32, device=dev),
+                                 torch.tensor(tile_nrows, dtype=torch.int32, device=dev), len(tile_row0), nh, nkv, d,
+                                 1.0 / math.sqrt(d), window, err)
+        torch.cuda.synchronize()
+    finally:
+        ops.attention_pair_tiles_mode(-1)
     assert int(err.item()) == 0
     for r in range(T):
         s, pos = seq_list[r], pos_list[r]
