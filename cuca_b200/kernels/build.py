@@ -92,9 +92,58 @@ def _compile_one(nvcc: str, src: Path, obj: Path, log: Path) -> tuple[Path, floa
     return src, time.time() - t0
 
 
+class _BuildLock:
+    """One builder at a time per build folder, across processes (two programs started together in a fresh checkout
+    would otherwise write the same object files at once)."""
+
+    def __init__(self, d: Path, verbose: bool):
+        self.path, self.verbose, self.f = d / ".build.lock", verbose, None
+
+    def __enter__(self):
+        import fcntl
+        self.f = open(self.path, "w")
+        try:
+            fcntl.flock(self.f, fcntl.LOCK_EX | fcntl.LOCK_NB)
+        except OSError:
+            if self.verbose:
+                _say("another process is building the kernel library; waiting for it")
+            fcntl.flock(self.f, fcntl.LOCK_EX)
+        return self
+
+    def __exit__(self, *exc):
+        import fcntl
+        fcntl.flock(self.f, fcntl.LOCK_UN)
+        self.f.close()
+
+
 def build(verbose: bool = True, force: bool = False) -> Path:
     """Bring the library up to date and return its path."""
     d = build_dir()
+    lib = _up_to_date(d) if not force else None
+    if lib is not None:
+        return lib
+    with _BuildLock(d, verbose):
+        return _build_locked(d, verbose, force)
+
+
+def _up_to_date(d: Path):
+    """The library's path if every source's hash is the one it was built from, else None."""
+    lib = d / LIB_NAME
+    try:
+        manifest = json.loads((d / "manifest.json").read_text())
+    except (OSError, ValueError):
+        return None
+    hh = _headers_hash()
+    srcs = sources()
+    if not srcs or not lib.is_file() or set(manifest) != {s.name for s in srcs}:
+        return None
+    for s in srcs:
+        if manifest.get(s.name) != hashlib.sha1(s.read_bytes()).hexdigest() + hh:
+            return None
+    return lib
+
+
+def _build_locked(d: Path, verbose: bool, force: bool) -> Path:
     lib = d / LIB_NAME
     manifest_path = d / "manifest.json"
     try:
