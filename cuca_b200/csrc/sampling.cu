@@ -95,9 +95,10 @@ __device__ int block_scan_i(int v, Shared& sh, int* total) {
   return r;
 }
 
-__device__ int block_argmax(const float* row, int V, Shared& sh) {
+// The largest (value, then lowest id) of row[lo..hi) as one 64-bit word: key of the value above 0xFFFFFFFF - id.
+__device__ unsigned long long block_argmax_word(const float* row, int lo, int hi, Shared& sh) {
   unsigned long long best = 0ull;
-  for (int i = threadIdx.x; i < V; i += NT) {
+  for (int i = lo + threadIdx.x; i < hi; i += NT) {
     float v = row[i];
     unsigned k = (v != v) ? 0u : ((__float_as_uint(v) & 0x80000000u) ? ~__float_as_uint(v) : (__float_as_uint(v) | 0x80000000u));
     unsigned long long c = composite(k, (unsigned)i);
@@ -113,11 +114,15 @@ __device__ int block_argmax(const float* row, int V, Shared& sh) {
   best = sh.red64[0];
   for (int i = 1; i < NT / 32; ++i) best = sh.red64[i] > best ? sh.red64[i] : best;
   __syncthreads();
+  return best;
+}
+__device__ __forceinline__ int argmax_id(unsigned long long best) {
   unsigned key = (unsigned)(best >> 32);
   // nothing above -inf: id 0, as the reference's greedy()
   if (key <= 0x007FFFFFu) return 0;  // key of -inf is ~0xFF800000 = 0x007FFFFF
   return (int)(0xFFFFFFFFu - (unsigned)(best & 0xFFFFFFFFull));
 }
+__device__ int block_argmax(const float* row, int V, Shared& sh) { return argmax_id(block_argmax_word(row, 0, V, sh)); }
 
 // The m best candidates by (key desc, id asc) into sh.cand[0..m) sorted; m <= SMEM_CAND, m <= n_finite.
 __device__ void select_sorted(const float* row, int V, float temp, int m, Shared& sh) {
@@ -285,23 +290,59 @@ __global__ void __launch_bounds__(NT)
 sample_kernel(const float* __restrict__ logits, size_t row_stride, int V, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p, unsigned long long* __restrict__ rng,
               const int* __restrict__ slot_of_row, int* __restrict__ out, unsigned long long* __restrict__ scratch,
-              int scratch_stride) {
+              int scratch_stride, unsigned long long* __restrict__ split_best, int* __restrict__ split_count) {
   __shared__ Shared sh;
+  __shared__ int last_of_row;
   pdl_trigger();
   pdl_wait();
   const int r = blockIdx.x;
+  const int n_split = gridDim.y, part = blockIdx.y;
   const float* row = logits + (size_t)r * row_stride;
   const int slot = slot_of_row[r];
   if (slot < 0) {  // a padding row of a fixed-size batch
-    if (threadIdx.x == 0) out[r] = -1;
+    if (threadIdx.x == 0 && part == 0) out[r] = -1;
     return;
   }
   const float temp = temperature[slot];
   if (!(temp > 0.f) || V <= 1) {
-    int id = block_argmax(row, V, sh);
-    if (threadIdx.x == 0) out[r] = id;
+    if (n_split == 1) {
+      int id = block_argmax(row, V, sh);
+      if (threadIdx.x == 0) out[r] = id;
+      return;
+    }
+    // A greedy row of a large vocabulary, cut over the CTAs of the row (one CTA alone reads 128,256 logits in
+    // 28 us at its own pace): each takes the best of its part, the last to arrive takes the best of those. The
+    // word orders by value, then by lowest id, so the result is the one CTA's.
+    const int per = (V + n_split - 1) / n_split;
+    const int lo = part * per, hi = min(V, lo + per);
+    const unsigned long long best = block_argmax_word(row, lo, hi, sh);
+    if (threadIdx.x == 0) {
+      split_best[(size_t)r * n_split + part] = best;
+      __threadfence();
+      last_of_row = atomicAdd(&split_count[r], 1) == n_split - 1 ? 1 : 0;
+    }
+    __syncthreads();
+    if (!last_of_row) return;
+    __threadfence();
+    if (threadIdx.x < 32) {
+      unsigned long long b = 0ull;
+      for (int i = threadIdx.x; i < n_split; i += 32) {
+        const unsigned long long c = *reinterpret_cast<volatile unsigned long long*>(&split_best[(size_t)r * n_split + i]);
+        b = c > b ? c : b;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        unsigned long long other = __shfl_xor_sync(0xffffffffu, b, o);
+        b = other > b ? other : b;
+      }
+      if (threadIdx.x == 0) {
+        out[r] = argmax_id(b);
+        split_count[r] = 0;  // ready for the next launch
+      }
+    }
     return;
   }
+  if (part > 0) return;  // a row that draws is one CTA's work
   const int K = top_k[slot];
   const float P = top_p[slot];
   unsigned long long* state = rng + slot;
@@ -474,15 +515,27 @@ CUCA_API int cuca_sample_scratch_stride(int V) {
 // One token per row. temperature/top_k/top_p and rng (SplitMix64 states, advanced once per drawn token)
 // are per request slot and indexed by slot_of_row[r]. scratch: n_rows * scratch_stride 64-bit words (may be null: rows that
 // would need it then yield -1).
+// split_best / split_count (may be null): split_rows x CUCA_SAMPLE_MAX_SPLIT 64-bit words and split_rows zeroed
+// counters (left zeroed), with which the greedy rows of a large vocabulary are cut over several CTAs each.
+CUCA_API int cuca_sample_max_split() { return 32; }
 CUCA_API int cuca_sample(const float* logits, size_t row_stride, int n_rows, int V, const float* temperature,
                          const int* top_k, const float* top_p, unsigned long long* rng, const int* slot_of_row,
-                         int* out, unsigned long long* scratch, int scratch_stride, cudaStream_t stream) {
+                         int* out, unsigned long long* scratch, int scratch_stride, unsigned long long* split_best,
+                         int* split_count, int split_rows, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   CUCA_REQUIRE(V > 0, "sample: empty vocabulary");
   CUCA_REQUIRE(scratch == nullptr || scratch_stride >= cuca_sample_scratch_stride(V),
                "sample: scratch rows of %d words are too short for a vocabulary of %d", scratch_stride, V);
-  cuca_launch(sample_kernel, dim3(n_rows), dim3(NT), 0, stream, true, logits, row_stride, V, temperature, top_k, top_p,
-              rng, slot_of_row, out, scratch, scratch_stride);
+  // about 8 K logits per CTA; rows times parts need not exceed a few hundred CTAs
+  int n_split = 1;
+  if (split_best && split_count && n_rows <= split_rows) {
+    n_split = (V + 8191) / 8192;
+    if (n_split > cuca_sample_max_split()) n_split = cuca_sample_max_split();
+    while (n_split > 1 && n_rows * n_split > 1024) n_split /= 2;
+    if (n_split < 1) n_split = 1;
+  }
+  cuca_launch(sample_kernel, dim3(n_rows, n_split), dim3(NT), 0, stream, true, logits, row_stride, V, temperature, top_k, top_p,
+              rng, slot_of_row, out, scratch, scratch_stride, split_best, split_count);
   CUCA_CHECK_LAUNCH("sample");
   return 0;
 }

@@ -62,6 +62,7 @@ class GpuBackend:
         self._scratch = None
         self.suppress = None  # int32 ids whose logits are set to -inf before sampling
         self._needs_scratch = [False] * n
+        self.sample_split = ops.SampleSplit(max(n, 64), dev)  # greedy rows of a large vocabulary: several CTAs a row
         self.vocab = core.spec.vocab_size
         self.use_graphs = core.model.graph_safe()
         self.graphs = DecodeGraphs(core, self)
@@ -158,7 +159,8 @@ class GpuBackend:
             scratch = self._scratch
         if self.suppress is not None:
             ops.suppress_tokens(logits, self.suppress)
-        ops.sample(logits, self.temperature, self.top_k, self.top_p, self.rng, slot_of_row, out, scratch)
+        ops.sample(logits, self.temperature, self.top_k, self.top_p, self.rng, slot_of_row, out, scratch,
+                   self.sample_split)
         tokens = out.tolist()  # the one synchronisation of a step
         self.h2d_bytes += 4 * len(rows)
         self.d2h_bytes += 4 * len(rows) + 4

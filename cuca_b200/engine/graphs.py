@@ -74,7 +74,8 @@ class DecodeGraph:
         be = self.backend
         if be.suppress is not None:
             ops.suppress_tokens(logits, be.suppress)
-        ops.sample(logits, be.temperature, be.top_k, be.top_p, be.rng, self.slot_of_row, self.sampled, self.scratch)
+        ops.sample(logits, be.temperature, be.top_k, be.top_p, be.rng, self.slot_of_row, self.sampled, self.scratch,
+                   be.sample_split)
         ops.decode_advance(self.tokens, self.positions, self.slot_of_row, self.sampled, self.history, self.counter,
                            MAX_HISTORY, self.core.rt.err, self.sampled[self.bucket:])
 

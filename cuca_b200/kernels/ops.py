@@ -485,7 +485,18 @@ def sample_scratch_words(vocab: int) -> int:
     return n
 
 
-def sample(logits, temperature, top_k, top_p, rng_state, slot_of_row, out, scratch=None) -> None:
+class SampleSplit:
+    """Scratch with which the greedy rows of a large vocabulary are cut over several CTAs each: per row the best of
+    every part and a counter of the parts that have arrived (left zeroed by every launch). One per engine; a
+    launch with more rows than it holds runs one CTA per row."""
+
+    def __init__(self, rows: int, device):
+        self.rows = int(rows)
+        self.best = torch.zeros(self.rows * int(library.load().cuca_sample_max_split()), dtype=torch.int64, device=device)
+        self.count = torch.zeros(self.rows, dtype=torch.int32, device=device)
+
+
+def sample(logits, temperature, top_k, top_p, rng_state, slot_of_row, out, scratch=None, split: SampleSplit | None = None) -> None:
     """One token per row of `logits` [R, V] (32-bit). temperature/top_p: float32 [slots]; top_k: int32 [slots];
     rng_state: int64 [slots] SplitMix64 states, advanced for rows that draw; slot_of_row: int32 [R];
     scratch: int64 [R, words] for rows whose cut is wider than 1024 candidates (see `sample_scratch_words`)."""
@@ -493,7 +504,9 @@ def sample(logits, temperature, top_k, top_p, rng_state, slot_of_row, out, scrat
     lib = library.load()
     library.check(lib.cuca_sample(_p(logits), logits.stride(0), logits.shape[0], logits.shape[1], _p(temperature),
                                   _p(top_k), _p(top_p), _p(rng_state), _p(slot_of_row), _p(out), _p(scratch),
-                                  0 if scratch is None else scratch.shape[1], _stream()), "sample")
+                                  0 if scratch is None else scratch.shape[1],
+                                  None if split is None else _p(split.best), None if split is None else _p(split.count),
+                                  0 if split is None else split.rows, _stream()), "sample")
 
 
 def decode_advance(tokens, positions, slot_of_row, sampled, history, counter, max_steps, err=None,

@@ -70,6 +70,43 @@ def test_sampler_matches_plain_on_every_path(V):
             assert same >= 22, f"case {i} {cases[i]}: only {same}/24 draws agree"
 
 
+@pytest.mark.parametrize("V", [8193, 50000, 128256, 300000])
+def test_greedy_rows_cut_over_several_ctas_give_the_one_ctas_token(V):
+    """A greedy row of a large vocabulary is cut over several CTAs (`SampleSplit`): the first maximum wins as with one
+    CTA, wherever it lies (in the first or the last part, at a part's edge, tied across parts), rows that draw and
+    padding rows beside it are untouched, and the arrival counters are zero again after every launch."""
+    import torch
+    from cuca_b200.kernels import ops
+    dev = torch.device("cuda:0")
+    rs = np.random.default_rng(V)
+    R = 9
+    logits = torch.tensor((rs.standard_normal((R, V)) * 3).astype(np.float32), device=dev)
+    per = -(-V // min(32, -(-V // 8192)))
+    logits[0, V - 1] = 50.0                      # in the last part
+    logits[1, 0] = 50.0                          # in the first
+    logits[2, per - 1] = logits[2, per] = 50.0   # tied across the edge of two parts: the lower id wins
+    logits[3, 7] = logits[3, V - 3] = 50.0       # tied across far parts
+    logits[4, :] = float("-inf")                 # nothing above -inf: id 0
+    logits[5, 5] = float("nan")                  # a NaN never wins
+    slot_of_row = torch.tensor([0, 1, 2, 3, 4, 5, -1, 6, 7], dtype=torch.int32, device=dev)
+    temperature = torch.tensor([0, 0, 0, 0, 0, 0, 0.8, 0], dtype=torch.float32, device=dev)
+    top_k = torch.full((8,), 64, dtype=torch.int32, device=dev)
+    top_p = torch.full((8,), 0.95, dtype=torch.float32, device=dev)
+    split = ops.SampleSplit(16, dev)
+    outs = []
+    for use in (None, split, split):
+        rng = torch.arange(8, dtype=torch.int64, device=dev) + 100
+        out = torch.full((R,), -7, dtype=torch.int32, device=dev)
+        ops.sample(logits, temperature, top_k, top_p, rng, slot_of_row, out, None, use)
+        torch.cuda.synchronize()
+        outs.append(out.tolist())
+        assert int(split.count.abs().sum().item()) == 0
+    assert outs[0] == outs[1] == outs[2]
+    assert outs[0][:5] == [V - 1, 0, per - 1, 7, 0] and outs[0][6] == -1
+    assert outs[0][5] == int(torch.argmax(torch.nan_to_num(logits[5], nan=-1e30)))
+    assert outs[0][8] == int(torch.argmax(logits[8]))
+
+
 def test_sampler_statistics_follow_the_distribution():
     V = 50
     logits = np.linspace(-2, 2, V, dtype=np.float32)[None, :].repeat(4, 0)
