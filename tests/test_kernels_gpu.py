@@ -198,11 +198,14 @@ def test_rmsnorm(dev):
         assert torch.allclose(out, ref[[T - 1, 0]], atol=1e-5, rtol=1e-5)
 
 
-def test_embed_and_bad_token(dev):
+@pytest.mark.parametrize("E,dtype", [(24, torch.bfloat16), (4096, torch.bfloat16), (4100, torch.bfloat16), (30, torch.bfloat16),
+                                     (24, torch.float32), (22, torch.float32)])
+def test_embed_and_bad_token(dev, E, dtype):
+    """Rows of 16-byte multiples take the vector path, others one value at a time."""
     from cuca_b200.kernels import ops
-    table = torch.randn(50, 24, device=dev).bfloat16()
+    table = torch.randn(50, E, device=dev).to(dtype)
     toks = torch.tensor([3, 49, 0, 7], device=dev, dtype=torch.int32)
-    out = torch.empty(4, 24, device=dev)
+    out = torch.empty(4, E, device=dev)
     err = torch.zeros(1, dtype=torch.int32, device=dev)
     ops.embed(table, toks, out, err)
     assert torch.equal(out, table[toks.long()].float()) and int(err.item()) == 0
