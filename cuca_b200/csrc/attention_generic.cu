@@ -90,6 +90,11 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
 
 }  // namespace
 
+// The largest head size any attention kernel of this library takes (the plain kernel's; the tensor-core forms take
+// fewer). A part asks at construction, so that a model with larger heads is refused when it is built, not at its
+// first step.
+CUCA_API int cuca_attention_max_head_dim() { return 256; }
+
 // q: rows of `q_stride` elements whose first nh*d hold the (rotated) query
 // heads; out: [n_rows, out_stride]; pools [n_blocks][nkv][bs][d]. Row r is at
 // position positions[r] of sequence seq_of_row[r] (< 0: padding, skipped) and
@@ -100,7 +105,7 @@ CUCA_API int cuca_attention_generic(const void* q, int q_stride, void* out, int 
                                     int table_stride, int n_rows, int nh, int nkv, int d, float scale,
                                     int window, int* err, cudaStream_t stream) {
   if (n_rows == 0) return 0;
-  CUCA_REQUIRE(d > 0 && d <= 256, "attention: head size %d is outside 1..256", d);
+  CUCA_REQUIRE(d > 0 && d <= cuca_attention_max_head_dim(), "attention: head size %d is outside 1..%d", d, cuca_attention_max_head_dim());
   CUCA_REQUIRE(nkv > 0 && nh % nkv == 0, "attention: %d query heads do not group over %d key heads", nh, nkv);
   CUCA_REQUIRE(n_rows <= 65535, "attention: %d rows in one step exceed the launch limit 65535", n_rows);
   dim3 grid((nh + 3) / 4, n_rows);

@@ -38,6 +38,7 @@ _SIGNATURES = {
     "cuca_scatter_int": [_P, _P, _P, _I, ctypes.c_longlong, _P],
     "cuca_sample": [_P, c_size_t, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _P],
     "cuca_sample_max_split": [],
+    "cuca_attention_max_head_dim": [],
     "cuca_attention_mma_supported": [_I, _I, _I, _I, _I],
     "cuca_attention_decode": [_P, _I, _P, _I, _P, _P, _I, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _I, _I, _I,
                               _P, _P, _P, _P],

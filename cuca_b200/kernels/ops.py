@@ -419,6 +419,11 @@ def attention_tc_supported(q, out, kpool, vpool, n_heads, n_kv_heads, head_dim) 
                                                 out.stride(0), _p(q), _p(kpool), _p(vpool)))
 
 
+def attention_max_head_dim() -> int:
+    """The largest head size the attention kernels take."""
+    return int(library.load().cuca_attention_max_head_dim())
+
+
 def attention_pair_tiles_mode(mode: int) -> None:
     """When a CTA of the tcgen05 prefill attention takes two tiles in turn (a heavy and a light one): 1 where that
     makes one round of CTAs out of more, 0 never, 2 whenever a launch has two tiles (tests), -1 as the environment

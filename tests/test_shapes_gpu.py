@@ -60,3 +60,26 @@ def test_odd_shapes_whole_prompts(folders, name):
     steps = ru.trace_whole(reqs)
     got = ru.run_in_process(folders[name], "bfloat16", steps, ru.peak_tokens(steps))
     ru.compare(steps, got, reqs, ru.Oracle(folders[name]), TOL["bfloat16"])
+
+
+@pytest.mark.parametrize("d,nh,nkv,hidden,ff,vocab", [(40, 4, 2, 96, 136, 301), (10, 6, 3, 64, 51, 13), (2, 3, 1, 7, 51, 301),
+                                                      (136, 2, 1, 272, 136, 301), (250, 1, 1, 250, 51, 301)])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_head_sizes_that_are_no_multiple_of_16(tmp_path, d, nh, nkv, hidden, ff, vocab, dtype):
+    """Any even head size up to 256, odd widths, a vocabulary of 13: the plain kernels take them in both precisions."""
+    from cuca_b200.weights.random_init import write_random_model
+    cfg = _cfg(2, hidden, nh, nkv, d, ff, vocab)
+    write_random_model(tmp_path, cfg, d, std=0.05, dtype=torch.bfloat16, norm_std=0.2)
+    reqs = {f"r{n}": tiny.random_tokens(n, vocab, seed=n) for n in (5, 70, 200)}
+    oracle = ru.Oracle(tmp_path)
+    for steps in (ru.trace_whole(reqs), ru.trace_tail_one_by_one(reqs), ru.trace_mixed(reqs, max_live=3, seed=1)):
+        got = ru.run_in_process(tmp_path, dtype, steps, ru.peak_tokens(steps))
+        ru.compare(steps, got, reqs, oracle, TOL[dtype])
+
+
+def test_a_head_size_beyond_the_kernels_is_refused_when_the_model_is_built(tmp_path):
+    from cuca_b200.engine.core import EngineCore
+    from cuca_b200.weights.random_init import write_random_model
+    with pytest.raises(ValueError, match="head size 320"):  # already when the parts are put together for the folder
+        write_random_model(tmp_path, _cfg(1, 64, 2, 1, 320, 51, 301), 1, std=0.05, dtype=torch.bfloat16)
+        EngineCore.from_folder(tmp_path, dtype="bfloat16", kv_tokens=256, max_sequences=4, block_size=16)
