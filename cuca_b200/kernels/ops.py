@@ -419,9 +419,9 @@ def attention_tc_supported(q, out, kpool, vpool, n_heads, n_kv_heads, head_dim) 
                                                 out.stride(0), _p(q), _p(kpool), _p(vpool)))
 
 
-def attention_max_head_dim() -> int:
-    """The largest head size the attention kernels take."""
-    return int(library.load().cuca_attention_max_head_dim())
+# The largest head size the attention kernels take (`cuca_attention_max_head_dim` says the same; a constant here so
+# that describing a model, as for writing a folder of random weights, does not need the kernel library).
+ATTENTION_MAX_HEAD_DIM = 256
 
 
 def attention_pair_tiles_mode(mode: int) -> None:

@@ -41,9 +41,9 @@ class PagedAttention(Mixer):
         self.shares_cache = bool(p.get("shares_cache", False))
         if self.n_heads % self.n_kv_heads:
             raise ValueError(f"{self.n_kv_heads} key heads must divide {self.n_heads} query heads")
-        if not 1 <= self.head_dim <= ops.attention_max_head_dim():
+        if not 1 <= self.head_dim <= ops.ATTENTION_MAX_HEAD_DIM:
             raise ValueError(f"attention: head size {self.head_dim} is outside what the kernels take "
-                             f"(1..{ops.attention_max_head_dim()})")
+                             f"(1..{ops.ATTENTION_MAX_HEAD_DIM})")
         pos = p.get("position")
         self.position = POSITIONS.get(pos.kind)(pos, runtime) if isinstance(pos, PartSpec) else None
         self.w_qkv = self.b_qkv = self.w_o = self.b_o = None

@@ -80,6 +80,8 @@ def test_head_sizes_that_are_no_multiple_of_16(tmp_path, d, nh, nkv, hidden, ff,
 def test_a_head_size_beyond_the_kernels_is_refused_when_the_model_is_built(tmp_path):
     from cuca_b200.engine.core import EngineCore
     from cuca_b200.weights.random_init import write_random_model
+    from cuca_b200.kernels import library, ops
+    assert ops.ATTENTION_MAX_HEAD_DIM == int(library.load().cuca_attention_max_head_dim())
     with pytest.raises(ValueError, match="head size 320"):  # already when the parts are put together for the folder
         write_random_model(tmp_path, _cfg(1, 64, 2, 1, 320, 51, 301), 1, std=0.05, dtype=torch.bfloat16)
         EngineCore.from_folder(tmp_path, dtype="bfloat16", kv_tokens=256, max_sequences=4, block_size=16)
