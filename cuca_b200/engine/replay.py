@@ -86,7 +86,9 @@ def main(argv=None) -> int:
                     help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
     ap.add_argument("--block-size", type=int, default=16, help="positions per page")
     args = ap.parse_args(argv)
-    kv_tokens = -(-args.max_tokens // 64) * 64
+    # --max-tokens counts every live request's tokens rounded up to 64; with larger pages each of those 64 may be a
+    # request of its own that needs a whole page
+    kv_tokens = -(-args.max_tokens // 64) * max(64, args.block_size)
     core = EngineCore.from_folder(args.model, dtype=args.dtype, kv_tokens=kv_tokens, max_sequences=MAX_LIVE,
                                   block_size=args.block_size, window_pools="full")
     Replayer(core, args.out).run(sys.stdin)
