@@ -93,8 +93,7 @@ class GpuBackend:
         g = self.graphs.get(n, max_len, any(self._needs_scratch[s.slot] for s in seqs))
         stepper = self.core.stepper
         handles, slots, tokens = [s.blocks.handle for s in seqs], [s.slot for s in seqs], [p.tokens[0] for p in plans]
-        stepper.check_single_tokens(handles, slots, tokens)  # the refusals of an eager step, before anything runs
-        stepper.upload_table_updates(handles, slots)
+        advance = stepper.single_token_step(handles, slots, tokens)  # an eager step's refusals, the page tables
         g.load_rows(tokens, starts, slots)
         g.replay()
         self.last_graph = g
@@ -104,7 +103,7 @@ class GpuBackend:
         if out[g.bucket]:
             self.core.rt.raise_device_error(out[g.bucket])  # before anything is applied: the step is lost
         tokens = out[:n]
-        stepper.advance(handles, [1] * n)
+        advance()
         self.core.stepper.steps += 1
         self.graph_steps += 1
         return tokens

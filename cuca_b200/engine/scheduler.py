@@ -160,7 +160,7 @@ class Scheduler:
         self.waiting: deque = deque()
         self.running: list = []
         self.finished: list = []
-        self.stats = ServingStats(max_sequences=config.max_sequences)
+        self._stats = ServingStats(max_sequences=config.max_sequences)
         self._next_id = 0
         self._seed_source = seed_source or _default_seed_source()
         self._lib = host.load()
@@ -218,7 +218,6 @@ class Scheduler:
             raise RuntimeError("the plan of a step has more requests than rows: the host core is confused")
         self._events()  # preemptions and failures found while planning
         if n == 0:
-            self._publish()
             return 0
         buf, plans = self._plan_buf, []
         for i in range(n):
@@ -233,7 +232,7 @@ class Scheduler:
             self._events()
             raise
         rows = sum(len(p.tokens) for p in plans)
-        st = self.stats
+        st = self._stats
         st.prefill_rows += sum(len(p.tokens) for p in plans if p.seq.phase == PREFILL)
         toks = [int(t) for t in tokens]
         if lib.cuca_host_sched_apply(self._h, host.ints(toks), len(toks)):
@@ -243,7 +242,6 @@ class Scheduler:
         st.batched_rows += rows
         st.step_seconds += time.perf_counter() - t0
         st.last_step_rows = rows
-        self._publish()
         return rows
 
     def cancel(self, seq: Sequence_) -> None:
@@ -279,7 +277,7 @@ class Scheduler:
                 seq.pending = value
                 if seq.request.temperature > 0:
                     seq.draws += 1
-                self.stats.generated_tokens += 1
+                self._stats.generated_tokens += 1
                 if self._on_token:
                     self._on_token(seq, value)
             elif kind == _EV_PREFILLED:
@@ -293,13 +291,13 @@ class Scheduler:
                 seq.started_at = seq.started_at or time.perf_counter()
                 self.backend.start(seq)
                 self.running.append(seq)
-                self.stats.admissions += 1
+                self._stats.admissions += 1
             elif kind == _EV_PREEMPTED:
                 self.running.remove(seq)
                 seq.prompt = list(seq.request.prompt) + list(seq.completion)
                 seq.phase, seq.pos, seq.pending, seq.slot = PREFILL, 0, None, -1
                 seq.preemptions += 1
-                self.stats.preemptions += 1
+                self._stats.preemptions += 1
                 self.waiting.appendleft(seq)
             elif kind == _EV_FINISHED:
                 if seq in self.running:
@@ -321,8 +319,15 @@ class Scheduler:
         if getattr(self, "_h", None) and self._seqs.get(sid) is None:
             self._lib.cuca_host_sched_forget(self._h, sid)
 
+    @property
+    def stats(self) -> ServingStats:
+        """The counters, with the queue lengths and the pools' figures as they are now (asked of the host core when
+        read, not at every turn)."""
+        self._publish()
+        return self._stats
+
     def _publish(self) -> None:
-        st, ps = self.stats, self.pools.stats()
+        st, ps = self._stats, self.pools.stats()
         st.running, st.waiting = len(self.running), len(self.waiting)
         st.prefix_hit_tokens = int(self._lib.cuca_host_sched_counter(self._h, 5))
         st.free_blocks, st.used_blocks, st.total_blocks = (min(ps["free_blocks"], default=0),

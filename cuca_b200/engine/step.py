@@ -187,16 +187,19 @@ class Stepper:
     def check_single_tokens(self, handles, slots, tokens) -> None:
         """The host-side refusals of `build`, for a captured step that brings one token per request."""
         n = len(handles)
-        if host.load().cuca_host_step_validate(self.pools._h, n, host.ints(handles), host.ints(slots),
-                                               host.ints([1] * n), host.ints(tokens), self.context_length, self.vocab,
+        self._validate_single(n, host.ints(handles), host.ints(slots), host.ints([1] * n), host.ints(tokens))
+
+    def _validate_single(self, n, hs, ss, ones, ts) -> None:
+        if host.load().cuca_host_step_validate(self.pools._h, n, hs, ss, ones, ts, self.context_length, self.vocab,
                                                self.cache.max_sequences):
             raise StepError(host.last_error())
 
     def upload_table_updates(self, handles, slots) -> None:
         """Page-table entries of these requests that changed since they were last sent, to the device tables."""
+        self._upload_tables(len(handles), host.ints(handles), host.ints(slots))
+
+    def _upload_tables(self, n, hs, ss) -> None:
         lib, staging, pools = host.load(), self._staging, self.pools
-        n = len(handles)
-        hs, ss = host.ints(handles), host.ints(slots)
         for gi in range(pools.n_groups):
             buf = staging.take()
             count = lib.cuca_host_table_updates(pools._h, hs, ss, n, self.cache.table_width, gi, buf.data_ptr(),
@@ -215,6 +218,20 @@ class Stepper:
         """Every request has `counts[i]` more positions cached; pages behind windows go back."""
         if host.load().cuca_host_step_advance(self.pools._h, host.ints(handles), host.ints(counts), len(handles)):
             raise StepError(host.last_error())
+
+    def single_token_step(self, handles, slots, tokens):
+        """What a captured step of one token per request needs of the host before it runs: the refusals of an eager
+        step and the page-table upload, with the requests' handles and slots converted once. Returns a function
+        that advances every request by one position, to be called when the step has run."""
+        n = len(handles)
+        hs, ss, ones = host.ints(handles), host.ints(slots), host.ints([1] * n)
+        self._validate_single(n, hs, ss, ones, host.ints(tokens))
+        self._upload_tables(n, hs, ss)
+
+        def advance():
+            if host.load().cuca_host_step_advance(self.pools._h, hs, ones, n):
+                raise StepError(host.last_error())
+        return advance
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run one step; returns logits [wanted, vocab] (32-bit, on the device) or None if nothing is wanted."""
